@@ -1,0 +1,268 @@
+/*
+ * nerve_cuda_moe.h — C ABI of the CUDA (sm_100a) backend for NERVE's route-native sparse-expert
+ * (MoE) layer with packaged MXFP4 expert weights.
+ *
+ * The reference runtime has no FFI for this path: its seam is Rust-internal, between the
+ * component runner that walks the kernel steps of a mounted component
+ *   runtime-rs/src/vulkan_stream_circuit/component_batch_slice_runner.rs:1867-2009 (run_segment)
+ * and the Vulkan device object that owns buffers and dispatches
+ *   runtime-rs/src/vulkan_compute/compute_device_dispatch.rs:2-273
+ *   runtime-rs/src/vulkan_compute/resident_buffers.rs:39-232.
+ * This header is what a `cuda-backend` crate would bind at that seam.  It mirrors the device
+ * object model (device, resident buffer, create-once/run-many plan), the binding order of each MoE
+ * operator (runtime-rs/src/vulkan_stream_circuit/circuit_binding_builder.rs:1-96) and the buffer
+ * contracts of the shaders, so that the runtime's slot planner and package layout stay untouched.
+ *
+ * Conventions
+ *   - every call returns 0 on success or a negative nvmoe_status; the text of the last failure is
+ *     kept per device (the reference returns Result<_, VulkanError(String)>,
+ *     runtime-rs/src/vulkan_compute/features.rs:276-285);
+ *   - argument validation is eager and happens before any launch
+ *     (compute_device_dispatch.rs:94-130); kernels never fault on bad dynamic metadata, they
+ *     leave the output untouched (fail closed) and raise a bit in the plan's status word;
+ *   - a device object is single-threaded, like the reference's (device_types.rs:13);
+ *   - "word" is a little-endian u32; bf16 values are packed two per word, even element low.
+ *
+ * Buffer contracts (T = batch_width tokens, K = experts_per_token = routed_k + always_count)
+ *   hidden          [T][H] bf16
+ *   router weights  [E][H] bf16 row-major
+ *   logits          [T][ceil(E/2)] words
+ *   routes          [T][K] words, (bf16 weight << 16) | expert id, ascending expert id per token
+ *   intermediates   [T][K*I/2 data words | K schedule words]   (frame = K*I/2 + K words)
+ *   expert outputs  [T][K][H] bf16
+ *   output          [T][H] bf16
+ *   control         7 words {batch_width, expert_start, expert_count, owned_route_count,
+ *                   dispatch_x, dispatch_y, dispatch_z}
+ *   address table   32-byte records {device_address u64, byte_count u64, generation u64,
+ *                   resident u32, representation u32}
+ *                   (runtime-rs/src/vulkan_compute/stable_resource_address_space.rs:1297-1317)
+ *   slot table      expert*P + parameter -> record index or 0xffffffff; P = 4 for gate/up
+ *                   (w1, w1 scales, w3, w3 scales), P = 2 for down (w2, w2 scales)
+ *   expert weight   I8 [rows][cols/2], low nibble = even column; scales F8_E8M0 [rows][cols/32]
+ *                   (nerve/model_package_independent_experts.py:182-257)
+ *   telemetry       [R_total counts | R_total(R_total-1)/2 pair counts] u32
+ */
+#ifndef NERVE_CUDA_MOE_H
+#define NERVE_CUDA_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct nvmoe_device nvmoe_device;
+typedef struct nvmoe_buffer nvmoe_buffer;
+typedef struct nvmoe_plan nvmoe_plan;
+
+typedef enum nvmoe_status {
+    NVMOE_OK = 0,
+    NVMOE_ERR_INVALID_ARGUMENT = -1, /* geometry, sizes, null handles, range overflow */
+    NVMOE_ERR_CUDA = -2,             /* a CUDA runtime call failed; text holds its message */
+    NVMOE_ERR_TIMEOUT = -3,          /* nvmoe_sync ran out of time */
+    NVMOE_ERR_OUT_OF_MEMORY = -4,
+    NVMOE_ERR_UNSUPPORTED = -5,      /* valid in the reference but not built here */
+    NVMOE_ERR_COLLECTIVE = -6,       /* expert-parallel exchange failed */
+    NVMOE_ERR_DEVICE_STATUS = -7     /* a kernel raised a fail-closed status bit */
+} nvmoe_status;
+
+/* Which reference router shader the plan's route call follows. */
+typedef enum nvmoe_router_kind {
+    NVMOE_ROUTER_SCORE_TOPK = 0,   /* moe_router_score_topk_batch1_bf16.comp.template */
+    NVMOE_ROUTER_TOPK_SOFTMAX = 1, /* moe_topk_bf16.comp.template (softmax over the k selected) */
+    NVMOE_ROUTER_TOPK_ROUTED = 2   /* moe_topk_routed_batch1_bf16.comp.template */
+} nvmoe_router_kind;
+
+typedef enum nvmoe_router_activation {
+    NVMOE_ACT_SIGMOID = 0,
+    NVMOE_ACT_SOFTMAX = 1,
+    NVMOE_ACT_SQRT_SOFTPLUS = 2
+} nvmoe_router_activation;
+
+typedef enum nvmoe_bias_dtype { NVMOE_BIAS_NONE = 0, NVMOE_BIAS_F32 = 1, NVMOE_BIAS_BF16 = 2 } nvmoe_bias_dtype;
+
+/* Bits of the device status word (nvmoe_plan_status). */
+enum {
+    NVMOE_STATUS_ROUTE_NONFINITE = 1u << 0,   /* a token had no selectable finite score */
+    NVMOE_STATUS_ROUTE_OUT_OF_RANGE = 1u << 1,/* compact slot or expert id out of range: skipped */
+    NVMOE_STATUS_EXPERT_NOT_RESIDENT = 1u << 2,/* address record failed validation: skipped */
+    NVMOE_STATUS_WAIT_EXPIRED = 1u << 3       /* a bounded in-kernel wait gave up */
+};
+
+/*
+ * Everything the reference bakes into shader file names and template constants
+ * (nerve/model_package_moe_routing.py:51-82,160-213; nerve/circuit_lowering_sparse_experts.py:80-211).
+ * Fields marked "extension" have no counterpart in the reference; their zero/one defaults give
+ * the reference behaviour.
+ */
+typedef struct nvmoe_geometry {
+    uint32_t hidden_size;        /* H, multiple of 32 (the reference insists on 128) */
+    uint32_t intermediate_size;  /* I, multiple of 32 */
+    uint32_t routed_experts;     /* E = routed_resource_count, 0 < k <= E, E + always <= 4096 */
+    uint32_t routed_k;           /* routed_selection_count */
+    uint32_t always_count;       /* always-selected resources appended with ids E.. */
+    float always_weight;         /* their common route weight */
+    uint32_t router_kind;        /* nvmoe_router_kind */
+    uint32_t activation;         /* nvmoe_router_activation (SCORE_TOPK; ROUTED uses sigmoid flag) */
+    uint32_t normalize_selected; /* NORMALIZE_SELECTED */
+    uint32_t bias_dtype;         /* nvmoe_bias_dtype of the selection bias */
+    float routed_scale;          /* ROUTED_SCALE applied by the router */
+    float logit_softcap;         /* TOPK_ROUTED only; 0 = off */
+    uint32_t n_group;            /* extension: group-limited routing, 0 = off */
+    uint32_t topk_group;         /* extension: groups kept */
+    float swiglu_limit;          /* SWIGLU_LIMIT, 0 = off */
+    float swiglu_alpha;          /* extension: sigmoid slope, 1 = reference */
+    float swiglu_up_offset;      /* extension: added to the up value, 0 = reference */
+    uint32_t act_block;          /* activation quantisation block: 128 = reference; 32 for shapes
+                                    that 128 does not divide (extension) */
+    uint32_t gate_tile_rows;     /* TILE_ROWS of the gate/up shader (32): only shapes control.dispatch_x */
+    uint32_t down_tile_rows;     /* TILE_ROWS of the down shader (64) */
+    float reduce_scale;          /* ROUTED_SCALE of moe_reduce (1.0 when the router already scaled) */
+    uint32_t max_tokens;         /* largest batch_width any call will pass */
+} nvmoe_geometry;
+
+/* Fills a geometry with the reference defaults for the given sizes. */
+void nvmoe_geometry_default(nvmoe_geometry* g, uint32_t hidden, uint32_t intermediate,
+                            uint32_t experts, uint32_t k);
+
+/* ---- device and resident buffers --------------------------------------------------------- */
+
+/* VulkanComputeDevice::new_for_device_uuid (vulkan_compute/mxfp4_tests.rs:56). */
+int nvmoe_device_open(int cuda_ordinal, nvmoe_device** out);
+void nvmoe_device_close(nvmoe_device* device);
+/* Text of the last error on this device; valid until the next failing call. With a null device
+ * it returns the text of the last failed nvmoe_device_open of this thread. */
+const char* nvmoe_last_error(const nvmoe_device* device);
+/* The CUDA stream every launch of this device uses (a cudaStream_t). */
+void* nvmoe_device_stream(const nvmoe_device* device);
+
+/* create_resident_buffer / write_bytes[_at] / read_bytes[_at] / device_address
+ * (vulkan_compute/resident_buffers.rs:39-232). Buffers are zero-filled at creation. */
+int nvmoe_buffer_create(nvmoe_device* device, size_t bytes, nvmoe_buffer** out);
+void nvmoe_buffer_destroy(nvmoe_buffer* buffer);
+int nvmoe_buffer_write(nvmoe_buffer* buffer, size_t offset, const void* src, size_t bytes);
+int nvmoe_buffer_read(nvmoe_buffer* buffer, size_t offset, void* dst, size_t bytes);
+int nvmoe_buffer_fill(nvmoe_buffer* buffer, size_t offset, int byte_value, size_t bytes);
+uint64_t nvmoe_buffer_device_address(const nvmoe_buffer* buffer);
+size_t nvmoe_buffer_byte_capacity(const nvmoe_buffer* buffer);
+
+/* Bounded wait for everything queued on the device (run_resident_kernel_sequence's
+ * wait-with-timeout, vulkan_compute/compute_device_sequence.rs:746). */
+int nvmoe_sync(nvmoe_device* device, uint64_t timeout_ns);
+
+/* ---- plan: one MoE layer geometry, created once and run many times ------------------------ */
+
+int nvmoe_plan_create(nvmoe_device* device, const nvmoe_geometry* geometry, nvmoe_plan** out);
+void nvmoe_plan_destroy(nvmoe_plan* plan);
+/* Reads and clears the device status word (synchronises the stream). */
+int nvmoe_plan_status(nvmoe_plan* plan, uint32_t* status_bits);
+/* Chooses the expert kernels: 0 = automatic, 1 = CUDA-core dequant-GEMV, 2 = tcgen05 grouped MMA. */
+int nvmoe_plan_set_expert_path(nvmoe_plan* plan, int path);
+
+/* Router projection, op `linear` (runtime-rs/shaders/linear_bf16.comp.template:39-95).
+ * bindings: 0 hidden, 1 logits, 2 router weights. */
+int nvmoe_router_linear(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hidden,
+                        nvmoe_buffer* logits, const nvmoe_buffer* router_weights);
+
+/* op `moe_route` (moe_router_score_topk_batch1_bf16.comp.template:109-220, moe_topk_bf16.comp.template:44-145,
+ * moe_topk_routed_batch1_bf16.comp.template:71-182). bindings: 0 logits, 1 routes, 2 bias, 3 telemetry
+ * (tests/test_model_package_moe_components.py:490-492). bias may be null when bias_dtype is NONE;
+ * telemetry may be null. */
+int nvmoe_route(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* logits,
+                nvmoe_buffer* routes, const nvmoe_buffer* bias, nvmoe_buffer* telemetry);
+
+/* Route scheduler in front of gate/up (runtime-rs/shaders/moe_route_compact_batch1.comp.template:26-105).
+ * bindings: 1 routes, 2 intermediates, 3 slots (optional), 31 control. The caller writes
+ * {batch_width, expert_start, expert_count, 0,0,0,0} into control first; expert_count == 0 selects
+ * the stable expert-major ranking, otherwise the owned-route filter in source order. */
+int nvmoe_route_compact(nvmoe_plan* plan, const nvmoe_buffer* routes, nvmoe_buffer* intermediates,
+                        const nvmoe_buffer* gate_up_slots, nvmoe_buffer* control);
+
+/* Route counter in front of down (runtime-rs/shaders/moe_route_count_batch1.comp.template:21-58).
+ * bindings: 1 routes, 3 slots (optional), 31 control. */
+int nvmoe_route_count(nvmoe_plan* plan, const nvmoe_buffer* routes, const nvmoe_buffer* down_slots,
+                      nvmoe_buffer* control);
+
+/* Shared activation pre-quantisation (runtime-rs/shaders/quantize_batch_fp8_e4m3.comp.template:47-71).
+ * bindings: 0 input [rows][columns] bf16, 1 quantised [rows][columns] E4M3 bytes, 2 scales
+ * [rows][columns/block] f32. block is geometry.act_block. */
+int nvmoe_quantize_fp8(nvmoe_plan* plan, uint32_t rows, uint32_t columns, const nvmoe_buffer* input,
+                       nvmoe_buffer* quantized, nvmoe_buffer* scales);
+
+/* op `independent_sparse_moe_gate_up`
+ * (runtime-rs/shaders/independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:643-802).
+ * bindings: 0 hidden, 1 routes, 2 intermediates, 3 addresses, 4 slots, 31 control. Reads the
+ * compact list from the schedule words of `intermediates` exactly as the shader does. */
+int nvmoe_gate_up(nvmoe_plan* plan, const nvmoe_buffer* hidden, const nvmoe_buffer* routes,
+                  nvmoe_buffer* intermediates, const nvmoe_buffer* addresses,
+                  const nvmoe_buffer* slots, const nvmoe_buffer* control);
+
+/* The `_prequant` variant: bindings 0 q_hidden, 1 scales, 2 routes, 3 intermediates, 4 addresses,
+ * 5 slots, 31 control (same template, PREQUANTIZED_INPUT = 1). */
+int nvmoe_gate_up_prequant(nvmoe_plan* plan, const nvmoe_buffer* quantized_hidden,
+                           const nvmoe_buffer* hidden_scales, const nvmoe_buffer* routes,
+                           nvmoe_buffer* intermediates, const nvmoe_buffer* addresses,
+                           const nvmoe_buffer* slots, const nvmoe_buffer* control);
+
+/* op `independent_sparse_moe_down`
+ * (runtime-rs/shaders/independent_sparse_moe_down_batch1_mxfp4.comp.template:507-610).
+ * bindings: 0 intermediates, 1 routes, 2 outputs, 3 addresses, 4 slots, 31 control. */
+int nvmoe_down(nvmoe_plan* plan, const nvmoe_buffer* intermediates, const nvmoe_buffer* routes,
+               nvmoe_buffer* outputs, const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
+               const nvmoe_buffer* control);
+
+/* op `moe_reduce` (runtime-rs/shaders/moe_reduce_batch1_bf16.comp.template:29-55).
+ * bindings: 0 expert outputs, 1 output. */
+int nvmoe_reduce(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* expert_outputs,
+                 nvmoe_buffer* output);
+
+/*
+ * The whole chain of nerve/circuit_lowering_sparse_experts.py:80-172 in one call:
+ * linear -> moe_route -> (compact -> gate_up) -> (count -> down) -> moe_reduce, with the
+ * intermediate frames held in plan-owned memory. router_weights may be null when `logits` is
+ * supplied instead (then the projection is skipped). routes_out, telemetry and logits are optional.
+ * expert_start/expert_count describe the experts this device owns (0,0 = all).
+ */
+typedef struct nvmoe_layer_args {
+    uint32_t batch_width;
+    uint32_t expert_start;
+    uint32_t expert_count;
+    const nvmoe_buffer* hidden;
+    const nvmoe_buffer* router_weights;
+    nvmoe_buffer* logits;
+    const nvmoe_buffer* bias;
+    const nvmoe_buffer* gate_up_addresses;
+    const nvmoe_buffer* gate_up_slots;
+    const nvmoe_buffer* down_addresses;
+    const nvmoe_buffer* down_slots;
+    nvmoe_buffer* output;
+    nvmoe_buffer* routes_out;
+    nvmoe_buffer* telemetry;
+} nvmoe_layer_args;
+
+int nvmoe_layer(nvmoe_plan* plan, const nvmoe_layer_args* args);
+
+/* Host-buffer form of nvmoe_layer: copies `hidden` in from host memory and `output` back inside
+ * the call (pinned staging owned by the plan) — the call a runtime makes per decode step. */
+int nvmoe_layer_host(nvmoe_plan* plan, const nvmoe_layer_args* args, const void* hidden_host,
+                     void* output_host);
+
+/* Device time of the last nvmoe_layer call in milliseconds (CUDA events on the device stream);
+ * the per-stage report mirrors RuntimeSparseMoeWorkReport
+ * (runtime-rs/src/vulkan_stream_circuit/sparse_moe_execution.rs:176-208). */
+typedef struct nvmoe_work_report {
+    float total_ms;
+    uint32_t batch_width;
+    uint32_t routes;
+    uint32_t distinct_experts;
+    uint32_t kernel_launches;
+    uint64_t weight_bytes_touched;
+} nvmoe_work_report;
+int nvmoe_plan_last_report(nvmoe_plan* plan, nvmoe_work_report* report);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NERVE_CUDA_MOE_H */
