@@ -159,11 +159,17 @@ void nvmoe_plan_destroy(nvmoe_plan* plan);
 int nvmoe_plan_status(nvmoe_plan* plan, uint32_t* status_bits);
 /* Chooses the expert kernels: 0 = automatic, 1 = CUDA-core dequant-GEMV, 2 = tcgen05 grouped MMA. */
 int nvmoe_plan_set_expert_path(nvmoe_plan* plan, int path);
+/* With profiling on, nvmoe_layer brackets every stage with CUDA events (nvmoe_work_report.stage_ms),
+ * the counterpart of the per-step GPU timestamps of
+ * runtime-rs/src/vulkan_compute/compute_device_sequence.rs:27-190. Off by default. */
+int nvmoe_plan_set_profiling(nvmoe_plan* plan, int enabled);
 
-/* Router projection, op `linear` (runtime-rs/shaders/linear_bf16.comp.template:39-95).
- * bindings: 0 hidden, 1 logits, 2 router weights. */
+/* Router projection, op `linear` (runtime-rs/shaders/linear_bf16.comp.template:39-95) or, with a
+ * non-null bias, `linear_bias` (runtime-rs/shaders/linear_bias_bf16.comp.template:31-84).
+ * bindings: 0 hidden, 1 logits, 2 router weights, 3 bias [E] bf16. */
 int nvmoe_router_linear(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hidden,
-                        nvmoe_buffer* logits, const nvmoe_buffer* router_weights);
+                        nvmoe_buffer* logits, const nvmoe_buffer* router_weights,
+                        const nvmoe_buffer* router_bias);
 
 /* op `moe_route` (moe_router_score_topk_batch1_bf16.comp.template:109-220, moe_topk_bf16.comp.template:44-145,
  * moe_topk_routed_batch1_bf16.comp.template:71-182). bindings: 0 logits, 1 routes, 2 bias, 3 telemetry
@@ -175,14 +181,17 @@ int nvmoe_route(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* logi
 /* Route scheduler in front of gate/up (runtime-rs/shaders/moe_route_compact_batch1.comp.template:26-105).
  * bindings: 1 routes, 2 intermediates, 3 slots (optional), 31 control. The caller writes
  * {batch_width, expert_start, expert_count, 0,0,0,0} into control first; expert_count == 0 selects
- * the stable expert-major ranking, otherwise the owned-route filter in source order. */
-int nvmoe_route_compact(nvmoe_plan* plan, const nvmoe_buffer* routes, nvmoe_buffer* intermediates,
-                        const nvmoe_buffer* gate_up_slots, nvmoe_buffer* control);
+ * the stable expert-major ranking, otherwise the owned-route filter in source order.
+ * batch_width is the host's copy of control[0]: it sizes the launch, as the reference host sizes its
+ * dispatch (component_batch_slice_runner.rs:909-918); kernels use min(control[0], batch_width). */
+int nvmoe_route_compact(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* routes,
+                        nvmoe_buffer* intermediates, const nvmoe_buffer* gate_up_slots,
+                        nvmoe_buffer* control);
 
 /* Route counter in front of down (runtime-rs/shaders/moe_route_count_batch1.comp.template:21-58).
  * bindings: 1 routes, 3 slots (optional), 31 control. */
-int nvmoe_route_count(nvmoe_plan* plan, const nvmoe_buffer* routes, const nvmoe_buffer* down_slots,
-                      nvmoe_buffer* control);
+int nvmoe_route_count(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* routes,
+                      const nvmoe_buffer* down_slots, nvmoe_buffer* control);
 
 /* Shared activation pre-quantisation (runtime-rs/shaders/quantize_batch_fp8_e4m3.comp.template:47-71).
  * bindings: 0 input [rows][columns] bf16, 1 quantised [rows][columns] E4M3 bytes, 2 scales
@@ -194,13 +203,15 @@ int nvmoe_quantize_fp8(nvmoe_plan* plan, uint32_t rows, uint32_t columns, const 
  * (runtime-rs/shaders/independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:643-802).
  * bindings: 0 hidden, 1 routes, 2 intermediates, 3 addresses, 4 slots, 31 control. Reads the
  * compact list from the schedule words of `intermediates` exactly as the shader does. */
-int nvmoe_gate_up(nvmoe_plan* plan, const nvmoe_buffer* hidden, const nvmoe_buffer* routes,
-                  nvmoe_buffer* intermediates, const nvmoe_buffer* addresses,
-                  const nvmoe_buffer* slots, const nvmoe_buffer* control);
+int nvmoe_gate_up(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hidden,
+                  const nvmoe_buffer* routes, nvmoe_buffer* intermediates,
+                  const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
+                  const nvmoe_buffer* control);
 
 /* The `_prequant` variant: bindings 0 q_hidden, 1 scales, 2 routes, 3 intermediates, 4 addresses,
- * 5 slots, 31 control (same template, PREQUANTIZED_INPUT = 1). */
-int nvmoe_gate_up_prequant(nvmoe_plan* plan, const nvmoe_buffer* quantized_hidden,
+ * 5 slots, 31 control (same template, PREQUANTIZED_INPUT = 1). The f32 scales may be any positive
+ * value (both pre-quantisation contracts of nerve/physical_representations.py:9-12). */
+int nvmoe_gate_up_prequant(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* quantized_hidden,
                            const nvmoe_buffer* hidden_scales, const nvmoe_buffer* routes,
                            nvmoe_buffer* intermediates, const nvmoe_buffer* addresses,
                            const nvmoe_buffer* slots, const nvmoe_buffer* control);
@@ -208,9 +219,9 @@ int nvmoe_gate_up_prequant(nvmoe_plan* plan, const nvmoe_buffer* quantized_hidde
 /* op `independent_sparse_moe_down`
  * (runtime-rs/shaders/independent_sparse_moe_down_batch1_mxfp4.comp.template:507-610).
  * bindings: 0 intermediates, 1 routes, 2 outputs, 3 addresses, 4 slots, 31 control. */
-int nvmoe_down(nvmoe_plan* plan, const nvmoe_buffer* intermediates, const nvmoe_buffer* routes,
-               nvmoe_buffer* outputs, const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
-               const nvmoe_buffer* control);
+int nvmoe_down(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* intermediates,
+               const nvmoe_buffer* routes, nvmoe_buffer* outputs, const nvmoe_buffer* addresses,
+               const nvmoe_buffer* slots, const nvmoe_buffer* control);
 
 /* op `moe_reduce` (runtime-rs/shaders/moe_reduce_batch1_bf16.comp.template:29-55).
  * bindings: 0 expert outputs, 1 output. */
@@ -230,8 +241,9 @@ typedef struct nvmoe_layer_args {
     uint32_t expert_count;
     const nvmoe_buffer* hidden;
     const nvmoe_buffer* router_weights;
+    const nvmoe_buffer* router_bias; /* optional bf16 bias of the router projection */
     nvmoe_buffer* logits;
-    const nvmoe_buffer* bias;
+    const nvmoe_buffer* bias;        /* selection bias of the router, per geometry.bias_dtype */
     const nvmoe_buffer* gate_up_addresses;
     const nvmoe_buffer* gate_up_slots;
     const nvmoe_buffer* down_addresses;
@@ -251,8 +263,15 @@ int nvmoe_layer_host(nvmoe_plan* plan, const nvmoe_layer_args* args, const void*
 /* Device time of the last nvmoe_layer call in milliseconds (CUDA events on the device stream);
  * the per-stage report mirrors RuntimeSparseMoeWorkReport
  * (runtime-rs/src/vulkan_stream_circuit/sparse_moe_execution.rs:176-208). */
+enum { NVMOE_STAGE_LINEAR, NVMOE_STAGE_ROUTE, NVMOE_STAGE_SCHEDULE, NVMOE_STAGE_QUANTIZE_HIDDEN,
+       NVMOE_STAGE_GATE_UP, NVMOE_STAGE_QUANTIZE_INTERMEDIATE, NVMOE_STAGE_DOWN, NVMOE_STAGE_REDUCE,
+       NVMOE_STAGE_COUNT };
 typedef struct nvmoe_work_report {
     float total_ms;
+    float stage_ms[NVMOE_STAGE_COUNT]; /* zeros unless profiling is on */
+    float gate_up_kernel_ms;           /* the gate/up expert kernel alone (profiling on) */
+    float down_kernel_ms;              /* the down expert kernel alone (profiling on) */
+    uint32_t tensor_path;              /* 1 when the expert kernels ran on tcgen05 */
     uint32_t batch_width;
     uint32_t routes;
     uint32_t distinct_experts;

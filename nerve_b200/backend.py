@@ -1,0 +1,306 @@
+"""Host-side mirror of the reference's device object model for the MoE operators.
+
+The reference drives its kernels through ``VulkanComputeDevice`` / ``VulkanResidentBuffer`` /
+resident kernel dispatches (runtime-rs/src/vulkan_compute/compute_device_dispatch.rs:2-273,
+resident_buffers.rs:39-232) with the per-operator binding order of
+runtime-rs/src/vulkan_stream_circuit/circuit_binding_builder.rs:1-96.  This module keeps those
+names, argument meanings and error behaviour (eager validation errors carrying a message, the way
+``VulkanError(String)`` does) on top of the C ABI, so tests written against it read like the
+reference's own conformance tests (runtime-rs/src/vulkan_compute/mxfp4_tests.rs).
+
+Everything here calls the CUDA library; nothing computes on the host.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import capi
+from .synthetic import MoeConfig
+
+UNBOUND_PARAMETER_SLOT = 0xFFFFFFFF
+
+
+class CudaError(RuntimeError):
+    """Counterpart of the reference's ``VulkanError(pub String)``."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+def _ptr(array: np.ndarray):
+    return array.ctypes.data_as(ctypes.c_void_p)
+
+
+class CudaComputeDevice:
+    """``VulkanComputeDevice`` for one CUDA ordinal. Not thread-safe, like the reference's."""
+
+    def __init__(self, ordinal: int = 0):
+        self._lib = capi.load()
+        handle = ctypes.c_void_p()
+        rc = self._lib.nvmoe_device_open(ordinal, ctypes.byref(handle))
+        if rc != 0:
+            raise CudaError(rc, self._lib.nvmoe_last_error(None).decode())
+        self._h = handle
+        self.ordinal = ordinal
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise CudaError(rc, self._lib.nvmoe_last_error(self._h).decode())
+
+    def create_resident_buffer(self, byte_capacity: int) -> "ResidentBuffer":
+        return ResidentBuffer(self, byte_capacity)
+
+    def resident_buffer_from(self, array: np.ndarray) -> "ResidentBuffer":
+        array = np.ascontiguousarray(array)
+        buf = ResidentBuffer(self, max(array.nbytes, 1))
+        if array.nbytes:
+            buf.write_bytes(array)
+        return buf
+
+    def stream(self) -> int:
+        """The ``cudaStream_t`` all launches of this device go to, as an integer."""
+        return int(self._lib.nvmoe_device_stream(self._h) or 0)
+
+    def synchronize(self, timeout_ns: int = 60_000_000_000) -> None:
+        self._check(self._lib.nvmoe_sync(self._h, timeout_ns))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.nvmoe_device_close(self._h)
+            self._h = None
+
+
+class ResidentBuffer:
+    """``VulkanResidentBuffer``: device memory with byte-level read/write and a device address."""
+
+    def __init__(self, device: CudaComputeDevice, byte_capacity: int):
+        self.device = device
+        handle = ctypes.c_void_p()
+        device._check(device._lib.nvmoe_buffer_create(device._h, byte_capacity, ctypes.byref(handle)))
+        self._h = handle
+        self.byte_capacity = byte_capacity
+
+    def write_bytes(self, data, offset: int = 0) -> None:
+        array = np.ascontiguousarray(data) if not isinstance(data, (bytes, bytearray)) else np.frombuffer(data, dtype=np.uint8)
+        self.device._check(self.device._lib.nvmoe_buffer_write(self._h, offset, _ptr(array), array.nbytes))
+
+    write_bytes_at = lambda self, offset, data: self.write_bytes(data, offset)  # noqa: E731
+
+    def read_bytes(self, byte_count: int | None = None, offset: int = 0) -> np.ndarray:
+        byte_count = self.byte_capacity - offset if byte_count is None else byte_count
+        out = np.empty(byte_count, dtype=np.uint8)
+        self.device._check(self.device._lib.nvmoe_buffer_read(self._h, offset, _ptr(out), byte_count))
+        return out
+
+    def read(self, dtype, count: int | None = None, offset: int = 0) -> np.ndarray:
+        itemsize = np.dtype(dtype).itemsize
+        nbytes = None if count is None else count * itemsize
+        return self.read_bytes(nbytes, offset).view(dtype)
+
+    def fill(self, byte_value: int, offset: int = 0, byte_count: int | None = None) -> None:
+        byte_count = self.byte_capacity - offset if byte_count is None else byte_count
+        self.device._check(self.device._lib.nvmoe_buffer_fill(self._h, offset, byte_value, byte_count))
+
+    def device_address(self) -> int:
+        return int(self.device._lib.nvmoe_buffer_device_address(self._h))
+
+    def destroy(self) -> None:
+        if self._h:
+            self.device._lib.nvmoe_buffer_destroy(self._h)
+            self._h = None
+
+
+def address_table(device: CudaComputeDevice, resources: list) -> ResidentBuffer:
+    """32-byte records {address, byte_count, generation = 1, resident = 1, representation = 0}, the
+    way the reference's conformance tests publish them
+    (runtime-rs/src/vulkan_compute/mxfp4_tests.rs:1633-1652)."""
+    words = np.zeros(max(len(resources), 1) * 8, dtype=np.uint32)
+    for slot, res in enumerate(resources):
+        if res is None:
+            continue
+        address, count = res.device_address(), res.byte_capacity
+        words[slot * 8 + 0] = address & 0xFFFFFFFF
+        words[slot * 8 + 1] = address >> 32
+        words[slot * 8 + 2] = count & 0xFFFFFFFF
+        words[slot * 8 + 3] = count >> 32
+        words[slot * 8 + 4] = 1
+        words[slot * 8 + 6] = 1
+    return device.resident_buffer_from(words)
+
+
+@dataclass
+class ExpertBank:
+    """Every expert's packaged tensors as separately resident buffers plus the two table pairs."""
+
+    resources: list
+    gate_up_addresses: ResidentBuffer
+    gate_up_slots: ResidentBuffer
+    down_addresses: ResidentBuffer
+    down_slots: ResidentBuffer
+
+    @staticmethod
+    def upload(device: CudaComputeDevice, w1, s1, w3, s3, w2, s2, present=None) -> "ExpertBank":
+        n = len(w1)
+        present = list(range(n)) if present is None else list(present)
+        keep, gres, dres = [], [], []
+        gslots = np.full(n * 4, UNBOUND_PARAMETER_SLOT, dtype=np.uint32)
+        dslots = np.full(n * 2, UNBOUND_PARAMETER_SLOT, dtype=np.uint32)
+        for e in present:
+            for j, arr in enumerate((w1[e], s1[e], w3[e], s3[e])):
+                buf = device.resident_buffer_from(arr)
+                gslots[e * 4 + j] = len(gres)
+                gres.append(buf)
+            for j, arr in enumerate((w2[e], s2[e])):
+                buf = device.resident_buffer_from(arr)
+                dslots[e * 2 + j] = len(dres)
+                dres.append(buf)
+        keep = gres + dres
+        return ExpertBank(keep, address_table(device, gres), device.resident_buffer_from(gslots),
+                          address_table(device, dres), device.resident_buffer_from(dslots))
+
+
+def geometry_from_config(cfg: MoeConfig, max_tokens: int) -> capi.Geometry:
+    g = capi.Geometry()
+    capi.load().nvmoe_geometry_default(ctypes.byref(g), cfg.hidden, cfg.intermediate, cfg.experts, cfg.k)
+    g.always_count = cfg.always_count
+    g.always_weight = cfg.always_weight
+    g.router_kind = cfg.router_kind
+    g.activation = cfg.activation
+    g.normalize_selected = cfg.normalize_selected
+    g.bias_dtype = cfg.bias_dtype
+    g.routed_scale = cfg.routed_scale
+    g.logit_softcap = cfg.logit_softcap
+    g.n_group = cfg.n_group
+    g.topk_group = cfg.topk_group
+    g.swiglu_limit = cfg.swiglu_limit
+    g.swiglu_alpha = cfg.swiglu_alpha
+    g.swiglu_up_offset = cfg.swiglu_up_offset
+    g.act_block = cfg.act_block
+    g.max_tokens = max_tokens
+    return g
+
+
+def _h(buf):
+    return None if buf is None else buf._h
+
+
+class MoePlan:
+    """One MoE layer geometry: create once, run many (the reference's resident kernel dispatches).
+
+    Method names are the reference's operator names; argument order is its binding order.
+    """
+
+    def __init__(self, device: CudaComputeDevice, geometry: capi.Geometry):
+        self.device = device
+        self.geometry = geometry
+        handle = ctypes.c_void_p()
+        device._check(device._lib.nvmoe_plan_create(device._h, ctypes.byref(geometry), ctypes.byref(handle)))
+        self._h = handle
+        self.experts_per_token = geometry.routed_k + geometry.always_count
+        self.total_experts = geometry.routed_experts + geometry.always_count
+        self.frame_words = self.experts_per_token * geometry.intermediate_size // 2 + self.experts_per_token
+        self.data_words = self.experts_per_token * geometry.intermediate_size // 2
+
+    @classmethod
+    def for_config(cls, device: CudaComputeDevice, cfg: MoeConfig, max_tokens: int) -> "MoePlan":
+        return cls(device, geometry_from_config(cfg, max_tokens))
+
+    def _call(self, name, *args):
+        self.device._check(getattr(self.device._lib, name)(self._h, *args))
+
+    def set_expert_path(self, path: int) -> None:
+        """0 automatic, 1 CUDA-core dequant-GEMV, 2 tcgen05 grouped MMA."""
+        self._call("nvmoe_plan_set_expert_path", path)
+
+    def set_profiling(self, enabled: bool) -> None:
+        self._call("nvmoe_plan_set_profiling", int(enabled))
+
+    def status(self) -> int:
+        bits = ctypes.c_uint32()
+        self._call("nvmoe_plan_status", ctypes.byref(bits))
+        return bits.value
+
+    def telemetry_words(self) -> int:
+        r = self.total_experts
+        return r + r * (r - 1) // 2
+
+    # -- operators, in chain order ---------------------------------------------------------
+    def linear(self, batch_width, hidden, logits, router_weights, router_bias=None):
+        self._call("nvmoe_router_linear", batch_width, _h(hidden), _h(logits), _h(router_weights), _h(router_bias))
+
+    def moe_route(self, batch_width, logits, routes, bias=None, telemetry=None):
+        self._call("nvmoe_route", batch_width, _h(logits), _h(routes), _h(bias), _h(telemetry))
+
+    def moe_route_compact(self, batch_width, routes, intermediates, control, slots=None):
+        self._call("nvmoe_route_compact", batch_width, _h(routes), _h(intermediates), _h(slots), _h(control))
+
+    def moe_route_count(self, batch_width, routes, control, slots=None):
+        self._call("nvmoe_route_count", batch_width, _h(routes), _h(slots), _h(control))
+
+    def quantize_fp8_e4m3(self, rows, columns, input, quantized, scales):
+        self._call("nvmoe_quantize_fp8", rows, columns, _h(input), _h(quantized), _h(scales))
+
+    def independent_sparse_moe_gate_up(self, batch_width, hidden, routes, intermediates, addresses, slots, control):
+        self._call("nvmoe_gate_up", batch_width, _h(hidden), _h(routes), _h(intermediates), _h(addresses), _h(slots),
+                   _h(control))
+
+    def independent_sparse_moe_gate_up_prequant(self, batch_width, q_hidden, scales, routes, intermediates,
+                                                addresses, slots, control):
+        self._call("nvmoe_gate_up_prequant", batch_width, _h(q_hidden), _h(scales), _h(routes), _h(intermediates),
+                   _h(addresses), _h(slots), _h(control))
+
+    def independent_sparse_moe_down(self, batch_width, intermediates, routes, outputs, addresses, slots, control):
+        self._call("nvmoe_down", batch_width, _h(intermediates), _h(routes), _h(outputs), _h(addresses), _h(slots),
+                   _h(control))
+
+    def moe_reduce(self, batch_width, expert_outputs, output):
+        self._call("nvmoe_reduce", batch_width, _h(expert_outputs), _h(output))
+
+    # -- the whole chain -------------------------------------------------------------------
+    def _layer_args(self, batch_width, bank: ExpertBank, hidden=None, output=None, router_weights=None,
+                    router_bias=None, logits=None, bias=None, routes_out=None, telemetry=None, expert_start=0,
+                    expert_count=0) -> capi.LayerArgs:
+        a = capi.LayerArgs()
+        a.batch_width, a.expert_start, a.expert_count = batch_width, expert_start, expert_count
+        a.hidden, a.output = _h(hidden), _h(output)
+        a.router_weights, a.router_bias, a.logits, a.bias = _h(router_weights), _h(router_bias), _h(logits), _h(bias)
+        a.gate_up_addresses, a.gate_up_slots = _h(bank.gate_up_addresses), _h(bank.gate_up_slots)
+        a.down_addresses, a.down_slots = _h(bank.down_addresses), _h(bank.down_slots)
+        a.routes_out, a.telemetry = _h(routes_out), _h(telemetry)
+        return a
+
+    def layer(self, batch_width, bank: ExpertBank, hidden, output, **kw):
+        args = self._layer_args(batch_width, bank, hidden=hidden, output=output, **kw)
+        self._call("nvmoe_layer", ctypes.byref(args))
+
+    def layer_host(self, batch_width, bank: ExpertBank, hidden_host: np.ndarray, output_host: np.ndarray, **kw):
+        """Host buffers in, host buffers out: the copies are inside the call."""
+        assert hidden_host.flags["C_CONTIGUOUS"] and output_host.flags["C_CONTIGUOUS"]
+        args = self._layer_args(batch_width, bank, **kw)
+        self._call("nvmoe_layer_host", ctypes.byref(args), _ptr(hidden_host), _ptr(output_host))
+
+    def last_report(self) -> dict:
+        r = capi.WorkReport()
+        self._call("nvmoe_plan_last_report", ctypes.byref(r))
+        return {
+            "total_ms": r.total_ms,
+            "stage_ms": dict(zip(capi.STAGE_NAMES, list(r.stage_ms))),
+            "gate_up_kernel_ms": r.gate_up_kernel_ms,
+            "down_kernel_ms": r.down_kernel_ms,
+            "tensor_path": bool(r.tensor_path),
+            "batch_width": r.batch_width,
+            "routes": r.routes,
+            "distinct_experts": r.distinct_experts,
+            "kernel_launches": r.kernel_launches,
+            "weight_bytes_touched": r.weight_bytes_touched,
+        }
+
+    def destroy(self) -> None:
+        if self._h:
+            self.device._lib.nvmoe_plan_destroy(self._h)
+            self._h = None

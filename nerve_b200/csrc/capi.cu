@@ -1,0 +1,841 @@
+// C ABI of the CUDA MoE backend (declared in include/nerve_cuda_moe.h): device, resident buffers,
+// plans, the node-granular operators and the fused layer call.  Host code only; the kernels live
+// in the other .cu files of this folder.
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "common.cuh"
+#include "experts_tc.cuh"
+
+using namespace nvmoe;
+
+struct nvmoe_device {
+    int ordinal = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t sync_event = nullptr;
+    std::string error;
+};
+
+struct nvmoe_buffer {
+    nvmoe_device* device = nullptr;
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+namespace {
+
+thread_local std::string g_open_error;
+
+int fail(nvmoe_device* d, int code, const char* fmt, ...) {
+    char text[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(text, sizeof(text), fmt, ap);
+    va_end(ap);
+    if (d) {
+        d->error = text;
+    } else {
+        g_open_error = text;
+    }
+    return code;
+}
+
+#define NVMOE_CUDA(d, call)                                                                      \
+    do {                                                                                         \
+        cudaError_t err__ = (call);                                                              \
+        if (err__ != cudaSuccess)                                                                \
+            return fail((d), err__ == cudaErrorMemoryAllocation ? NVMOE_ERR_OUT_OF_MEMORY : NVMOE_ERR_CUDA, \
+                        "%s failed: %s", #call, cudaGetErrorString(err__));                      \
+    } while (0)
+
+struct DeviceArray {  // plan-owned scratch
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    cudaError_t ensure(size_t want) {
+        if (want <= bytes) return cudaSuccess;
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        bytes = 0;
+        cudaError_t err = cudaMalloc(&ptr, want);
+        if (err == cudaSuccess) bytes = want;
+        return err;
+    }
+    void release() {
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        bytes = 0;
+    }
+    template <class T>
+    T* as() const {
+        return reinterpret_cast<T*>(ptr);
+    }
+};
+
+enum Stage { kStageLinear, kStageRoute, kStageSchedule, kStageQuantX, kStageGateUp, kStageQuantI, kStageDown, kStageReduce, kStageCount };
+
+}  // namespace
+
+struct nvmoe_plan {
+    nvmoe_device* device = nullptr;
+    nvmoe_geometry g{};
+    uint32_t K = 0;            // routes per token
+    uint32_t experts = 0;      // routed + always
+    uint32_t frame_words = 0;
+    int expert_path = 0;
+    // scratch every expert call needs
+    DeviceArray status, gu_ptrs, down_ptrs, grouped[2], offsets[2], block_hist, bucket_base;
+    DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list;
+    // scratch of the fused layer call
+    DeviceArray logits, routes, frames, expert_outputs, controls, hidden_dev, output_dev;
+    void* pinned_in = nullptr;
+    void* pinned_out = nullptr;
+    size_t pinned_bytes = 0;
+    cudaEvent_t ev[kStageCount + 1] = {};
+    cudaEvent_t kernel_ev[2][2] = {};  // [gate_up, down][begin, end] around the expert kernel alone
+    bool events_valid = false;
+    bool profile_stages = false;
+    nvmoe_work_report report{};
+    uint32_t launches = 0;
+};
+
+namespace {
+
+size_t scratch_blocks(const nvmoe_plan* p) { return ((size_t)p->g.max_tokens * p->K + kSortChunk - 1u) / kSortChunk; }
+
+SortScratch sort_scratch(const nvmoe_plan* p) {
+    return SortScratch{p->block_hist.as<uint32_t>(), p->bucket_base.as<uint32_t>(), (uint32_t)scratch_blocks(p),
+                       p->experts + 1u};
+}
+
+int check_buffer(nvmoe_plan* p, const nvmoe_buffer* b, size_t need, const char* what) {
+    if (!b) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "%s buffer is null", what);
+    if (b->device != p->device)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "%s buffer belongs to another device", what);
+    if (b->bytes < need)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "%s buffer holds %zu bytes, the call needs %zu", what,
+                    b->bytes, need);
+    return NVMOE_OK;
+}
+
+int check_tokens(nvmoe_plan* p, uint32_t T) {
+    if (T == 0u) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "batch_width is zero");
+    if (T > p->g.max_tokens)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "batch_width %u exceeds the plan's max_tokens %u", T,
+                    p->g.max_tokens);
+    return NVMOE_OK;
+}
+
+int post_launch(nvmoe_plan* p, const char* what) {
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(p->device, NVMOE_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(err));
+    return NVMOE_OK;
+}
+
+#define NVMOE_TRY(expr)              \
+    do {                             \
+        int rc__ = (expr);           \
+        if (rc__ != NVMOE_OK) return rc__; \
+    } while (0)
+
+bool use_tensor_path(const nvmoe_plan* p) {
+    if (p->expert_path == 1) return false;
+    if (!tc_shape_supported(p->g)) return false;
+    if (p->expert_path == 2) return true;
+    return tc_enabled_by_default();
+}
+
+int validate_geometry(const nvmoe_geometry& g) {
+    auto bad = [](const char* fmt, ...) {
+        char text[256];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(text, sizeof(text), fmt, ap);
+        va_end(ap);
+        g_open_error = text;
+        return (int)NVMOE_ERR_INVALID_ARGUMENT;
+    };
+    if (g.hidden_size == 0u || g.hidden_size % 32u) return bad("hidden_size %u must be a positive multiple of 32", g.hidden_size);
+    if (g.intermediate_size == 0u || g.intermediate_size % 32u)
+        return bad("intermediate_size %u must be a positive multiple of 32", g.intermediate_size);
+    if (!(0u < g.routed_k && g.routed_k <= g.routed_experts && g.routed_experts <= kMaxExperts))
+        return bad("invalid routing geometry r%u k%u", g.routed_experts, g.routed_k);
+    if (g.router_kind > NVMOE_ROUTER_TOPK_ROUTED) return bad("unknown router_kind %u", g.router_kind);
+    if (g.activation > NVMOE_ACT_SQRT_SOFTPLUS) return bad("unknown router activation %u", g.activation);
+    if (g.router_kind == NVMOE_ROUTER_TOPK_ROUTED && g.activation == NVMOE_ACT_SQRT_SOFTPLUS)
+        return bad("the routed top-k router scores with sigmoid or softmax only");
+    if (g.bias_dtype > NVMOE_BIAS_BF16) return bad("unknown bias dtype %u", g.bias_dtype);
+    if (g.always_count && g.router_kind != NVMOE_ROUTER_SCORE_TOPK)
+        return bad("always-selected resources need the score_topk router");
+    if (g.always_count && !(g.always_weight > 0.0f) ) return bad("always-selected weight must be positive and finite");
+    if (g.routed_experts + g.always_count > kMaxExperts) return bad("total resource count exceeds %u", kMaxExperts);
+    if (g.routed_k + g.always_count > kMaxTopK) return bad("more than %u routes per token", kMaxTopK);
+    if (g.n_group) {
+        if (g.n_group > 32u || g.routed_experts % g.n_group || g.topk_group == 0u || g.topk_group > g.n_group ||
+            (g.routed_experts / g.n_group) * g.topk_group < g.routed_k)
+            return bad("invalid group-limited routing n_group %u topk_group %u", g.n_group, g.topk_group);
+    }
+    if (g.act_block == 0u || g.act_block % 32u || g.hidden_size % g.act_block || g.intermediate_size % g.act_block)
+        return bad("act_block %u must be a multiple of 32 dividing hidden and intermediate sizes", g.act_block);
+    if (g.gate_tile_rows == 0u || g.down_tile_rows == 0u) return bad("tile rows must be positive");
+    if (g.max_tokens == 0u) return bad("max_tokens is zero");
+    if ((uint64_t)g.max_tokens * (g.routed_k + g.always_count) > 0x7fffffffull) return bad("max_tokens * routes overflows");
+    return NVMOE_OK;
+}
+
+__global__ void write_control_kernel(uint32_t* control, uint32_t T, uint32_t start, uint32_t count) {
+    if (threadIdx.x < 7u) control[threadIdx.x] = threadIdx.x == 0u ? T : threadIdx.x == 1u ? start : threadIdx.x == 2u ? count : 0u;
+}
+
+}  // namespace
+
+extern "C" {
+
+void nvmoe_geometry_default(nvmoe_geometry* g, uint32_t hidden, uint32_t intermediate, uint32_t experts, uint32_t k) {
+    std::memset(g, 0, sizeof(*g));
+    g->hidden_size = hidden;
+    g->intermediate_size = intermediate;
+    g->routed_experts = experts;
+    g->routed_k = k;
+    g->always_weight = 1.0f;
+    g->router_kind = NVMOE_ROUTER_SCORE_TOPK;
+    g->activation = NVMOE_ACT_SOFTMAX;
+    g->normalize_selected = 1;
+    g->routed_scale = 1.0f;
+    g->swiglu_alpha = 1.0f;
+    g->act_block = 128;
+    g->gate_tile_rows = 32;
+    g->down_tile_rows = 64;
+    g->reduce_scale = 1.0f;
+    g->max_tokens = 1;
+}
+
+int nvmoe_device_open(int cuda_ordinal, nvmoe_device** out) {
+    if (!out) return fail(nullptr, NVMOE_ERR_INVALID_ARGUMENT, "out pointer is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t err = cudaGetDeviceCount(&count);
+    if (err != cudaSuccess) return fail(nullptr, NVMOE_ERR_CUDA, "no CUDA device: %s", cudaGetErrorString(err));
+    if (cuda_ordinal < 0 || cuda_ordinal >= count)
+        return fail(nullptr, NVMOE_ERR_INVALID_ARGUMENT, "CUDA ordinal %d out of range (%d devices)", cuda_ordinal, count);
+    cudaDeviceProp prop;
+    NVMOE_CUDA(nullptr, cudaGetDeviceProperties(&prop, cuda_ordinal));
+    if (prop.major != 10)
+        return fail(nullptr, NVMOE_ERR_UNSUPPORTED, "device %d is sm_%d%d; this backend is built for sm_100a only",
+                    cuda_ordinal, prop.major, prop.minor);
+    NVMOE_CUDA(nullptr, cudaSetDevice(cuda_ordinal));
+    nvmoe_device* d = new (std::nothrow) nvmoe_device();
+    if (!d) return fail(nullptr, NVMOE_ERR_OUT_OF_MEMORY, "out of host memory");
+    d->ordinal = cuda_ordinal;
+    cudaError_t e1 = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+    cudaError_t e2 = e1 == cudaSuccess ? cudaEventCreateWithFlags(&d->sync_event, cudaEventDisableTiming) : e1;
+    if (e2 != cudaSuccess) {
+        if (d->stream) cudaStreamDestroy(d->stream);
+        delete d;
+        return fail(nullptr, NVMOE_ERR_CUDA, "stream setup failed: %s", cudaGetErrorString(e2));
+    }
+    *out = d;
+    return NVMOE_OK;
+}
+
+void nvmoe_device_close(nvmoe_device* d) {
+    if (!d) return;
+    cudaSetDevice(d->ordinal);
+    cudaStreamSynchronize(d->stream);
+    cudaEventDestroy(d->sync_event);
+    cudaStreamDestroy(d->stream);
+    delete d;
+}
+
+const char* nvmoe_last_error(const nvmoe_device* d) { return d ? d->error.c_str() : g_open_error.c_str(); }
+
+void* nvmoe_device_stream(const nvmoe_device* d) { return d ? (void*)d->stream : nullptr; }
+
+int nvmoe_buffer_create(nvmoe_device* d, size_t bytes, nvmoe_buffer** out) {
+    if (!d || !out) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "null device or out pointer");
+    *out = nullptr;
+    if (bytes == 0) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "resident buffer of zero bytes");
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    nvmoe_buffer* b = new (std::nothrow) nvmoe_buffer();
+    if (!b) return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "out of host memory");
+    cudaError_t err = cudaMalloc(&b->ptr, bytes);
+    if (err != cudaSuccess) {
+        delete b;
+        return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(err));
+    }
+    err = cudaMemsetAsync(b->ptr, 0, bytes, d->stream);
+    if (err != cudaSuccess) {
+        cudaFree(b->ptr);
+        delete b;
+        return fail(d, NVMOE_ERR_CUDA, "zero fill failed: %s", cudaGetErrorString(err));
+    }
+    b->device = d;
+    b->bytes = bytes;
+    *out = b;
+    return NVMOE_OK;
+}
+
+void nvmoe_buffer_destroy(nvmoe_buffer* b) {
+    if (!b) return;
+    cudaSetDevice(b->device->ordinal);
+    cudaStreamSynchronize(b->device->stream);
+    cudaFree(b->ptr);
+    delete b;
+}
+
+static int range_ok(nvmoe_buffer* b, size_t offset, size_t bytes, const void* host) {
+    if (!b) return NVMOE_ERR_INVALID_ARGUMENT;
+    if (!host && bytes) return fail(b->device, NVMOE_ERR_INVALID_ARGUMENT, "host pointer is null");
+    if (offset > b->bytes || bytes > b->bytes - offset)
+        return fail(b->device, NVMOE_ERR_INVALID_ARGUMENT, "range [%zu, %zu) overflows a buffer of %zu bytes", offset,
+                    offset + bytes, b->bytes);
+    return NVMOE_OK;
+}
+
+int nvmoe_buffer_write(nvmoe_buffer* b, size_t offset, const void* src, size_t bytes) {
+    NVMOE_TRY(range_ok(b, offset, bytes, src));
+    if (bytes == 0) return NVMOE_OK;
+    nvmoe_device* d = b->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaMemcpyAsync((char*)b->ptr + offset, src, bytes, cudaMemcpyHostToDevice, d->stream));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));  // the caller may reuse src at once
+    return NVMOE_OK;
+}
+
+int nvmoe_buffer_read(nvmoe_buffer* b, size_t offset, void* dst, size_t bytes) {
+    NVMOE_TRY(range_ok(b, offset, bytes, dst));
+    if (bytes == 0) return NVMOE_OK;
+    nvmoe_device* d = b->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaMemcpyAsync(dst, (const char*)b->ptr + offset, bytes, cudaMemcpyDeviceToHost, d->stream));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
+    return NVMOE_OK;
+}
+
+int nvmoe_buffer_fill(nvmoe_buffer* b, size_t offset, int byte_value, size_t bytes) {
+    NVMOE_TRY(range_ok(b, offset, bytes, b));
+    if (bytes == 0) return NVMOE_OK;
+    nvmoe_device* d = b->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaMemsetAsync((char*)b->ptr + offset, byte_value, bytes, d->stream));
+    return NVMOE_OK;
+}
+
+uint64_t nvmoe_buffer_device_address(const nvmoe_buffer* b) { return b ? (uint64_t)(uintptr_t)b->ptr : 0u; }
+size_t nvmoe_buffer_byte_capacity(const nvmoe_buffer* b) { return b ? b->bytes : 0u; }
+
+int nvmoe_sync(nvmoe_device* d, uint64_t timeout_ns) {
+    if (!d) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaEventRecord(d->sync_event, d->stream));
+    auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
+    for (;;) {
+        cudaError_t q = cudaEventQuery(d->sync_event);
+        if (q == cudaSuccess) return NVMOE_OK;
+        if (q != cudaErrorNotReady) return fail(d, NVMOE_ERR_CUDA, "device failed while waiting: %s", cudaGetErrorString(q));
+        if (std::chrono::steady_clock::now() >= deadline)
+            return fail(d, NVMOE_ERR_TIMEOUT, "device did not finish within %llu ns", (unsigned long long)timeout_ns);
+        std::this_thread::yield();
+    }
+}
+
+// ---- plan ------------------------------------------------------------------------------------
+
+int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_plan** out) {
+    if (!d || !geometry || !out) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    int rc = validate_geometry(*geometry);
+    if (rc != NVMOE_OK) return fail(d, rc, "%s", g_open_error.c_str());
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    nvmoe_plan* p = new (std::nothrow) nvmoe_plan();
+    if (!p) return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "out of host memory");
+    p->device = d;
+    p->g = *geometry;
+    const nvmoe_geometry& g = p->g;
+    p->K = g.routed_k + g.always_count;
+    p->experts = g.routed_experts + g.always_count;
+    p->frame_words = p->K * (g.intermediate_size / 2u) + p->K;
+    const size_t T = g.max_tokens, R = T * p->K, H = g.hidden_size, I = g.intermediate_size;
+    cudaError_t err = cudaSuccess;
+    auto want = [&](DeviceArray& a, size_t bytes) {
+        if (err == cudaSuccess) err = a.ensure(bytes);
+    };
+    want(p->status, 256);
+    want(p->gu_ptrs, sizeof(ExpertPtrs) * p->experts);
+    want(p->down_ptrs, sizeof(ExpertPtrs) * p->experts);
+    for (int i = 0; i < 2; i++) {
+        want(p->grouped[i], sizeof(uint32_t) * R);
+        want(p->offsets[i], sizeof(uint32_t) * (p->experts + 2u));
+    }
+    want(p->block_hist, sizeof(uint32_t) * scratch_blocks(p) * (p->experts + 1u));
+    want(p->bucket_base, sizeof(uint32_t) * (p->experts + 2u));
+    want(p->xq, T * H);
+    want(p->x_scales, sizeof(float) * T * (H / g.act_block));
+    want(p->x_e8m0, sizeof(uint32_t) * T * ((H + 127u) / 128u));
+    want(p->iq, R * I);
+    want(p->i_scales, sizeof(float) * R * (I / g.act_block));
+    want(p->i_e8m0, sizeof(uint32_t) * R * ((I + 127u) / 128u));
+    want(p->tile_list, sizeof(uint32_t) * (R / 16u + p->experts + 1u) + 256u);
+    if (err == cudaSuccess) err = cudaMemsetAsync(p->status.ptr, 0, 256, d->stream);
+    for (int i = 0; i <= kStageCount && err == cudaSuccess; i++) err = cudaEventCreate(&p->ev[i]);
+    for (int i = 0; i < 4 && err == cudaSuccess; i++) err = cudaEventCreate(&p->kernel_ev[i / 2][i % 2]);
+    if (err != cudaSuccess) {
+        int code = err == cudaErrorMemoryAllocation ? NVMOE_ERR_OUT_OF_MEMORY : NVMOE_ERR_CUDA;
+        fail(d, code, "plan scratch allocation failed: %s", cudaGetErrorString(err));
+        nvmoe_plan_destroy(p);
+        return code;
+    }
+    configure_simt_kernels();
+    tc_configure_kernels();
+    *out = p;
+    return NVMOE_OK;
+}
+
+void nvmoe_plan_destroy(nvmoe_plan* p) {
+    if (!p) return;
+    cudaSetDevice(p->device->ordinal);
+    cudaStreamSynchronize(p->device->stream);
+    DeviceArray* all[] = {&p->status, &p->gu_ptrs, &p->down_ptrs, &p->grouped[0], &p->grouped[1], &p->offsets[0],
+                          &p->offsets[1], &p->block_hist, &p->bucket_base, &p->xq, &p->x_scales, &p->x_e8m0, &p->iq,
+                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
+                          &p->controls, &p->hidden_dev, &p->output_dev};
+    for (DeviceArray* a : all) a->release();
+    if (p->pinned_in) cudaFreeHost(p->pinned_in);
+    if (p->pinned_out) cudaFreeHost(p->pinned_out);
+    for (int i = 0; i <= kStageCount; i++)
+        if (p->ev[i]) cudaEventDestroy(p->ev[i]);
+    for (int i = 0; i < 4; i++)
+        if (p->kernel_ev[i / 2][i % 2]) cudaEventDestroy(p->kernel_ev[i / 2][i % 2]);
+    delete p;
+}
+
+int nvmoe_plan_status(nvmoe_plan* p, uint32_t* status_bits) {
+    if (!p || !status_bits) return NVMOE_ERR_INVALID_ARGUMENT;
+    nvmoe_device* d = p->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaMemcpyAsync(status_bits, p->status.ptr, 4, cudaMemcpyDeviceToHost, d->stream));
+    NVMOE_CUDA(d, cudaMemsetAsync(p->status.ptr, 0, 4, d->stream));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
+    return NVMOE_OK;
+}
+
+int nvmoe_plan_set_expert_path(nvmoe_plan* p, int path) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    if (path < 0 || path > 2) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "expert path %d is not 0, 1 or 2", path);
+    if (path == 2 && !tc_shape_supported(p->g))
+        return fail(p->device, NVMOE_ERR_UNSUPPORTED, "the tensor-core path needs a power-of-two activation scale per 32-column block layout this geometry lacks");
+    p->expert_path = path;
+    return NVMOE_OK;
+}
+
+int nvmoe_plan_set_profiling(nvmoe_plan* p, int enabled) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    p->profile_stages = enabled != 0;
+    return NVMOE_OK;
+}
+
+// ---- node-granular operators -----------------------------------------------------------------
+
+int nvmoe_router_linear(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, nvmoe_buffer* logits,
+                        const nvmoe_buffer* router_weights, const nvmoe_buffer* router_bias) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    NVMOE_TRY(check_buffer(p, hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
+    NVMOE_TRY(check_buffer(p, logits, (size_t)T * ((g.routed_experts + 1u) / 2u) * 4u, "logits"));
+    NVMOE_TRY(check_buffer(p, router_weights, (size_t)g.routed_experts * g.hidden_size * 2u, "router weights"));
+    if (router_bias) NVMOE_TRY(check_buffer(p, router_bias, (size_t)g.routed_experts * 2u, "router bias"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_router_linear((const uint16_t*)hidden->ptr, (const uint16_t*)router_weights->ptr,
+                         router_bias ? (const uint16_t*)router_bias->ptr : nullptr, (uint32_t*)logits->ptr, T,
+                         g.hidden_size, g.routed_experts, p->device->stream);
+    p->launches++;
+    return post_launch(p, "router projection");
+}
+
+int nvmoe_route(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* logits, nvmoe_buffer* routes,
+                const nvmoe_buffer* bias, nvmoe_buffer* telemetry) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    NVMOE_TRY(check_buffer(p, logits, (size_t)T * ((g.routed_experts + 1u) / 2u) * 4u, "logits"));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    const bool uses_bias = g.bias_dtype != NVMOE_BIAS_NONE && g.router_kind != NVMOE_ROUTER_TOPK_SOFTMAX;
+    if (uses_bias)
+        NVMOE_TRY(check_buffer(p, bias, (size_t)g.routed_experts * (g.bias_dtype == NVMOE_BIAS_F32 ? 4u : 2u), "selection bias"));
+    if (telemetry) {
+        const size_t r = p->experts;
+        NVMOE_TRY(check_buffer(p, telemetry, (r + r * (r - 1u) / 2u) * 4u, "telemetry"));
+    }
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    RouterLaunch rl{};
+    rl.logits = (const uint32_t*)logits->ptr;
+    rl.bias = uses_bias ? bias->ptr : nullptr;
+    rl.routes = (uint32_t*)routes->ptr;
+    rl.telemetry = telemetry ? (uint32_t*)telemetry->ptr : nullptr;
+    rl.status = p->status.as<uint32_t>();
+    rl.tokens = T;
+    rl.g = g;
+    if (!uses_bias) rl.g.bias_dtype = NVMOE_BIAS_NONE;
+    launch_router(rl, p->device->stream);
+    p->launches++;
+    return post_launch(p, "router");
+}
+
+static int check_slots(nvmoe_plan* p, const nvmoe_buffer* slots) {
+    if (slots && slots->device != p->device) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "slot table belongs to another device");
+    return NVMOE_OK;
+}
+
+int nvmoe_route_compact(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* routes, nvmoe_buffer* intermediates,
+                        const nvmoe_buffer* gate_up_slots, nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, intermediates, (size_t)T * p->frame_words * 4u, "intermediates"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_slots(p, gate_up_slots));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    const nvmoe_geometry& g = p->g;
+    const uint32_t tiles = (g.intermediate_size + g.gate_tile_rows - 1u) / g.gate_tile_rows;
+    launch_route_compact((const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr,
+                         gate_up_slots ? (const uint32_t*)gate_up_slots->ptr : nullptr,
+                         gate_up_slots ? (uint32_t)(gate_up_slots->bytes / 4u) : 0u, 4u, (uint32_t*)control->ptr, T, p->K,
+                         g.intermediate_size, tiles, p->experts, sort_scratch(p), p->device->stream);
+    p->launches += (size_t)T * p->K <= 4096u ? 1u : 3u;
+    return post_launch(p, "route compact");
+}
+
+int nvmoe_route_count(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* routes, const nvmoe_buffer* down_slots,
+                      nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_slots(p, down_slots));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    const nvmoe_geometry& g = p->g;
+    const uint32_t tiles = (g.hidden_size + g.down_tile_rows - 1u) / g.down_tile_rows;
+    launch_route_count((const uint32_t*)routes->ptr, down_slots ? (const uint32_t*)down_slots->ptr : nullptr,
+                       down_slots ? (uint32_t)(down_slots->bytes / 4u) : 0u, 2u, (uint32_t*)control->ptr, T, p->K, tiles,
+                       p->device->stream);
+    p->launches++;
+    return post_launch(p, "route count");
+}
+
+int nvmoe_quantize_fp8(nvmoe_plan* p, uint32_t rows, uint32_t columns, const nvmoe_buffer* input,
+                       nvmoe_buffer* quantized, nvmoe_buffer* scales) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    const uint32_t block = p->g.act_block;
+    if (rows == 0u || columns == 0u || columns % block)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "quantize: %u x %u is not a whole number of %u-column blocks", rows, columns, block);
+    NVMOE_TRY(check_buffer(p, input, (size_t)rows * columns * 2u, "input"));
+    NVMOE_TRY(check_buffer(p, quantized, (size_t)rows * columns, "quantized"));
+    NVMOE_TRY(check_buffer(p, scales, (size_t)rows * (columns / block) * 4u, "scales"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_quantize((const uint16_t*)input->ptr, rows, columns, block, columns, (uint8_t*)quantized->ptr,
+                    (float*)scales->ptr, nullptr, p->device->stream);
+    p->launches++;
+    return post_launch(p, "quantize");
+}
+
+// shared tail of the two gate/up entry points and of down
+static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* act_q, const float* act_scales,
+                       const uint32_t* act_e8m0, const uint32_t* routes, uint32_t* intermediates, uint16_t* outputs,
+                       const nvmoe_buffer* addresses, const nvmoe_buffer* slots, const uint32_t* control,
+                       bool allow_tensor_path) {
+    const nvmoe_geometry& g = p->g;
+    cudaStream_t st = p->device->stream;
+    const int set = gate_up ? 0 : 1;
+    ExpertPtrs* ptrs = (gate_up ? p->gu_ptrs : p->down_ptrs).as<ExpertPtrs>();
+    const uint64_t rows = gate_up ? g.intermediate_size : g.hidden_size;
+    const uint64_t cols = gate_up ? g.hidden_size : g.intermediate_size;
+    launch_resolve_experts((const uint32_t*)addresses->ptr, (uint32_t)(addresses->bytes / 4u), (const uint32_t*)slots->ptr,
+                           (uint32_t)(slots->bytes / 4u), gate_up ? 4u : 2u, p->experts, rows * (cols / 2u),
+                           rows * (cols / 32u), ptrs, st);
+    launch_group_slots(routes, intermediates, control, ptrs, p->experts, T, p->K, g.intermediate_size,
+                       p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->status.as<uint32_t>(),
+                       sort_scratch(p), st);
+    p->launches += 1u + ((size_t)T * p->K <= 4096u ? 1u : 3u);
+    ExpertLaunch el{};
+    el.work = GroupedWork{p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), ptrs, p->experts};
+    el.act_q = act_q;
+    el.act_scales = act_scales;
+    el.act_e8m0 = act_e8m0;
+    el.routes = routes;
+    el.intermediates = intermediates;
+    el.outputs = outputs;
+    el.status = p->status.as<uint32_t>();
+    el.tile_count = p->tile_list.as<uint32_t>();  // first word; the list follows at a 256-byte offset
+    el.tile_list = p->tile_list.as<uint32_t>() + 64;
+    el.tokens = T;
+    el.g = g;
+    const bool tensor = allow_tensor_path && use_tensor_path(p);
+    if (tensor) launch_build_tiles_tc(el, st);
+    if (p->profile_stages) cudaEventRecord(p->kernel_ev[set][0], st);
+    if (tensor) {
+        if (gate_up) {
+            launch_gate_up_tc(el, st);
+        } else {
+            launch_down_tc(el, st);
+        }
+        p->launches++;
+    } else {
+        if (gate_up) {
+            launch_gate_up_simt(el, st);
+        } else {
+            launch_down_simt(el, st);
+        }
+    }
+    if (p->profile_stages) cudaEventRecord(p->kernel_ev[set][1], st);
+    p->report.tensor_path = tensor ? 1u : 0u;
+    p->launches++;
+    return post_launch(p, gate_up ? "gate/up" : "down");
+}
+
+static int check_expert_tables(nvmoe_plan* p, const nvmoe_buffer* addresses, const nvmoe_buffer* slots, uint32_t params) {
+    if (!addresses || !slots) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "address or slot table is null");
+    if (addresses->device != p->device || slots->device != p->device)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "address or slot table belongs to another device");
+    if (addresses->bytes % 32u) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "address table is not a whole number of 32-byte records");
+    if (slots->bytes < (size_t)p->experts * params * 4u)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "slot table holds %zu bytes, %u experts x %u parameters need %zu",
+                    slots->bytes, p->experts, params, (size_t)p->experts * params * 4u);
+    return NVMOE_OK;
+}
+
+int nvmoe_gate_up(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const nvmoe_buffer* routes,
+                  nvmoe_buffer* intermediates, const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
+                  const nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    NVMOE_TRY(check_buffer(p, hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, intermediates, (size_t)T * p->frame_words * 4u, "intermediates"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_expert_tables(p, addresses, slots, 4u));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_quantize((const uint16_t*)hidden->ptr, T, g.hidden_size, g.act_block, g.hidden_size, p->xq.as<uint8_t>(),
+                    p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(), p->device->stream);
+    p->launches++;
+    NVMOE_TRY(post_launch(p, "quantize hidden"));
+    return run_experts(p, true, T, p->xq.as<uint8_t>(), p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(),
+                       (const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr, nullptr, addresses, slots,
+                       (const uint32_t*)control->ptr, true);
+}
+
+int nvmoe_gate_up_prequant(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* quantized_hidden,
+                           const nvmoe_buffer* hidden_scales, const nvmoe_buffer* routes, nvmoe_buffer* intermediates,
+                           const nvmoe_buffer* addresses, const nvmoe_buffer* slots, const nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    NVMOE_TRY(check_buffer(p, quantized_hidden, (size_t)T * g.hidden_size, "quantized hidden"));
+    NVMOE_TRY(check_buffer(p, hidden_scales, (size_t)T * (g.hidden_size / g.act_block) * 4u, "hidden scales"));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, intermediates, (size_t)T * p->frame_words * 4u, "intermediates"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_expert_tables(p, addresses, slots, 4u));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    // the f32 scales of this contract need not be powers of two: the CUDA-core kernels take them as they are
+    return run_experts(p, true, T, (const uint8_t*)quantized_hidden->ptr, (const float*)hidden_scales->ptr, nullptr,
+                       (const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr, nullptr, addresses, slots,
+                       (const uint32_t*)control->ptr, false);
+}
+
+int nvmoe_down(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* intermediates, const nvmoe_buffer* routes,
+               nvmoe_buffer* outputs, const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
+               const nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    NVMOE_TRY(check_buffer(p, intermediates, (size_t)T * p->frame_words * 4u, "intermediates"));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, outputs, (size_t)T * p->K * g.hidden_size * 2u, "expert outputs"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_expert_tables(p, addresses, slots, 2u));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_quantize_frames((const uint32_t*)intermediates->ptr, T, p->K, g.intermediate_size, g.act_block,
+                           p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), p->device->stream);
+    p->launches++;
+    NVMOE_TRY(post_launch(p, "quantize intermediates"));
+    return run_experts(p, false, T, p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(),
+                       (const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr, (uint16_t*)outputs->ptr, addresses,
+                       slots, (const uint32_t*)control->ptr, true);
+}
+
+int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, nvmoe_buffer* output) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    NVMOE_TRY(check_buffer(p, expert_outputs, (size_t)T * p->K * g.hidden_size * 2u, "expert outputs"));
+    NVMOE_TRY(check_buffer(p, output, (size_t)T * g.hidden_size * 2u, "output"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_reduce((const uint16_t*)expert_outputs->ptr, (uint16_t*)output->ptr, T, p->K, g.hidden_size, g.reduce_scale,
+                  p->device->stream);
+    p->launches++;
+    return post_launch(p, "reduce");
+}
+
+// ---- fused layer -------------------------------------------------------------------------------
+
+static int ensure_layer_scratch(nvmoe_plan* p) {
+    const nvmoe_geometry& g = p->g;
+    const size_t T = g.max_tokens;
+    cudaError_t err = cudaSuccess;
+    auto want = [&](DeviceArray& a, size_t bytes) {
+        if (err == cudaSuccess) err = a.ensure(bytes);
+    };
+    const bool fresh_frames = p->frames.ptr == nullptr;
+    want(p->logits, T * ((g.routed_experts + 1u) / 2u) * 4u);
+    want(p->routes, T * p->K * 4u);
+    want(p->frames, T * (size_t)p->frame_words * 4u);
+    want(p->expert_outputs, T * p->K * (size_t)g.hidden_size * 2u);
+    want(p->controls, 64u);
+    if (err == cudaSuccess && fresh_frames) err = cudaMemsetAsync(p->frames.ptr, 0, p->frames.bytes, p->device->stream);
+    if (err != cudaSuccess)
+        return fail(p->device, err == cudaErrorMemoryAllocation ? NVMOE_ERR_OUT_OF_MEMORY : NVMOE_ERR_CUDA,
+                    "layer scratch allocation failed: %s", cudaGetErrorString(err));
+    return NVMOE_OK;
+}
+
+int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
+    if (!p || !a) return NVMOE_ERR_INVALID_ARGUMENT;
+    const uint32_t T = a->batch_width;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    nvmoe_device* d = p->device;
+    if (!a->router_weights && !a->logits)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "the layer needs router weights or precomputed logits");
+    if (a->expert_count && (uint64_t)a->expert_start + a->expert_count > p->experts)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "expert range [%u, %u) exceeds %u resources", a->expert_start,
+                    a->expert_start + a->expert_count, p->experts);
+    NVMOE_TRY(check_buffer(p, a->hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
+    NVMOE_TRY(check_buffer(p, a->output, (size_t)T * g.hidden_size * 2u, "output"));
+    NVMOE_TRY(check_expert_tables(p, a->gate_up_addresses, a->gate_up_slots, 4u));
+    NVMOE_TRY(check_expert_tables(p, a->down_addresses, a->down_slots, 2u));
+    if (a->routes_out) NVMOE_TRY(check_buffer(p, a->routes_out, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_TRY(ensure_layer_scratch(p));
+    cudaStream_t st = d->stream;
+    const uint32_t launches_before = p->launches;
+    const bool prof = p->profile_stages;
+    auto mark = [&](int i) {
+        if (prof || i == 0 || i == kStageCount) cudaEventRecord(p->ev[i], st);
+    };
+
+    nvmoe_buffer logits_view{d, p->logits.ptr, p->logits.bytes};
+    nvmoe_buffer* logits = a->logits ? a->logits : &logits_view;
+    nvmoe_buffer routes_view{d, p->routes.ptr, p->routes.bytes};
+    nvmoe_buffer* routes = a->routes_out ? a->routes_out : &routes_view;
+    nvmoe_buffer frames{d, p->frames.ptr, p->frames.bytes};
+    nvmoe_buffer outs{d, p->expert_outputs.ptr, p->expert_outputs.bytes};
+    nvmoe_buffer gate_control{d, p->controls.ptr, 28u};
+    nvmoe_buffer down_control{d, (char*)p->controls.ptr + 32u, 28u};
+
+    mark(kStageLinear);
+    if (a->router_weights) NVMOE_TRY(nvmoe_router_linear(p, T, a->hidden, logits, a->router_weights, a->router_bias));
+    mark(kStageRoute);
+    NVMOE_TRY(nvmoe_route(p, T, logits, routes, a->bias, a->telemetry));
+    mark(kStageSchedule);
+    write_control_kernel<<<1, 32, 0, st>>>((uint32_t*)gate_control.ptr, T, a->expert_start, a->expert_count);
+    write_control_kernel<<<1, 32, 0, st>>>((uint32_t*)down_control.ptr, T, a->expert_start, a->expert_count);
+    p->launches += 2;
+    NVMOE_TRY(nvmoe_route_compact(p, T, routes, &frames, a->gate_up_slots, &gate_control));
+    NVMOE_TRY(nvmoe_route_count(p, T, routes, a->down_slots, &down_control));
+    mark(kStageQuantX);
+    // nvmoe_gate_up quantises then runs the experts; the stage marks split the two for the report
+    launch_quantize((const uint16_t*)a->hidden->ptr, T, g.hidden_size, g.act_block, g.hidden_size, p->xq.as<uint8_t>(),
+                    p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(), st);
+    p->launches++;
+    NVMOE_TRY(post_launch(p, "quantize hidden"));
+    mark(kStageGateUp);
+    NVMOE_TRY(run_experts(p, true, T, p->xq.as<uint8_t>(), p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(),
+                          (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, nullptr, a->gate_up_addresses,
+                          a->gate_up_slots, (const uint32_t*)gate_control.ptr, true));
+    mark(kStageQuantI);
+    launch_quantize_frames((const uint32_t*)frames.ptr, T, p->K, g.intermediate_size, g.act_block, p->iq.as<uint8_t>(),
+                           p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), st);
+    p->launches++;
+    NVMOE_TRY(post_launch(p, "quantize intermediates"));
+    mark(kStageDown);
+    // routes that are skipped (owned by another device, expert not resident) leave their rows
+    // untouched: start every row at zero so that the combine adds nothing for them
+    cudaMemsetAsync(outs.ptr, 0, (size_t)T * p->K * g.hidden_size * 2u, st);
+    NVMOE_TRY(run_experts(p, false, T, p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(),
+                          (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, (uint16_t*)outs.ptr, a->down_addresses,
+                          a->down_slots, (const uint32_t*)down_control.ptr, true));
+    mark(kStageReduce);
+    NVMOE_TRY(nvmoe_reduce(p, T, &outs, a->output));
+    mark(kStageCount);
+    p->events_valid = true;
+    p->report.batch_width = T;
+    p->report.routes = T * p->K;
+    p->report.kernel_launches = p->launches - launches_before;
+    return NVMOE_OK;
+}
+
+int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hidden_host, void* output_host) {
+    if (!p || !args || !hidden_host || !output_host) return NVMOE_ERR_INVALID_ARGUMENT;
+    const uint32_t T = args->batch_width;
+    NVMOE_TRY(check_tokens(p, T));
+    nvmoe_device* d = p->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    const size_t bytes = (size_t)T * p->g.hidden_size * 2u;
+    const size_t cap = (size_t)p->g.max_tokens * p->g.hidden_size * 2u;
+    if (!p->pinned_in) {
+        NVMOE_CUDA(d, cudaMallocHost(&p->pinned_in, cap));
+        NVMOE_CUDA(d, cudaMallocHost(&p->pinned_out, cap));
+        p->pinned_bytes = cap;
+    }
+    cudaError_t err = p->hidden_dev.ensure(cap);
+    if (err == cudaSuccess) err = p->output_dev.ensure(cap);
+    if (err != cudaSuccess) return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "staging allocation failed: %s", cudaGetErrorString(err));
+    std::memcpy(p->pinned_in, hidden_host, bytes);
+    NVMOE_CUDA(d, cudaMemcpyAsync(p->hidden_dev.ptr, p->pinned_in, bytes, cudaMemcpyHostToDevice, d->stream));
+    nvmoe_buffer hidden{d, p->hidden_dev.ptr, cap};
+    nvmoe_buffer output{d, p->output_dev.ptr, cap};
+    nvmoe_layer_args local = *args;
+    local.hidden = &hidden;
+    local.output = &output;
+    NVMOE_TRY(nvmoe_layer(p, &local));
+    NVMOE_CUDA(d, cudaMemcpyAsync(p->pinned_out, p->output_dev.ptr, bytes, cudaMemcpyDeviceToHost, d->stream));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
+    std::memcpy(output_host, p->pinned_out, bytes);
+    return NVMOE_OK;
+}
+
+int nvmoe_plan_last_report(nvmoe_plan* p, nvmoe_work_report* report) {
+    if (!p || !report) return NVMOE_ERR_INVALID_ARGUMENT;
+    nvmoe_device* d = p->device;
+    if (!p->events_valid) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "no layer call has run on this plan");
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
+    NVMOE_CUDA(d, cudaEventElapsedTime(&p->report.total_ms, p->ev[0], p->ev[kStageCount]));
+    for (int i = 0; i < kStageCount; i++) {
+        p->report.stage_ms[i] = 0.0f;
+        if (p->profile_stages) cudaEventElapsedTime(&p->report.stage_ms[i], p->ev[i], p->ev[i + 1]);
+    }
+    p->report.gate_up_kernel_ms = p->report.down_kernel_ms = 0.0f;
+    if (p->profile_stages) {
+        cudaEventElapsedTime(&p->report.gate_up_kernel_ms, p->kernel_ev[0][0], p->kernel_ev[0][1]);
+        cudaEventElapsedTime(&p->report.down_kernel_ms, p->kernel_ev[1][0], p->kernel_ev[1][1]);
+    }
+    std::vector<uint32_t> offsets(p->experts + 1u);
+    NVMOE_CUDA(d, cudaMemcpy(offsets.data(), p->offsets[0].ptr, offsets.size() * 4u, cudaMemcpyDeviceToHost));
+    uint32_t distinct = 0;
+    for (uint32_t e = 0; e < p->experts; e++) distinct += offsets[e + 1u] > offsets[e];
+    p->report.distinct_experts = distinct;
+    const uint64_t per_expert = 3ull * p->g.hidden_size * p->g.intermediate_size * 17ull / 32ull;
+    p->report.weight_bytes_touched = per_expert * distinct;
+    *report = p->report;
+    return NVMOE_OK;
+}
+
+}  // extern "C"

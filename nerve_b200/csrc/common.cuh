@@ -1,0 +1,135 @@
+// Shared declarations of the CUDA MoE backend: launch parameter blocks, the resolved expert
+// pointer table, fail-closed status bits and small device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nerve_cuda_moe.h"
+#include "../../include/nvmoe_math.h"
+
+namespace nvmoe {
+
+constexpr uint32_t kUnboundSlot = 0xffffffffu;
+constexpr uint32_t kRecordWords = 8u;
+constexpr uint32_t kMaxTopK = 64u;       // routed_k + always_count
+constexpr uint32_t kMaxExperts = 4096u;  // ids travel in the low 16 bits of a route word
+constexpr uint32_t kSortChunk = 256u;    // routes per block in the multi-block counting sort
+
+// Weight pointers of one expert after the address/slot tables were validated
+// (address_record_is_resident + dynamic_expert_is_valid of
+// runtime-rs/shaders/independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:120-228).
+// A null w pointer means "not resident": every route to that expert is skipped.
+struct ExpertPtrs {
+    const uint8_t* w[2];  // gate/up: w1, w3;  down: w2, unused
+    const uint8_t* s[2];  // matching E8M0 scale rows
+};
+
+// Everything a grouped expert kernel needs to find its work, produced by group_slots().
+struct GroupedWork {
+    const uint32_t* grouped_routes;   // route indices (t*K + r) sorted by expert, stable
+    const uint32_t* expert_offsets;   // [num_experts + 1] into grouped_routes
+    const ExpertPtrs* experts;        // [num_experts]
+    uint32_t num_experts;
+};
+
+__device__ __forceinline__ void raise_status(uint32_t* status, uint32_t bit) {
+    if (status) atomicOr(status, bit);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return nvmoe_f32_to_bf16(lo) | (nvmoe_f32_to_bf16(hi) << 16);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// xor-butterfly sum: every lane ends with the same bits; the order is part of the numeric contract
+__device__ __forceinline__ float warp_butterfly_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---- kernels launched by capi.cu (defined in the .cu file named in the comment) ------------
+
+struct RouterLaunch {  // router.cu
+    const uint32_t* logits;
+    const void* bias;
+    uint32_t* routes;
+    uint32_t* telemetry;
+    uint32_t* status;
+    uint32_t tokens;
+    nvmoe_geometry g;
+};
+void launch_router(const RouterLaunch& p, cudaStream_t stream);
+void launch_router_linear(const uint16_t* x, const uint16_t* w, const uint16_t* bias, uint32_t* logits,
+                          uint32_t tokens, uint32_t hidden, uint32_t outputs, cudaStream_t stream);
+
+struct SortScratch {  // schedule.cu: scratch of the counting sort, sized for max_tokens
+    uint32_t* block_hist;      // [blocks][buckets]
+    uint32_t* bucket_base;     // [buckets + 1]
+    uint32_t blocks_capacity;
+    uint32_t buckets_capacity;
+};
+// moe_route_compact_batch1 / moe_route_count_batch1
+void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const uint32_t* slots,
+                          uint32_t slot_words, uint32_t params_per_resource, uint32_t* control,
+                          uint32_t max_tokens, uint32_t K, uint32_t intermediate_size,
+                          uint32_t tiles_per_route, uint32_t num_experts, const SortScratch& scratch,
+                          cudaStream_t stream);
+void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t slot_words,
+                        uint32_t params_per_resource, uint32_t* control, uint32_t max_tokens, uint32_t K,
+                        uint32_t tiles_per_route, cudaStream_t stream);
+// validates the address/slot tables of every expert once per call
+void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
+                            uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
+                            uint64_t weight_bytes, uint64_t scale_bytes, ExpertPtrs* out,
+                            cudaStream_t stream);
+// groups the compact slots the expert shaders would visit by expert (stable), skipping what the
+// shaders skip; writes grouped_routes and expert_offsets
+void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,
+                        const ExpertPtrs* experts, uint32_t num_experts, uint32_t max_tokens, uint32_t K,
+                        uint32_t intermediate_size, uint32_t* grouped_routes, uint32_t* expert_offsets,
+                        uint32_t* status, const SortScratch& scratch, cudaStream_t stream);
+
+// quantize.cu: bf16 rows -> E4M3 bytes + per-block power-of-two scales.
+// scales_f32 ([rows][cols/block]) and scales_e8m0 ([rows][ceil(cols/128)] words, four E8M0 bytes of
+// consecutive 32-column blocks per word) are both optional.
+void launch_quantize(const uint16_t* input, uint32_t rows, uint32_t cols, uint32_t block,
+                     size_t input_row_stride, uint8_t* q, float* scales_f32, uint32_t* scales_e8m0,
+                     cudaStream_t stream);
+// the same for the K rows of every intermediates frame (skips the schedule words)
+void launch_quantize_frames(const uint32_t* intermediates, uint32_t tokens, uint32_t K,
+                            uint32_t intermediate_size, uint32_t block, uint8_t* q, float* scales_f32,
+                            uint32_t* scales_e8m0, cudaStream_t stream);
+// f32 scales -> packed E8M0 words, for prequantised inputs; sets *not_pow2 if a scale is not a power of two
+void launch_scales_to_e8m0(const float* scales, uint32_t rows, uint32_t cols, uint32_t block,
+                           uint32_t* scales_e8m0, uint32_t* status, cudaStream_t stream);
+
+struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
+    GroupedWork work;
+    const uint8_t* act_q;        // [rows][K_dim] E4M3; row = token (gate/up) or route index (down)
+    const float* act_scales;     // [rows][K_dim/act_block] f32
+    const uint32_t* act_e8m0;    // [rows][ceil(K_dim/128)] packed E8M0 (tensor path)
+    const uint32_t* routes;      // route words (down: weights)
+    uint32_t* intermediates;     // gate/up output frames
+    uint16_t* outputs;           // down output [T][K][H]
+    uint32_t* status;
+    uint32_t* tile_list;         // tensor path scratch: routes / 16 + experts + 1 words
+    uint32_t* tile_count;        // tensor path scratch: one word
+    uint32_t tokens;             // upper bound (max over what control may hold)
+    nvmoe_geometry g;
+};
+void configure_simt_kernels();
+void launch_gate_up_simt(const ExpertLaunch& p, cudaStream_t stream);
+void launch_down_simt(const ExpertLaunch& p, cudaStream_t stream);
+
+// reduce.cu: moe_reduce_batch1_bf16
+void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t tokens, uint32_t K,
+                   uint32_t hidden, float routed_scale, cudaStream_t stream);
+
+}  // namespace nvmoe

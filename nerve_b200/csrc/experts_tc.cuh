@@ -1,0 +1,19 @@
+// Interface of the tcgen05 grouped expert kernels (experts_tc.cu).
+#pragma once
+#include "common.cuh"
+
+namespace nvmoe {
+
+// Shapes the tensor-core path takes: columns in whole 32-blocks with a power-of-two activation
+// scale per block (always true for the plan's own quantiser).
+bool tc_shape_supported(const nvmoe_geometry& g);
+// Whether "automatic" picks the tensor-core path.
+bool tc_enabled_by_default();
+void tc_configure_kernels();
+// token tile size for this call, and the (expert, token tile) list the kernels walk
+uint32_t tc_token_tile(const ExpertLaunch& p);
+void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream);
+void launch_gate_up_tc(const ExpertLaunch& p, cudaStream_t stream);
+void launch_down_tc(const ExpertLaunch& p, cudaStream_t stream);
+
+}  // namespace nvmoe

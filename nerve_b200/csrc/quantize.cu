@@ -1,0 +1,127 @@
+// Activation quantisation bf16 -> FP8 E4M3 with one power-of-two scale per block of columns.
+//
+//   quantize_batch_fp8_e4m3.comp.template:47-71 (shared pre-quantisation, power-of-two scale)
+//   independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:357-383 (quantize_hidden)
+//   independent_sparse_moe_down_batch1_mxfp4.comp.template:307-353 (quantize_intermediate)
+//
+// scale = 2^ceil(log2(max(|x|, 1e-4) / 448)), q = E4M3(x / scale) with round-to-nearest-even.
+// The reference block is 128 columns; any multiple of 32 that divides the row works here.  Besides
+// the f32 scales of the reference contract the kernel can emit the same scales as E8M0 bytes, one
+// per 32 columns, four to a word — the form a block-scaled MMA reads.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace nvmoe {
+namespace {
+
+__device__ __forceinline__ uint32_t to_e4m3x4(float a, float b, float c, float d) {
+    // cvt.rn.satfinite.e4m3x2.f32: round-to-nearest-even, saturating (|x/scale| <= 448 by construction)
+    uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+// One warp per (row, block of `block` columns); a lane owns 4 columns at a time.
+// row_of(r) gives the bf16 row pointer, so the same body serves plain matrices and MoE frames.
+template <class RowFn>
+__device__ void quantize_body(RowFn row_of, uint32_t rows, uint32_t cols, uint32_t block, uint8_t* q,
+                              float* scales_f32, uint32_t* scales_e8m0) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t blocks_per_row = cols / block;
+    const uint32_t words128 = (cols + 127u) / 128u;
+    const uint64_t total = (uint64_t)rows * blocks_per_row;
+    for (uint64_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < total; item += warps_per_grid) {
+        const uint32_t r = (uint32_t)(item / blocks_per_row), b = (uint32_t)(item % blocks_per_row);
+        const uint2* in = reinterpret_cast<const uint2*>(row_of(r) + (size_t)b * block);
+        float m = 0.0f;
+        for (uint32_t c4 = lane; c4 < block / 4u; c4 += 32u) {
+            uint2 v = in[c4];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(nvmoe_bf16_to_f32(v.x)), fabsf(nvmoe_bf16_to_f32(v.x >> 16))),
+                               fmaxf(fabsf(nvmoe_bf16_to_f32(v.y)), fabsf(nvmoe_bf16_to_f32(v.y >> 16)))));
+        }
+        m = warp_max(m);
+        const float scale = nvmoe_rounded_fp8_scale(m);
+        const float inv = __fdiv_rn(1.0f, scale);  // exact: the scale is a power of two
+        uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)r * cols + (size_t)b * block);
+        for (uint32_t c4 = lane; c4 < block / 4u; c4 += 32u) {
+            uint2 v = in[c4];
+            out[c4] = to_e4m3x4(nvmoe_bf16_to_f32(v.x) * inv, nvmoe_bf16_to_f32(v.x >> 16) * inv,
+                                nvmoe_bf16_to_f32(v.y) * inv, nvmoe_bf16_to_f32(v.y >> 16) * inv);
+        }
+        if (scales_f32 && lane == 0u) scales_f32[(size_t)r * blocks_per_row + b] = scale;
+        if (scales_e8m0) {
+            // one byte per 32 columns; this block covers block/32 of them
+            uint8_t* bytes = reinterpret_cast<uint8_t*>(scales_e8m0 + (size_t)r * words128);
+            const uint32_t e8 = nvmoe_f32_bits(scale) >> 23;
+            for (uint32_t j = lane; j < block / 32u; j += 32u) bytes[b * (block / 32u) + j] = (uint8_t)e8;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) quantize_kernel(const uint16_t* input, uint32_t rows, uint32_t cols,
+                                                      uint32_t block, size_t row_stride, uint8_t* q,
+                                                      float* scales_f32, uint32_t* scales_e8m0) {
+    quantize_body([&](uint32_t r) { return input + (size_t)r * row_stride; }, rows, cols, block, q, scales_f32,
+                  scales_e8m0);
+}
+
+__global__ void __launch_bounds__(256) quantize_frames_kernel(const uint32_t* intermediates, uint32_t tokens,
+                                                             uint32_t K, uint32_t I, uint32_t block, uint8_t* q,
+                                                             float* scales_f32, uint32_t* scales_e8m0) {
+    const uint32_t frame_words = K * (I / 2u) + K;
+    quantize_body(
+        [&](uint32_t r) {
+            return reinterpret_cast<const uint16_t*>(intermediates + (size_t)(r / K) * frame_words) + (size_t)(r % K) * I;
+        },
+        tokens * K, I, block, q, scales_f32, scales_e8m0);
+}
+
+__global__ void __launch_bounds__(256) scales_to_e8m0_kernel(const float* scales, uint32_t rows, uint32_t cols,
+                                                            uint32_t block, uint32_t* scales_e8m0, uint32_t* status) {
+    const uint32_t blocks_per_row = cols / block;
+    const uint32_t words128 = (cols + 127u) / 128u;
+    const uint64_t total = (uint64_t)rows * blocks_per_row;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t r = (uint32_t)(i / blocks_per_row), b = (uint32_t)(i % blocks_per_row);
+        const uint32_t bits = nvmoe_f32_bits(scales[i]);
+        // a block-scaled MMA can only take power-of-two scales with a biased exponent in 1..254
+        if ((bits & 0x807fffffu) != 0u || (bits >> 23) == 0u || (bits >> 23) == 255u) raise_status(status, 1u);
+        uint8_t* bytes = reinterpret_cast<uint8_t*>(scales_e8m0 + (size_t)r * words128);
+        for (uint32_t j = 0; j < block / 32u; j++) bytes[b * (block / 32u) + j] = (uint8_t)(bits >> 23);
+    }
+}
+
+uint32_t grid_for(uint64_t warps) {
+    uint64_t blocks = (warps + 7u) / 8u;
+    return (uint32_t)(blocks < 1u ? 1u : (blocks > 148u * 16u ? 148u * 16u : blocks));
+}
+
+}  // namespace
+
+void launch_quantize(const uint16_t* input, uint32_t rows, uint32_t cols, uint32_t block, size_t input_row_stride,
+                     uint8_t* q, float* scales_f32, uint32_t* scales_e8m0, cudaStream_t stream) {
+    if (rows == 0u) return;
+    quantize_kernel<<<grid_for((uint64_t)rows * (cols / block)), 256, 0, stream>>>(
+        input, rows, cols, block, input_row_stride, q, scales_f32, scales_e8m0);
+}
+
+void launch_quantize_frames(const uint32_t* intermediates, uint32_t tokens, uint32_t K, uint32_t intermediate_size,
+                            uint32_t block, uint8_t* q, float* scales_f32, uint32_t* scales_e8m0,
+                            cudaStream_t stream) {
+    if (tokens == 0u) return;
+    quantize_frames_kernel<<<grid_for((uint64_t)tokens * K * (intermediate_size / block)), 256, 0, stream>>>(
+        intermediates, tokens, K, intermediate_size, block, q, scales_f32, scales_e8m0);
+}
+
+void launch_scales_to_e8m0(const float* scales, uint32_t rows, uint32_t cols, uint32_t block,
+                           uint32_t* scales_e8m0, uint32_t* status, cudaStream_t stream) {
+    if (rows == 0u) return;
+    uint64_t total = (uint64_t)rows * (cols / block);
+    uint32_t blocks = (uint32_t)((total + 255u) / 256u);
+    scales_to_e8m0_kernel<<<blocks > 2368u ? 2368u : blocks, 256, 0, stream>>>(scales, rows, cols, block,
+                                                                               scales_e8m0, status);
+}
+
+}  // namespace nvmoe

@@ -1,0 +1,44 @@
+// Weighted combine of the per-route expert outputs.
+//
+//   runtime-rs/shaders/moe_reduce_batch1_bf16.comp.template:29-55
+//
+// The route weight is already inside each per-route row (the down stage applied it), so the
+// combine is a sum over the K routes of a token in route order — ascending expert id — with a
+// bf16 rounding after every add, then one multiply by ROUTED_SCALE and a final rounding.  That
+// order and those roundings are the reference's and are reproduced exactly.
+#include "common.cuh"
+
+namespace nvmoe {
+namespace {
+
+__global__ void __launch_bounds__(256) reduce_kernel(const uint32_t* __restrict__ expert_outputs,
+                                                    uint32_t* __restrict__ output, uint32_t tokens, uint32_t K,
+                                                    uint32_t hidden_words, float routed_scale) {
+    const uint64_t total = (uint64_t)tokens * hidden_words;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / hidden_words), word = (uint32_t)(i % hidden_words);
+        const uint32_t* in = expert_outputs + (size_t)t * K * hidden_words + word;
+        float lo = 0.0f, hi = 0.0f;
+        for (uint32_t r = 0; r < K; r++) {
+            const uint32_t c = in[(size_t)r * hidden_words];
+            lo = nvmoe_round_bf16(__fadd_rn(lo, nvmoe_bf16_to_f32(c)));
+            hi = nvmoe_round_bf16(__fadd_rn(hi, nvmoe_bf16_to_f32(c >> 16)));
+        }
+        output[i] = pack_bf16x2(__fmul_rn(lo, routed_scale), __fmul_rn(hi, routed_scale));
+    }
+}
+
+}  // namespace
+
+void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t tokens, uint32_t K, uint32_t hidden,
+                   float routed_scale, cudaStream_t stream) {
+    if (tokens == 0u) return;
+    const uint64_t total = (uint64_t)tokens * (hidden / 2u);
+    uint64_t blocks = (total + 255u) / 256u;
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    reduce_kernel<<<(uint32_t)blocks, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(expert_outputs),
+                                                        reinterpret_cast<uint32_t*>(output), tokens, K, hidden / 2u,
+                                                        routed_scale);
+}
+
+}  // namespace nvmoe

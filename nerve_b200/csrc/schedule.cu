@@ -1,0 +1,489 @@
+// Route scheduling: the reference's compact/count stages and the expert grouping the grouped
+// expert kernels consume.
+//
+//   route_compact   runtime-rs/shaders/moe_route_compact_batch1.comp.template:26-105
+//   route_count     runtime-rs/shaders/moe_route_count_batch1.comp.template:21-58
+//
+// The reference ranks every (token, route) against every other one — quadratic in T*K.  The
+// rank it computes, #{c : expert(c) < expert(s) or (expert(c) == expert(s) and c < s)}, is the
+// position of s in a STABLE sort by expert id, so the same list comes out of a counting sort:
+// per-block histograms, an exclusive scan over (expert, block), and a scatter in which equal
+// experts keep source order (warp match + popcount of lower lanes, warps taken in order).
+// Route ids at or above the expert count cannot be produced by the routers here; they are placed
+// after every valid id in source order (the reference would order them by id).
+#include "common.cuh"
+
+namespace nvmoe {
+namespace {
+
+// ---- generic stable counting sort over `count` keys ------------------------------------------
+// KeyFn(i) -> bucket in [0, buckets) or kUnboundSlot to drop item i.  EmitFn(rank, i) stores it.
+
+template <class KeyFn>
+__device__ void block_histogram(uint32_t begin, uint32_t end, uint32_t buckets, uint32_t* hist, KeyFn key) {
+    for (uint32_t b = threadIdx.x; b < buckets; b += blockDim.x) hist[b] = 0u;
+    __syncthreads();
+    for (uint32_t i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        uint32_t kb = key(i);
+        if (kb != kUnboundSlot) atomicAdd(hist + kb, 1u);
+    }
+    __syncthreads();
+}
+
+// Stable scatter of items [begin, end) given running[b] = rank of the next item of bucket b.
+// blockDim.x must be a multiple of 32; warps take turns so that source order is kept.
+template <class KeyFn, class EmitFn>
+__device__ void block_stable_scatter(uint32_t begin, uint32_t end, uint32_t* running, KeyFn key, EmitFn emit) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (uint32_t base = begin; base < end; base += blockDim.x) {
+        uint32_t i = base + threadIdx.x;
+        uint32_t kb = i < end ? key(i) : kUnboundSlot;
+        for (uint32_t w = 0; w < warps; w++) {
+            if (w == warp) {
+                uint32_t peers = __match_any_sync(0xffffffffu, kb);
+                if (kb != kUnboundSlot) {
+                    uint32_t before = __popc(peers & ((1u << lane) - 1u));
+                    uint32_t leader = __ffs(peers) - 1u;
+                    uint32_t start = 0u;
+                    if (lane == leader) {
+                        start = running[kb];
+                        running[kb] = start + __popc(peers);
+                    }
+                    start = __shfl_sync(peers, start, leader);
+                    emit(start + before, i);
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// One block does the whole sort (small inputs: one launch instead of three).
+template <class KeyFn, class EmitFn, class DoneFn>
+__device__ void sort_single_block(uint32_t count, uint32_t buckets, uint32_t* smem_hist, KeyFn key,
+                                  EmitFn emit, DoneFn done) {
+    block_histogram(0u, count, buckets, smem_hist, key);
+    // exclusive scan over buckets by one warp (buckets <= 4097)
+    if (threadIdx.x < 32u) {
+        uint32_t carry = 0u;
+        for (uint32_t b0 = 0; b0 < buckets; b0 += 32u) {
+            uint32_t b = b0 + threadIdx.x;
+            uint32_t v = b < buckets ? smem_hist[b] : 0u;
+            uint32_t incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)threadIdx.x >= o) incl += n;
+            }
+            if (b < buckets) smem_hist[b] = carry + incl - v;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (threadIdx.x == 0u) smem_hist[buckets] = carry;
+    }
+    __syncthreads();
+    done(smem_hist);  // bucket bases (exclusive) with the total at [buckets]
+    __syncthreads();
+    block_stable_scatter(0u, count, smem_hist, key, emit);
+}
+
+// ---- keys ----------------------------------------------------------------------------------
+
+struct RouteKey {  // compact: rank all T*K routes by expert id
+    const uint32_t* routes;
+    uint32_t num_experts;
+    __device__ uint32_t operator()(uint32_t i) const {
+        uint32_t e = routes[i] & 0xffffu;
+        return e < num_experts ? e : num_experts;
+    }
+};
+
+__device__ __forceinline__ bool resource_is_local(const uint32_t* slots, uint32_t slot_words,
+                                                  uint32_t params, uint32_t expert) {
+    if (!slots) return true;
+    uint64_t index = (uint64_t)expert * params;
+    if (index >= slot_words) return false;
+    return slots[index] != kUnboundSlot;
+}
+
+struct OwnedKey {  // partitioned compact: keep owned routes, in source order (one bucket)
+    const uint32_t* routes;
+    const uint32_t* slots;
+    uint32_t slot_words, params, start, end;
+    __device__ uint32_t operator()(uint32_t i) const {
+        uint32_t e = routes[i] & 0xffffu;
+        if (e < start || e >= end || !resource_is_local(slots, slot_words, params, e)) return kUnboundSlot;
+        return 0u;
+    }
+};
+
+struct ScheduleEmit {  // writes the compact list into the schedule words of the frames
+    uint32_t* intermediates;
+    uint32_t K, frame_words, data_words;
+    __device__ void operator()(uint32_t rank, uint32_t i) const {
+        intermediates[(size_t)(rank / K) * frame_words + data_words + rank % K] = i;
+    }
+};
+
+// the slot the expert shaders read for compact position c, or kUnboundSlot when they return early
+struct SlotKey {
+    const uint32_t* routes;
+    const uint32_t* intermediates;
+    const ExpertPtrs* experts;
+    uint32_t* status;
+    uint32_t num_experts, K, frame_words, data_words, capacity;
+    __device__ uint32_t route_index(uint32_t c) const {
+        return intermediates[(size_t)(c / K) * frame_words + data_words + c % K];
+    }
+    __device__ uint32_t operator()(uint32_t c) const {
+        uint32_t ri = route_index(c);
+        if (ri >= capacity) {
+            raise_status(status, NVMOE_STATUS_ROUTE_OUT_OF_RANGE);
+            return kUnboundSlot;
+        }
+        uint32_t e = routes[ri] & 0xffffu;
+        if (e >= num_experts) {
+            raise_status(status, NVMOE_STATUS_ROUTE_OUT_OF_RANGE);
+            return kUnboundSlot;
+        }
+        if (experts[e].w[0] == nullptr) {
+            raise_status(status, NVMOE_STATUS_EXPERT_NOT_RESIDENT);
+            return kUnboundSlot;
+        }
+        return e;
+    }
+};
+
+struct GroupEmit {
+    const SlotKey key;
+    uint32_t* grouped;
+    __device__ void operator()(uint32_t rank, uint32_t c) const { grouped[rank] = key.route_index(c); }
+};
+
+// ---- kernels ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t min_u32(uint32_t a, uint32_t b) { return a < b ? a : b; }
+
+// Single-block compact (T*K small).  `control` is read for batch_width / expert range and the
+// owned count and indirect-dispatch words are written back exactly as the shader does.
+__global__ void __launch_bounds__(1024) compact_small_kernel(const uint32_t* routes, uint32_t* intermediates,
+                                                            const uint32_t* slots, uint32_t slot_words,
+                                                            uint32_t params, uint32_t* control,
+                                                            uint32_t max_tokens, uint32_t K, uint32_t I,
+                                                            uint32_t tiles_per_route, uint32_t num_experts) {
+    extern __shared__ uint32_t hist[];
+    const uint32_t T = min_u32(control[0], max_tokens);
+    const uint32_t count = T * K;
+    const uint32_t data_words = K * (I / 2u);
+    ScheduleEmit emit{intermediates, K, data_words + K, data_words};
+    if (control[2] != 0u) {
+        OwnedKey key{routes, slots, slot_words, params, control[1], control[1] + control[2]};
+        sort_single_block(count, 1u, hist, key, emit, [&](const uint32_t* base) {
+            if (threadIdx.x == 0u) {
+                control[3] = base[1];
+                control[4] = base[1] * tiles_per_route;
+                control[5] = 1u;
+                control[6] = 1u;
+            }
+        });
+    } else {
+        RouteKey key{routes, num_experts};
+        sort_single_block(count, num_experts + 1u, hist, key, emit, [&](const uint32_t*) {
+            if (threadIdx.x == 0u) {
+                control[3] = count;
+                control[4] = K * tiles_per_route;
+                control[5] = T;
+                control[6] = 1u;
+            }
+        });
+    }
+}
+
+// Multi-block sort, phase 1: per-block histograms.
+template <class KeyFn>
+__device__ void phase_hist(uint32_t count, uint32_t buckets, uint32_t* block_hist, KeyFn key) {
+    extern __shared__ uint32_t hist[];
+    uint32_t begin = blockIdx.x * kSortChunk;
+    if (begin >= count) {
+        for (uint32_t b = threadIdx.x; b < buckets; b += blockDim.x) block_hist[(size_t)blockIdx.x * buckets + b] = 0u;
+        return;
+    }
+    uint32_t end = min_u32(begin + kSortChunk, count);
+    block_histogram(begin, end, buckets, hist, key);
+    for (uint32_t b = threadIdx.x; b < buckets; b += blockDim.x) block_hist[(size_t)blockIdx.x * buckets + b] = hist[b];
+}
+
+// phase 2 (one block): block_hist[blk][b] <- rank of the first item of bucket b in block blk;
+// bucket_base[b] <- exclusive scan of bucket totals, total at [buckets].
+__global__ void __launch_bounds__(1024) phase_scan_kernel(uint32_t* block_hist, uint32_t* bucket_base,
+                                                         uint32_t blocks, uint32_t buckets) {
+    extern __shared__ uint32_t totals[];
+    for (uint32_t b = threadIdx.x; b < buckets; b += blockDim.x) {
+        uint32_t run = 0u;
+        for (uint32_t blk = 0; blk < blocks; blk++) {
+            uint32_t v = block_hist[(size_t)blk * buckets + b];
+            block_hist[(size_t)blk * buckets + b] = run;
+            run += v;
+        }
+        totals[b] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32u) {
+        uint32_t carry = 0u;
+        for (uint32_t b0 = 0; b0 < buckets; b0 += 32u) {
+            uint32_t b = b0 + threadIdx.x;
+            uint32_t v = b < buckets ? totals[b] : 0u;
+            uint32_t incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)threadIdx.x >= o) incl += n;
+            }
+            if (b < buckets) bucket_base[b] = carry + incl - v;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (threadIdx.x == 0u) bucket_base[buckets] = carry;
+    }
+}
+
+template <class KeyFn, class EmitFn>
+__device__ void phase_scatter(uint32_t count, uint32_t buckets, const uint32_t* block_hist,
+                              const uint32_t* bucket_base, KeyFn key, EmitFn emit) {
+    extern __shared__ uint32_t running[];
+    uint32_t begin = blockIdx.x * kSortChunk;
+    if (begin >= count) return;
+    uint32_t end = min_u32(begin + kSortChunk, count);
+    for (uint32_t b = threadIdx.x; b < buckets; b += blockDim.x)
+        running[b] = bucket_base[b] + block_hist[(size_t)blockIdx.x * buckets + b];
+    __syncthreads();
+    block_stable_scatter(begin, end, running, key, emit);
+}
+
+__global__ void __launch_bounds__(256) compact_hist_kernel(const uint32_t* routes, const uint32_t* slots,
+                                                          uint32_t slot_words, uint32_t params,
+                                                          const uint32_t* control, uint32_t max_tokens,
+                                                          uint32_t K, uint32_t num_experts, uint32_t* block_hist) {
+    const uint32_t count = min_u32(control[0], max_tokens) * K;
+    if (control[2] != 0u) {
+        OwnedKey key{routes, slots, slot_words, params, control[1], control[1] + control[2]};
+        phase_hist(count, num_experts + 1u, block_hist, key);  // one bucket used, same stride
+    } else {
+        RouteKey key{routes, num_experts};
+        phase_hist(count, num_experts + 1u, block_hist, key);
+    }
+}
+
+__global__ void __launch_bounds__(256) compact_scatter_kernel(const uint32_t* routes, uint32_t* intermediates,
+                                                             const uint32_t* slots, uint32_t slot_words,
+                                                             uint32_t params, uint32_t* control,
+                                                             uint32_t max_tokens, uint32_t K, uint32_t I,
+                                                             uint32_t tiles_per_route, uint32_t num_experts,
+                                                             const uint32_t* block_hist, const uint32_t* bucket_base) {
+    const uint32_t T = min_u32(control[0], max_tokens);
+    const uint32_t count = T * K;
+    const uint32_t data_words = K * (I / 2u);
+    ScheduleEmit emit{intermediates, K, data_words + K, data_words};
+    const bool partitioned = control[2] != 0u;
+    // every block has read what it needs from control[0..2]; block 0 publishes the command words
+    if (partitioned) {
+        OwnedKey key{routes, slots, slot_words, params, control[1], control[1] + control[2]};
+        phase_scatter(count, num_experts + 1u, block_hist, bucket_base, key, emit);
+        if (blockIdx.x == 0u && threadIdx.x == 0u) {
+            uint32_t owned = bucket_base[1];
+            control[3] = owned;
+            control[4] = owned * tiles_per_route;
+            control[5] = 1u;
+            control[6] = 1u;
+        }
+    } else {
+        RouteKey key{routes, num_experts};
+        phase_scatter(count, num_experts + 1u, block_hist, bucket_base, key, emit);
+        if (blockIdx.x == 0u && threadIdx.x == 0u) {
+            control[3] = count;
+            control[4] = K * tiles_per_route;
+            control[5] = T;
+            control[6] = 1u;
+        }
+    }
+}
+
+// moe_route_count: the owned count only (one block; a grid-stride count is plenty here)
+__global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* routes, const uint32_t* slots,
+                                                          uint32_t slot_words, uint32_t params, uint32_t* control,
+                                                          uint32_t max_tokens, uint32_t K, uint32_t tiles_per_route) {
+    __shared__ uint32_t owned;
+    const uint32_t T = min_u32(control[0], max_tokens);
+    if (control[2] == 0u) {
+        if (threadIdx.x == 0u) {
+            control[3] = T * K;
+            control[4] = K * tiles_per_route;
+            control[5] = T;
+            control[6] = 1u;
+        }
+        return;
+    }
+    if (threadIdx.x == 0u) owned = 0u;
+    __syncthreads();
+    const uint32_t start = control[1], end = control[1] + control[2];
+    uint32_t mine = 0u;
+    for (uint32_t i = threadIdx.x; i < T * K; i += blockDim.x) {
+        uint32_t e = routes[i] & 0xffffu;
+        if (e >= start && e < end && resource_is_local(slots, slot_words, params, e)) mine++;
+    }
+    atomicAdd(&owned, mine);
+    __syncthreads();
+    if (threadIdx.x == 0u) {
+        control[3] = owned;
+        control[4] = owned * tiles_per_route;
+        control[5] = 1u;
+        control[6] = 1u;
+    }
+}
+
+// address_record_is_resident + dynamic_parameter_record_is_valid for every expert, once per call
+__global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
+                                       uint32_t slot_words, uint32_t params, uint32_t num_experts,
+                                       uint64_t weight_bytes, uint64_t scale_bytes, ExpertPtrs* out) {
+    uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= num_experts) return;
+    ExpertPtrs r{{nullptr, nullptr}, {nullptr, nullptr}};
+    bool ok = true;
+    const uint8_t* ptrs[4] = {nullptr, nullptr, nullptr, nullptr};
+    for (uint32_t j = 0; j < params && ok; j++) {
+        uint64_t index = (uint64_t)e * params + j;
+        if (index >= slot_words) {
+            ok = false;
+            break;
+        }
+        uint32_t slot = slots[index];
+        if (slot == kUnboundSlot || slot >= address_words / kRecordWords) {
+            ok = false;
+            break;
+        }
+        const uint32_t* rec = addresses + (size_t)slot * kRecordWords;
+        uint64_t address = (uint64_t)rec[0] | ((uint64_t)rec[1] << 32);
+        uint64_t bytes = (uint64_t)rec[2] | ((uint64_t)rec[3] << 32);
+        uint64_t required = (j & 1u) ? scale_bytes : weight_bytes;
+        // representation 0 (compact MXFP4) is the only one built; anything else fails closed
+        // and the kernels read rows with 16-byte loads, so the shader's 4-byte rule becomes 16
+        if (address == 0u || (address & 15u) != 0u || bytes < required || (rec[4] | rec[5]) == 0u ||
+            rec[6] != 1u || rec[7] != 0u) {
+            ok = false;
+            break;
+        }
+        ptrs[j] = reinterpret_cast<const uint8_t*>(address);
+    }
+    if (ok) {
+        r.w[0] = ptrs[0];
+        r.s[0] = ptrs[1];
+        r.w[1] = params == 4u ? ptrs[2] : nullptr;
+        r.s[1] = params == 4u ? ptrs[3] : nullptr;
+    }
+    out[e] = r;
+}
+
+__device__ __forceinline__ uint32_t slot_count(const uint32_t* control, uint32_t max_tokens, uint32_t K) {
+    const uint32_t T = min_u32(control[0], max_tokens);
+    // route-native calls visit owned_route_count slots, the others every (batch, route) position
+    return control[2] != 0u ? min_u32(control[3], T * K) : T * K;
+}
+
+__global__ void __launch_bounds__(1024) group_small_kernel(SlotKey key, const uint32_t* control,
+                                                          uint32_t max_tokens, uint32_t* grouped,
+                                                          uint32_t* expert_offsets) {
+    extern __shared__ uint32_t hist[];
+    const uint32_t T = min_u32(control[0], max_tokens);
+    key.capacity = T * key.K;
+    const uint32_t count = slot_count(control, max_tokens, key.K);
+    GroupEmit emit{key, grouped};
+    const uint32_t buckets = key.num_experts;
+    sort_single_block(count, buckets, hist, key, emit, [&](const uint32_t* base) {
+        for (uint32_t b = threadIdx.x; b <= buckets; b += blockDim.x) expert_offsets[b] = base[b];
+    });
+}
+
+__global__ void __launch_bounds__(256) group_hist_kernel(SlotKey key, const uint32_t* control,
+                                                        uint32_t max_tokens, uint32_t* block_hist) {
+    key.capacity = min_u32(control[0], max_tokens) * key.K;
+    key.status = nullptr;  // raised once, by the scatter pass
+    phase_hist(slot_count(control, max_tokens, key.K), key.num_experts, block_hist, key);
+}
+
+__global__ void __launch_bounds__(256) group_scatter_kernel(SlotKey key, const uint32_t* control,
+                                                           uint32_t max_tokens, uint32_t* grouped,
+                                                           uint32_t* expert_offsets, const uint32_t* block_hist,
+                                                           const uint32_t* bucket_base) {
+    key.capacity = min_u32(control[0], max_tokens) * key.K;
+    GroupEmit emit{key, grouped};
+    phase_scatter(slot_count(control, max_tokens, key.K), key.num_experts, block_hist, bucket_base, key, emit);
+    if (blockIdx.x == 0u)
+        for (uint32_t b = threadIdx.x; b <= key.num_experts; b += blockDim.x) expert_offsets[b] = bucket_base[b];
+}
+
+constexpr uint32_t kSmallSortLimit = 4096u;
+
+}  // namespace
+
+void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const uint32_t* slots,
+                          uint32_t slot_words, uint32_t params_per_resource, uint32_t* control,
+                          uint32_t max_tokens, uint32_t K, uint32_t intermediate_size,
+                          uint32_t tiles_per_route, uint32_t num_experts, const SortScratch& scratch,
+                          cudaStream_t stream) {
+    const uint32_t count = max_tokens * K;
+    const uint32_t buckets = num_experts + 1u;
+    if (count <= kSmallSortLimit) {
+        uint32_t threads = count <= 256u ? 256u : 1024u;
+        compact_small_kernel<<<1, threads, (buckets + 1u) * sizeof(uint32_t), stream>>>(
+            routes, intermediates, slots, slot_words, params_per_resource, control, max_tokens, K,
+            intermediate_size, tiles_per_route, num_experts);
+        return;
+    }
+    const uint32_t blocks = (count + kSortChunk - 1u) / kSortChunk;
+    compact_hist_kernel<<<blocks, 256, buckets * sizeof(uint32_t), stream>>>(
+        routes, slots, slot_words, params_per_resource, control, max_tokens, K, num_experts, scratch.block_hist);
+    // the partitioned form uses one bucket; scanning all of them costs nothing and needs no host read
+    phase_scan_kernel<<<1, 1024, buckets * sizeof(uint32_t), stream>>>(scratch.block_hist, scratch.bucket_base,
+                                                                        blocks, buckets);
+    compact_scatter_kernel<<<blocks, 256, buckets * sizeof(uint32_t), stream>>>(
+        routes, intermediates, slots, slot_words, params_per_resource, control, max_tokens, K,
+        intermediate_size, tiles_per_route, num_experts, scratch.block_hist, scratch.bucket_base);
+}
+
+void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t slot_words,
+                        uint32_t params_per_resource, uint32_t* control, uint32_t max_tokens, uint32_t K,
+                        uint32_t tiles_per_route, cudaStream_t stream) {
+    route_count_kernel<<<1, 1024, 0, stream>>>(routes, slots, slot_words, params_per_resource, control,
+                                               max_tokens, K, tiles_per_route);
+}
+
+void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
+                            uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
+                            uint64_t weight_bytes, uint64_t scale_bytes, ExpertPtrs* out,
+                            cudaStream_t stream) {
+    resolve_experts_kernel<<<(num_experts + 127u) / 128u, 128, 0, stream>>>(
+        addresses, address_words, slots, slot_words, params_per_resource, num_experts, weight_bytes,
+        scale_bytes, out);
+}
+
+void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,
+                        const ExpertPtrs* experts, uint32_t num_experts, uint32_t max_tokens, uint32_t K,
+                        uint32_t intermediate_size, uint32_t* grouped_routes, uint32_t* expert_offsets,
+                        uint32_t* status, const SortScratch& scratch, cudaStream_t stream) {
+    const uint32_t data_words = K * (intermediate_size / 2u);
+    SlotKey key{routes, intermediates, experts, status, num_experts, K, data_words + K, data_words, 0u};
+    const uint32_t count = max_tokens * K;
+    if (count <= kSmallSortLimit) {
+        uint32_t threads = count <= 256u ? 256u : 1024u;
+        group_small_kernel<<<1, threads, (num_experts + 1u) * sizeof(uint32_t), stream>>>(
+            key, control, max_tokens, grouped_routes, expert_offsets);
+        return;
+    }
+    const uint32_t blocks = (count + kSortChunk - 1u) / kSortChunk;
+    group_hist_kernel<<<blocks, 256, num_experts * sizeof(uint32_t), stream>>>(key, control, max_tokens,
+                                                                               scratch.block_hist);
+    phase_scan_kernel<<<1, 1024, num_experts * sizeof(uint32_t), stream>>>(scratch.block_hist, scratch.bucket_base,
+                                                                            blocks, num_experts);
+    group_scatter_kernel<<<blocks, 256, num_experts * sizeof(uint32_t), stream>>>(
+        key, control, max_tokens, grouped_routes, expert_offsets, scratch.block_hist, scratch.bucket_base);
+}
+
+}  // namespace nvmoe

@@ -413,3 +413,19 @@ def moe_layer(rp: RouterParams, ep: ExpertParams, hidden_bf16: np.ndarray, logit
     down(ep, inter, routes, outputs, daddr, dslots, dcontrol)
     out = reduce(outputs, tokens, K, H, reduce_scale)
     return out, routes, outputs, inter
+
+
+def router_params_from(cfg) -> RouterParams:
+    """RouterParams of a ``nerve_b200.synthetic.MoeConfig`` (duck-typed: the checker imports no product code)."""
+    return RouterParams(
+        routed_experts=cfg.experts, routed_k=cfg.k, always_count=cfg.always_count,
+        always_weight=cfg.always_weight, kind=cfg.router_kind, activation=cfg.activation,
+        normalize_selected=cfg.normalize_selected, bias_dtype=cfg.bias_dtype, routed_scale=cfg.routed_scale,
+        logit_softcap=cfg.logit_softcap, n_group=cfg.n_group, topk_group=cfg.topk_group)
+
+
+def expert_params_from(cfg, tier: int = 1) -> ExpertParams:
+    return ExpertParams(
+        hidden_size=cfg.hidden, intermediate_size=cfg.intermediate, num_experts=cfg.total_experts,
+        experts_per_token=cfg.total_k, tile_rows=32, swiglu_limit=cfg.swiglu_limit,
+        swiglu_alpha=cfg.swiglu_alpha, swiglu_up_offset=cfg.swiglu_up_offset, act_block=cfg.act_block, tier=tier)
