@@ -136,6 +136,9 @@ void nvmoe_device_close(nvmoe_device* device);
 const char* nvmoe_last_error(const nvmoe_device* device);
 /* The CUDA stream every launch of this device uses (a cudaStream_t). */
 void* nvmoe_device_stream(const nvmoe_device* device);
+/* Launch on a stream the caller owns instead (null restores the device's own stream), so that
+ * the operators order with the caller's collectives without events. */
+int nvmoe_device_set_stream(nvmoe_device* device, void* cuda_stream);
 
 /* create_resident_buffer / write_bytes[_at] / read_bytes[_at] / device_address
  * (vulkan_compute/resident_buffers.rs:39-232). Buffers are zero-filled at creation. */
@@ -144,6 +147,10 @@ void nvmoe_buffer_destroy(nvmoe_buffer* buffer);
 int nvmoe_buffer_write(nvmoe_buffer* buffer, size_t offset, const void* src, size_t bytes);
 int nvmoe_buffer_read(nvmoe_buffer* buffer, size_t offset, void* dst, size_t bytes);
 int nvmoe_buffer_fill(nvmoe_buffer* buffer, size_t offset, int byte_value, size_t bytes);
+/* A handle over device memory the caller allocated (for example a tensor of the host framework);
+ * destroying it frees the handle only. The reference's buffers are always device-owned
+ * (resident_buffers.rs:39-60); this exists so that collectives and kernels can share memory. */
+int nvmoe_buffer_wrap(nvmoe_device* device, void* device_ptr, size_t bytes, nvmoe_buffer** out);
 uint64_t nvmoe_buffer_device_address(const nvmoe_buffer* buffer);
 size_t nvmoe_buffer_byte_capacity(const nvmoe_buffer* buffer);
 
@@ -279,6 +286,29 @@ typedef struct nvmoe_work_report {
     uint64_t weight_bytes_touched;
 } nvmoe_work_report;
 int nvmoe_plan_last_report(nvmoe_plan* plan, nvmoe_work_report* report);
+/* Kernels launched through this plan since it was created. */
+uint64_t nvmoe_plan_launch_count(const nvmoe_plan* plan);
+
+/*
+ * Expert-parallel exchange, the all-to-all form of the reference's expert-range ownership
+ * (nerve/physical_execution_contracts.py:690-757; ownership "every resource owned exactly once",
+ * runtime-rs/src/vulkan_distributed/selected_resource_placement.rs:289-351).
+ *
+ * nvmoe_ep_pack groups the T*K routes of this rank's tokens by the rank that owns their expert
+ * (owner_table[expert] = rank, 0xffffffff = replicated on every rank, i.e. kept local), stably in
+ * source order, and gathers the hidden row of each route into send_rows in that order.
+ *   send_routes[pos]  the route word travelling with row pos
+ *   send_index[i]     position of source route i = t*K + r (0xffffffff if it was dropped)
+ *   dest_counts[rank] rows bound for each rank (the split sizes of the all-to-all)
+ * nvmoe_ep_unpack puts the rows that came back (same positions) into expert_outputs [T][K][H] so
+ * that moe_reduce runs unchanged.
+ */
+int nvmoe_ep_pack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hidden,
+                  const nvmoe_buffer* routes, const nvmoe_buffer* owner_table, uint32_t world_size,
+                  uint32_t rank, nvmoe_buffer* send_rows, nvmoe_buffer* send_routes,
+                  nvmoe_buffer* send_index, nvmoe_buffer* dest_counts);
+int nvmoe_ep_unpack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* returned_rows,
+                    const nvmoe_buffer* send_index, nvmoe_buffer* expert_outputs);
 
 #ifdef __cplusplus
 }

@@ -66,6 +66,10 @@ class CudaComputeDevice:
         """The ``cudaStream_t`` all launches of this device go to, as an integer."""
         return int(self._lib.nvmoe_device_stream(self._h) or 0)
 
+    def set_stream(self, cuda_stream: int) -> None:
+        """Launch on a stream the caller owns (0 restores the device's own stream)."""
+        self._check(self._lib.nvmoe_device_set_stream(self._h, ctypes.c_void_p(cuda_stream or None)))
+
     def synchronize(self, timeout_ns: int = 60_000_000_000) -> None:
         self._check(self._lib.nvmoe_sync(self._h, timeout_ns))
 
@@ -78,12 +82,21 @@ class CudaComputeDevice:
 class ResidentBuffer:
     """``VulkanResidentBuffer``: device memory with byte-level read/write and a device address."""
 
-    def __init__(self, device: CudaComputeDevice, byte_capacity: int):
+    def __init__(self, device: CudaComputeDevice, byte_capacity: int, _wrap_ptr: int | None = None):
         self.device = device
         handle = ctypes.c_void_p()
-        device._check(device._lib.nvmoe_buffer_create(device._h, byte_capacity, ctypes.byref(handle)))
+        if _wrap_ptr is None:
+            device._check(device._lib.nvmoe_buffer_create(device._h, byte_capacity, ctypes.byref(handle)))
+        else:
+            device._check(device._lib.nvmoe_buffer_wrap(device._h, ctypes.c_void_p(_wrap_ptr), byte_capacity,
+                                                        ctypes.byref(handle)))
         self._h = handle
         self.byte_capacity = byte_capacity
+
+    @classmethod
+    def wrap(cls, device: CudaComputeDevice, device_ptr: int, byte_capacity: int) -> "ResidentBuffer":
+        """A handle over device memory the caller owns (a framework tensor); destroy frees the handle only."""
+        return cls(device, byte_capacity, _wrap_ptr=device_ptr)
 
     def write_bytes(self, data, offset: int = 0) -> None:
         array = np.ascontiguousarray(data) if not isinstance(data, (bytes, bytearray)) else np.frombuffer(data, dtype=np.uint8)
@@ -260,6 +273,19 @@ class MoePlan:
 
     def moe_reduce(self, batch_width, expert_outputs, output):
         self._call("nvmoe_reduce", batch_width, _h(expert_outputs), _h(output))
+
+    # -- expert-parallel exchange ------------------------------------------------------------
+    def ep_pack(self, batch_width, hidden, routes, owner_table, world_size, rank, send_rows, send_routes, send_index,
+                dest_counts):
+        self._call("nvmoe_ep_pack", batch_width, _h(hidden), _h(routes), _h(owner_table), world_size, rank,
+                   _h(send_rows), _h(send_routes), _h(send_index), _h(dest_counts))
+
+    def ep_unpack(self, batch_width, returned_rows, send_index, expert_outputs):
+        self._call("nvmoe_ep_unpack", batch_width, _h(returned_rows), _h(send_index), _h(expert_outputs))
+
+    def launches(self) -> int:
+        """Kernels this plan has launched since it was created."""
+        return int(self.device._lib.nvmoe_plan_launch_count(self._h))
 
     # -- the whole chain -------------------------------------------------------------------
     def _layer_args(self, batch_width, bank: ExpertBank, hidden=None, output=None, router_weights=None,

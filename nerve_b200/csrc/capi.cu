@@ -17,7 +17,8 @@ using namespace nvmoe;
 
 struct nvmoe_device {
     int ordinal = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;      // where launches go: own_stream unless the caller lent one
+    cudaStream_t own_stream = nullptr;
     cudaEvent_t sync_event = nullptr;
     std::string error;
 };
@@ -26,6 +27,7 @@ struct nvmoe_buffer {
     nvmoe_device* device = nullptr;
     void* ptr = nullptr;
     size_t bytes = 0;
+    bool owned = true;  // false for handles over memory the caller allocated
 };
 
 namespace {
@@ -90,7 +92,7 @@ struct nvmoe_plan {
     int expert_path = 0;
     // scratch every expert call needs
     DeviceArray status, gu_ptrs, down_ptrs, grouped[2], offsets[2], block_hist, bucket_base;
-    DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list;
+    DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list, ep_source;
     // scratch of the fused layer call
     DeviceArray logits, routes, frames, expert_outputs, controls, hidden_dev, output_dev;
     void* pinned_in = nullptr;
@@ -239,6 +241,7 @@ int nvmoe_device_open(int cuda_ordinal, nvmoe_device** out) {
         delete d;
         return fail(nullptr, NVMOE_ERR_CUDA, "stream setup failed: %s", cudaGetErrorString(e2));
     }
+    d->own_stream = d->stream;
     *out = d;
     return NVMOE_OK;
 }
@@ -248,8 +251,16 @@ void nvmoe_device_close(nvmoe_device* d) {
     cudaSetDevice(d->ordinal);
     cudaStreamSynchronize(d->stream);
     cudaEventDestroy(d->sync_event);
-    cudaStreamDestroy(d->stream);
+    cudaStreamDestroy(d->own_stream);
     delete d;
+}
+
+int nvmoe_device_set_stream(nvmoe_device* d, void* stream) {
+    if (!d) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));  // nothing may straddle the switch
+    d->stream = stream ? (cudaStream_t)stream : d->own_stream;
+    return NVMOE_OK;
 }
 
 const char* nvmoe_last_error(const nvmoe_device* d) { return d ? d->error.c_str() : g_open_error.c_str(); }
@@ -280,11 +291,32 @@ int nvmoe_buffer_create(nvmoe_device* d, size_t bytes, nvmoe_buffer** out) {
     return NVMOE_OK;
 }
 
+int nvmoe_buffer_wrap(nvmoe_device* d, void* device_ptr, size_t bytes, nvmoe_buffer** out) {
+    if (!d || !out) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "null device or out pointer");
+    *out = nullptr;
+    if (!device_ptr || bytes == 0) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "cannot wrap a null or empty range");
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    cudaPointerAttributes attr;
+    NVMOE_CUDA(d, cudaPointerGetAttributes(&attr, device_ptr));
+    if (attr.type != cudaMemoryTypeDevice || attr.device != d->ordinal)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "the pointer is not device memory of CUDA ordinal %d", d->ordinal);
+    nvmoe_buffer* b = new (std::nothrow) nvmoe_buffer();
+    if (!b) return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "out of host memory");
+    b->device = d;
+    b->ptr = device_ptr;
+    b->bytes = bytes;
+    b->owned = false;
+    *out = b;
+    return NVMOE_OK;
+}
+
 void nvmoe_buffer_destroy(nvmoe_buffer* b) {
     if (!b) return;
-    cudaSetDevice(b->device->ordinal);
-    cudaStreamSynchronize(b->device->stream);
-    cudaFree(b->ptr);
+    if (b->owned) {
+        cudaSetDevice(b->device->ordinal);
+        cudaStreamSynchronize(b->device->stream);
+        cudaFree(b->ptr);
+    }
     delete b;
 }
 
@@ -402,7 +434,7 @@ void nvmoe_plan_destroy(nvmoe_plan* p) {
     cudaStreamSynchronize(p->device->stream);
     DeviceArray* all[] = {&p->status, &p->gu_ptrs, &p->down_ptrs, &p->grouped[0], &p->grouped[1], &p->offsets[0],
                           &p->offsets[1], &p->block_hist, &p->bucket_base, &p->xq, &p->x_scales, &p->x_e8m0, &p->iq,
-                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
+                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
                           &p->controls, &p->hidden_dev, &p->output_dev};
     for (DeviceArray* a : all) a->release();
     if (p->pinned_in) cudaFreeHost(p->pinned_in);
@@ -683,6 +715,53 @@ int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, 
     return post_launch(p, "reduce");
 }
 
+// ---- expert-parallel exchange helpers -----------------------------------------------------------
+
+int nvmoe_ep_pack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const nvmoe_buffer* routes,
+                  const nvmoe_buffer* owner_table, uint32_t world, uint32_t rank, nvmoe_buffer* send_rows,
+                  nvmoe_buffer* send_routes, nvmoe_buffer* send_index, nvmoe_buffer* dest_counts) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    if (world == 0u || world > 1024u || rank >= world)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "rank %u of %u is not a valid expert-parallel position", rank, world);
+    const size_t R = (size_t)T * p->K;
+    NVMOE_TRY(check_buffer(p, hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
+    NVMOE_TRY(check_buffer(p, routes, R * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, owner_table, (size_t)p->experts * 4u, "owner table"));
+    NVMOE_TRY(check_buffer(p, send_rows, R * g.hidden_size * 2u, "send rows"));
+    NVMOE_TRY(check_buffer(p, send_routes, R * 4u, "send routes"));
+    NVMOE_TRY(check_buffer(p, send_index, R * 4u, "send index"));
+    NVMOE_TRY(check_buffer(p, dest_counts, (size_t)world * 4u, "destination counts"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    cudaError_t err = p->ep_source.ensure(((size_t)p->g.max_tokens * p->K + 64u) * 4u);
+    if (err != cudaSuccess) return fail(p->device, NVMOE_ERR_OUT_OF_MEMORY, "exchange scratch allocation failed: %s", cudaGetErrorString(err));
+    if ((size_t)world > (size_t)p->experts + 1u)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "more ranks (%u) than resources (%u)", world, p->experts);
+    uint32_t* total = p->ep_source.as<uint32_t>();
+    launch_ep_pack((const uint16_t*)hidden->ptr, (const uint32_t*)routes->ptr, (const uint32_t*)owner_table->ptr, T, p->K,
+                   g.hidden_size, p->experts, world, rank, (uint16_t*)send_rows->ptr, (uint32_t*)send_routes->ptr,
+                   (uint32_t*)send_index->ptr, total + 64, (uint32_t*)dest_counts->ptr, total, sort_scratch(p),
+                   p->device->stream);
+    p->launches += 3;
+    return post_launch(p, "expert-parallel pack");
+}
+
+int nvmoe_ep_unpack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* returned_rows, const nvmoe_buffer* send_index,
+                    nvmoe_buffer* expert_outputs) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const size_t R = (size_t)T * p->K;
+    NVMOE_TRY(check_buffer(p, returned_rows, R * p->g.hidden_size * 2u, "returned rows"));
+    NVMOE_TRY(check_buffer(p, send_index, R * 4u, "send index"));
+    NVMOE_TRY(check_buffer(p, expert_outputs, R * p->g.hidden_size * 2u, "expert outputs"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_ep_unpack((const uint16_t*)returned_rows->ptr, (const uint32_t*)send_index->ptr, T, p->K, p->g.hidden_size,
+                     (uint16_t*)expert_outputs->ptr, p->device->stream);
+    p->launches++;
+    return post_launch(p, "expert-parallel unpack");
+}
+
 // ---- fused layer -------------------------------------------------------------------------------
 
 static int ensure_layer_scratch(nvmoe_plan* p) {
@@ -810,6 +889,8 @@ int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hi
     std::memcpy(output_host, p->pinned_out, bytes);
     return NVMOE_OK;
 }
+
+uint64_t nvmoe_plan_launch_count(const nvmoe_plan* p) { return p ? p->launches : 0u; }
 
 int nvmoe_plan_last_report(nvmoe_plan* p, nvmoe_work_report* report) {
     if (!p || !report) return NVMOE_ERR_INVALID_ARGUMENT;

@@ -96,6 +96,16 @@ void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, c
                         uint32_t intermediate_size, uint32_t* grouped_routes, uint32_t* expert_offsets,
                         uint32_t* status, const SortScratch& scratch, cudaStream_t stream);
 
+// expert-parallel dispatch (schedule.cu): routes grouped by the rank owning their expert, stable
+// in source order; send_index[i] = position of source route i (kUnboundSlot if dropped),
+// send_source[pos] = source route; hidden rows are gathered into send_rows in that order
+void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32_t* owner, uint32_t tokens,
+                    uint32_t K, uint32_t hidden_size, uint32_t num_experts, uint32_t world, uint32_t self,
+                    uint16_t* send_rows, uint32_t* send_routes, uint32_t* send_index, uint32_t* send_source,
+                    uint32_t* dest_counts, uint32_t* total, const SortScratch& scratch, cudaStream_t stream);
+void launch_ep_unpack(const uint16_t* returned_rows, const uint32_t* send_index, uint32_t tokens, uint32_t K,
+                      uint32_t hidden_size, uint16_t* expert_outputs, cudaStream_t stream);
+
 // quantize.cu: bf16 rows -> E4M3 bytes + per-block power-of-two scales.
 // scales_f32 ([rows][cols/block]) and scales_e8m0 ([rows][ceil(cols/128)] words, four E8M0 bytes of
 // consecutive 32-column blocks per word) are both optional.

@@ -15,12 +15,13 @@
 // a handful of tokens per expert still fills an MMA (N = 16), and every weight byte is read once.
 // One CTA per SM walks a list of (expert, token tile) x weight-row tiles.
 //
-// Roles (288 threads): warps 0-3 epilogue (TMEM lane quadrant = warp), warp 4 allocates TMEM and
+// Roles (320 threads): warps 0-3 epilogue (TMEM lane quadrant = warp), warp 4 allocates TMEM and
 // one of its lanes issues the scale copies and MMAs, warps 5-8 stage operands into shared memory
-// with cp.async.  E2M1 codes travel as 8-byte pieces into the low half of 16-byte slots (the
-// padded 4-bit format the f8f6f4 kinds read), rows are gathered through the expert-grouped route
-// list, and E8M0 scales are laid out in the 32x16-byte blocks tcgen05.cp expands into TMEM.
-// Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
+// with cp.async whose completion arrives on the stage's mbarrier without stalling the issuer, and
+// warp 9 moves the scale bytes.  E2M1 codes travel as 8-byte pieces into the low half of 16-byte
+// slots (the padded 4-bit format the f8f6f4 kinds read), rows are gathered through the
+// expert-grouped route list, and E8M0 scales are laid out in the 32x16-byte blocks tcgen05.cp
+// expands into TMEM.  Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
 #include "experts_tc.cuh"
 #include "tcgen05.cuh"
 
@@ -33,12 +34,12 @@ constexpr uint32_t kBlockM = 128u;   // weight rows per tile
 constexpr uint32_t kBlockK = 128u;   // K elements per pipeline stage = 4 MMAs of K = 32
 constexpr uint32_t kProducerThreads = 128u;
 constexpr uint32_t kEpilogueThreads = 128u;
-constexpr uint32_t kThreads = 288u;
+constexpr uint32_t kThreads = 320u;
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
 constexpr uint32_t kSmemBudget = 215u * 1024u;
 constexpr uint32_t kMaxStages = 8u;
-constexpr uint32_t kSfPrefetch = 2u;               // stages of weight-scale loads kept in registers
+constexpr uint32_t kSfPrefetch = 2u;               // stages of scale loads the scale warp keeps in registers
 
 struct TileList {
     const uint32_t* tiles;   // (expert << 16) | token tile within the expert
@@ -49,10 +50,11 @@ template <bool GATE_UP, uint32_t N_TILE>
 struct Config {
     static constexpr uint32_t kMatrices = GATE_UP ? 2u : 1u;
     static constexpr uint32_t kBTileBytes = N_TILE * 128u;
-    static constexpr uint32_t kStageBytes = kMatrices * kATileBytes + kBTileBytes + (kMatrices + 1u) * kScaleBlockBytes;
+    // every stage starts on a 1024-byte boundary: the 128-byte swizzle is a function of the address
+    static constexpr uint32_t kStageBytes =
+        (kMatrices * kATileBytes + kBTileBytes + (kMatrices + 1u) * kScaleBlockBytes + 1023u) / 1024u * 1024u;
     static constexpr uint32_t kStagesRaw = kSmemBudget / kStageBytes;
     static constexpr uint32_t kStages = kStagesRaw > kMaxStages ? kMaxStages : kStagesRaw;
-    static constexpr uint32_t kLookahead = kStages - 1u;  // cp.async groups in flight per producer thread
     static constexpr uint32_t kAccColumns = kMatrices * N_TILE;
     static constexpr uint32_t kAccStages = (2u * kAccColumns + 16u <= 512u) ? 2u : 1u;
     static constexpr uint32_t kScaleColumns = 4u * (kMatrices + 1u);
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
     // ---- one-time setup ---------------------------------------------------------------------
     if (threadIdx.x == 0u) {
         for (uint32_t s = 0; s < C::kStages; s++) {
-            mbar_init(&bars->full[s], kProducerThreads);
+            mbar_init(&bars->full[s], kProducerThreads + 32u);  // 128 copy threads + the scale warp
             mbar_init(&bars->empty[s], 1u);
         }
         for (uint32_t a = 0; a < 2u; a++) {
@@ -121,12 +123,10 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_scales = tmem_base + C::kAccStages * C::kAccColumns;
 
-    if (warp >= 5u) {
-        // ===== producers =========================================================================
+    if (warp >= 5u && warp <= 8u) {
+        // ===== operand producers: cp.async into the swizzled tiles, completion arrives on `full` =====
         const uint32_t pt = threadIdx.x - 160u;  // 0..127
-        uint32_t it = 0u;          // k-block iterations issued
-        uint32_t signalled = 0u;   // k-block iterations handed to the MMA warp
-        uint32_t sf_regs[kSfPrefetch][C::kMatrices];
+        uint32_t it = 0u;
         bool alive = true;
         for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
             const uint32_t pair = list.tiles[tile / m_tiles];
@@ -136,8 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
             const uint32_t first = e_begin + n_tile * N_TILE;
             const uint32_t valid = min(N_TILE, e_end - first);
             const ExpertPtrs ptrs = p.work.experts[expert];
-            // activation rows this thread gathers: token rows (pt / 8) + 16 i for the codes and
-            // row pt for the scales (gate/up reads the token's hidden row, down the route's row)
+            // activation rows this thread gathers: token (pt / 8) + 16 i of the tile
+            // (gate/up reads the token's hidden row, down the route's own row)
             uint32_t code_rows[N_TILE / 16u];
 #pragma unroll
             for (uint32_t i = 0; i < N_TILE / 16u; i++) {
@@ -145,33 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
                 const uint32_t ri = n < valid ? __ldg(p.work.grouped_routes + first + n) : 0u;
                 code_rows[i] = GATE_UP ? ri / K : ri;
             }
-            uint32_t scale_row = 0u;
-            if (pt < valid) {
-                const uint32_t ri = __ldg(p.work.grouped_routes + first + pt);
-                scale_row = GATE_UP ? ri / K : ri;
-            }
             const uint32_t row0 = m_tile * kBlockM;
-            const uint32_t my_row = row0 + pt;  // this thread's weight row for the scale bytes
-            const bool my_row_ok = my_row < out_rows;
-            const uint32_t scale_row_bytes = k_dim / 32u;
-
-            auto load_weight_scales = [&](uint32_t kb, uint32_t (&dst)[C::kMatrices]) {
-#pragma unroll
-                for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
-                    uint32_t word = 0x7f7f7f7fu;
-                    if (my_row_ok && kb < k_blocks) {
-                        const uint8_t* src = ptrs.s[mx] + (size_t)my_row * scale_row_bytes + kb * 4u;
-                        const uint32_t have = min(4u, scale_row_bytes - kb * 4u);
-                        // scale rows are only 2-byte aligned in general: take them a byte at a time
-                        word = 0u;
-                        for (uint32_t j = 0; j < 4u; j++) word |= (uint32_t)(j < have ? __ldg(src + j) : 127u) << (8u * j);
-                    }
-                    dst[mx] = word;
-                }
-            };
-#pragma unroll
-            for (uint32_t f = 0; f < kSfPrefetch; f++) load_weight_scales(f, sf_regs[f]);
-
             for (uint32_t kb = 0; kb < k_blocks; kb++, it++) {
                 const uint32_t slot = it % C::kStages;
                 if (!mbar_wait(&bars->empty[slot], ((it / C::kStages) & 1u) ^ 1u, abort_flag)) {
@@ -179,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
                     break;
                 }
                 unsigned char* stage = smem + slot * C::kStageBytes;
-                const uint32_t k_bytes_left = (k_dim - kb * kBlockK);  // elements left in K from this block on
+                const uint32_t k_left = k_dim - kb * kBlockK;  // elements of K from this block on
                 // weights: 8-byte pieces of 16 codes into the low half of 16-byte slots
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
@@ -188,49 +162,109 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
 #pragma unroll
                     for (uint32_t i = 0; i < 8u; i++) {
                         const uint32_t r = (pt >> 3) + 16u * i, c = pt & 7u;
-                        const bool ok = (row0 + r < out_rows) && (c * 16u < k_bytes_left);
+                        const bool ok = (row0 + r < out_rows) && (c * 16u < k_left);
                         const uint8_t* src = ok ? wbase + (size_t)(row0 + r) * (k_dim / 2u) + kb * 64u + c * 8u : wbase;
                         cp_async_8(a_base + swizzle128_offset(r, c), src, ok ? 8u : 0u);
                     }
                 }
                 // activations: 16-byte pieces of 16 E4M3 codes, rows gathered through the route list
-                {
-                    const uint32_t b_base = smem_u32(stage + C::kMatrices * kATileBytes);
+                const uint32_t b_base = smem_u32(stage + C::kMatrices * kATileBytes);
 #pragma unroll
-                    for (uint32_t i = 0; i < N_TILE / 16u; i++) {
-                        const uint32_t n = (pt >> 3) + 16u * i, c = pt & 7u;
-                        const bool ok = (n < valid) && (c * 16u < k_bytes_left);
-                        const uint8_t* src = ok ? p.act_q + (size_t)code_rows[i] * k_dim + kb * kBlockK + c * 16u : p.act_q;
-                        cp_async_16(b_base + swizzle128_offset(n, c), src, ok ? 16u : 0u);
+                for (uint32_t i = 0; i < N_TILE / 16u; i++) {
+                    const uint32_t n = (pt >> 3) + 16u * i, c = pt & 7u;
+                    const bool ok = (n < valid) && (c * 16u < k_left);
+                    const uint8_t* src = ok ? p.act_q + (size_t)code_rows[i] * k_dim + kb * kBlockK + c * 16u : p.act_q;
+                    cp_async_16(b_base + swizzle128_offset(n, c), src, ok ? 16u : 0u);
+                }
+                // the arrival fires when this thread's copies have landed; the thread moves on at once
+                cp_async_arrive_noinc(&bars->full[slot]);
+            }
+        }
+        cp_async_wait_all();  // nothing of this thread may still be landing when the CTA retires
+    } else if (warp == 9u) {
+        // ===== scale producer: E8M0 bytes through registers into the 32x16-byte scale blocks ==========
+        // Weight scale rows are only 2-byte aligned (K/32 bytes per row), so they go through registers;
+        // lane l serves rows l, l+32, l+64, l+96 of the tile, loads run kSfPrefetch stages ahead.
+        uint32_t it = 0u;
+        bool alive = true;
+        const uint32_t scale_row_bytes = k_dim / 32u;
+        for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
+            const uint32_t pair = list.tiles[tile / m_tiles];
+            const uint32_t m_tile = tile % m_tiles;
+            const uint32_t expert = pair >> 16, n_tile = pair & 0xffffu;
+            const uint32_t e_begin = p.work.expert_offsets[expert], e_end = p.work.expert_offsets[expert + 1u];
+            const uint32_t first = e_begin + n_tile * N_TILE;
+            const uint32_t valid = min(N_TILE, e_end - first);
+            const ExpertPtrs ptrs = p.work.experts[expert];
+            const uint32_t row0 = m_tile * kBlockM;
+            constexpr uint32_t kTokenGroups = (N_TILE + 31u) / 32u;
+            uint32_t token_rows[kTokenGroups];
+#pragma unroll
+            for (uint32_t q = 0; q < kTokenGroups; q++) {
+                const uint32_t n = lane + 32u * q;
+                const uint32_t ri = n < valid ? __ldg(p.work.grouped_routes + first + n) : kUnboundSlot;
+                token_rows[q] = ri == kUnboundSlot ? kUnboundSlot : (GATE_UP ? ri / K : ri);
+            }
+            uint32_t wreg[kSfPrefetch][C::kMatrices][4];
+            uint32_t treg[kSfPrefetch][kTokenGroups];
+            auto load = [&](uint32_t kb, uint32_t (&w)[C::kMatrices][4], uint32_t (&t)[kTokenGroups]) {
+                const uint32_t have = kb < k_blocks ? min(4u, scale_row_bytes - kb * 4u) : 0u;
+#pragma unroll
+                for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
+#pragma unroll
+                    for (uint32_t q = 0; q < 4u; q++) {
+                        const uint32_t row = row0 + lane + 32u * q;
+                        uint32_t word = 0x7f7f7f7fu;
+                        if (have != 0u && row < out_rows) {
+                            const uint8_t* src = ptrs.s[mx] + (size_t)row * scale_row_bytes + kb * 4u;
+                            if ((scale_row_bytes & 1u) == 0u) {
+                                // even row length: every group of four starts on a 2-byte boundary
+                                const uint16_t* src16 = reinterpret_cast<const uint16_t*>(src);
+                                const uint32_t lo = __ldg(src16);
+                                const uint32_t hi = have > 2u ? __ldg(src16 + 1) : 0x7f7fu;
+                                word = lo | (hi << 16);
+                            } else {
+                                word = 0u;
+#pragma unroll
+                                for (uint32_t j = 0; j < 4u; j++) word |= (uint32_t)(j < have ? __ldg(src + j) : 127u) << (8u * j);
+                            }
+                        }
+                        w[mx][q] = word;
                     }
                 }
-                // scales: rows land at (row % 32) * 16 + (row / 32) * 4, four K-groups per word
-                unsigned char* sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
-                {
-                    const uint32_t off = (pt & 31u) * 16u + (pt >> 5) * 4u;
+#pragma unroll
+                for (uint32_t q = 0; q < kTokenGroups; q++)
+                    t[q] = (kb < k_blocks && token_rows[q] != kUnboundSlot) ? __ldg(p.act_e8m0 + (size_t)token_rows[q] * k_blocks + kb) : 0u;
+            };
+#pragma unroll
+            for (uint32_t f = 0; f < kSfPrefetch; f++) load(f, wreg[f], treg[f]);
+            for (uint32_t kb0 = 0; kb0 < k_blocks && alive; kb0 += kSfPrefetch) {
+#pragma unroll
+                for (uint32_t f = 0; f < kSfPrefetch; f++) {
+                    const uint32_t kb = kb0 + f;
+                    if (kb >= k_blocks) break;
+                    const uint32_t slot = it % C::kStages;
+                    if (!mbar_wait(&bars->empty[slot], ((it / C::kStages) & 1u) ^ 1u, abort_flag)) {
+                        alive = false;
+                        break;
+                    }
+                    unsigned char* sf = smem + slot * C::kStageBytes + C::kMatrices * kATileBytes + C::kBTileBytes;
+                    // row r of a block sits at (r % 32) * 16 + (r / 32) * 4: lane l owns one 16-byte line
 #pragma unroll
                     for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                        *reinterpret_cast<uint32_t*>(sf + mx * kScaleBlockBytes + off) = sf_regs[kb % kSfPrefetch][mx];
-                    load_weight_scales(kb + kSfPrefetch, sf_regs[kb % kSfPrefetch]);
-                    if (pt < N_TILE) {
-                        const bool ok = pt < valid;
-                        const uint32_t* src = ok ? p.act_e8m0 + (size_t)scale_row * k_blocks + kb : p.act_e8m0;
-                        cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + off), src, ok ? 4u : 0u);
-                    }
-                }
-                cp_async_commit();
-                if (it - signalled >= C::kLookahead) {
-                    cp_async_wait<C::kLookahead>();
-                    fence_proxy_async();
-                    mbar_arrive(&bars->full[signalled % C::kStages]);
-                    signalled++;
+                        *reinterpret_cast<uint4*>(sf + mx * kScaleBlockBytes + lane * 16u) =
+                            make_uint4(wreg[f][mx][0], wreg[f][mx][1], wreg[f][mx][2], wreg[f][mx][3]);
+                    uint32_t t4[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (uint32_t q = 0; q < kTokenGroups; q++) t4[q] = treg[f][q];
+                    *reinterpret_cast<uint4*>(sf + C::kMatrices * kScaleBlockBytes + lane * 16u) = make_uint4(t4[0], t4[1], t4[2], t4[3]);
+                    fence_proxy_async();  // this warp has no copies in flight: the fence is cheap
+                    mbar_arrive(&bars->full[slot]);
+                    it++;
+                    load(kb + kSfPrefetch, wreg[f], treg[f]);
                 }
             }
         }
-        // hand over what is still in flight
-        cp_async_wait<0>();
-        fence_proxy_async();
-        for (; signalled < it; signalled++) mbar_arrive(&bars->full[signalled % C::kStages]);
     } else if (warp == 4u) {
         // ===== MMA issue (one elected lane) ======================================================
         if (elect_one()) {
@@ -249,6 +283,7 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
                         break;
                     }
                     tc_fence_after();
+                    fence_proxy_async();  // the stage was written through the generic proxy
                     const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
                     const uint32_t sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
 #pragma unroll

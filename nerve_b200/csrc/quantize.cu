@@ -34,10 +34,11 @@ __device__ void quantize_body(RowFn row_of, uint32_t rows, uint32_t cols, uint32
     const uint64_t total = (uint64_t)rows * blocks_per_row;
     for (uint64_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < total; item += warps_per_grid) {
         const uint32_t r = (uint32_t)(item / blocks_per_row), b = (uint32_t)(item % blocks_per_row);
-        const uint2* in = reinterpret_cast<const uint2*>(row_of(r) + (size_t)b * block);
+        // rows of a frame are only 4-byte aligned when the route count is odd: 4-byte loads
+        const uint32_t* in = reinterpret_cast<const uint32_t*>(row_of(r) + (size_t)b * block);
         float m = 0.0f;
         for (uint32_t c4 = lane; c4 < block / 4u; c4 += 32u) {
-            uint2 v = in[c4];
+            uint2 v = make_uint2(in[2u * c4], in[2u * c4 + 1u]);
             m = fmaxf(m, fmaxf(fmaxf(fabsf(nvmoe_bf16_to_f32(v.x)), fabsf(nvmoe_bf16_to_f32(v.x >> 16))),
                                fmaxf(fabsf(nvmoe_bf16_to_f32(v.y)), fabsf(nvmoe_bf16_to_f32(v.y >> 16)))));
         }
@@ -46,7 +47,7 @@ __device__ void quantize_body(RowFn row_of, uint32_t rows, uint32_t cols, uint32
         const float inv = __fdiv_rn(1.0f, scale);  // exact: the scale is a power of two
         uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)r * cols + (size_t)b * block);
         for (uint32_t c4 = lane; c4 < block / 4u; c4 += 32u) {
-            uint2 v = in[c4];
+            uint2 v = make_uint2(in[2u * c4], in[2u * c4 + 1u]);
             out[c4] = to_e4m3x4(nvmoe_bf16_to_f32(v.x) * inv, nvmoe_bf16_to_f32(v.x >> 16) * inv,
                                 nvmoe_bf16_to_f32(v.y) * inv, nvmoe_bf16_to_f32(v.y >> 16) * inv);
         }

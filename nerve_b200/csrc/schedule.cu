@@ -419,9 +419,122 @@ __global__ void __launch_bounds__(256) group_scatter_kernel(SlotKey key, const u
         for (uint32_t b = threadIdx.x; b <= key.num_experts; b += blockDim.x) expert_offsets[b] = bucket_base[b];
 }
 
+// ---- expert-parallel dispatch: group routes by the rank that owns their expert ------------------
+
+struct DestKey {  // bucket = destination rank; kUnboundSlot in the owner table means "this rank"
+    const uint32_t* routes;
+    const uint32_t* owner;
+    uint32_t num_experts, world, self;
+    __device__ uint32_t operator()(uint32_t i) const {
+        uint32_t e = routes[i] & 0xffffu;
+        if (e >= num_experts) return kUnboundSlot;
+        uint32_t r = owner[e];
+        if (r == kUnboundSlot) r = self;
+        return r < world ? r : kUnboundSlot;
+    }
+};
+
+struct PackEmit {  // one warp-wide row copy per route would be faster; rows are copied by a second kernel
+    const uint32_t* routes;
+    uint32_t* send_routes;
+    uint32_t* send_index;
+    uint32_t* send_source;
+    __device__ void operator()(uint32_t rank, uint32_t i) const {
+        send_routes[rank] = routes[i];
+        send_index[i] = rank;
+        send_source[rank] = i;
+    }
+};
+
+__global__ void __launch_bounds__(1024) ep_pack_small_kernel(DestKey key, PackEmit emit, uint32_t count,
+                                                            uint32_t* dest_counts) {
+    extern __shared__ uint32_t hist[];
+    for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) emit.send_index[i] = kUnboundSlot;
+    __syncthreads();
+    sort_single_block(count, key.world, hist, key, emit, [&](const uint32_t* base) {
+        for (uint32_t b = threadIdx.x; b < key.world; b += blockDim.x) dest_counts[b] = base[b + 1u] - base[b];
+    });
+}
+
+__global__ void __launch_bounds__(256) ep_pack_hist_kernel(DestKey key, uint32_t count, uint32_t* block_hist,
+                                                          uint32_t* send_index) {
+    for (uint32_t i = blockIdx.x * kSortChunk + threadIdx.x; i < min_u32(count, (blockIdx.x + 1u) * kSortChunk); i += blockDim.x)
+        send_index[i] = kUnboundSlot;
+    phase_hist(count, key.world, block_hist, key);
+}
+
+__global__ void __launch_bounds__(256) ep_pack_scatter_kernel(DestKey key, PackEmit emit, uint32_t count,
+                                                             const uint32_t* block_hist, const uint32_t* bucket_base,
+                                                             uint32_t* dest_counts) {
+    phase_scatter(count, key.world, block_hist, bucket_base, key, emit);
+    if (blockIdx.x == 0u)
+        for (uint32_t b = threadIdx.x; b < key.world; b += blockDim.x) dest_counts[b] = bucket_base[b + 1u] - bucket_base[b];
+}
+
+// send_rows[p] = hidden[token of route send_source[p]]; one warp per row, 16-byte pieces
+__global__ void __launch_bounds__(256) ep_gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                            const uint32_t* __restrict__ index, const uint32_t* total,
+                                                            uint32_t max_rows, uint32_t divide, uint32_t row_vec) {
+    const uint32_t rows = total ? min_u32(*total, max_rows) : max_rows;
+    const uint32_t warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31u;
+    for (uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const uint32_t s = index[r];
+        if (s == kUnboundSlot) {
+            for (uint32_t c = lane; c < row_vec; c += 32u) dst[(size_t)r * row_vec + c] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
+        const uint4* from = src + (size_t)(s / divide) * row_vec;
+        for (uint32_t c = lane; c < row_vec; c += 32u) dst[(size_t)r * row_vec + c] = from[c];
+    }
+}
+
+__global__ void sum_counts_kernel(const uint32_t* counts, uint32_t n, uint32_t* total) {
+    if (threadIdx.x == 0u && blockIdx.x == 0u) {
+        uint32_t s = 0u;
+        for (uint32_t i = 0; i < n; i++) s += counts[i];
+        *total = s;
+    }
+}
+
 constexpr uint32_t kSmallSortLimit = 4096u;
 
 }  // namespace
+
+void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32_t* owner, uint32_t tokens,
+                    uint32_t K, uint32_t hidden_size, uint32_t num_experts, uint32_t world, uint32_t self,
+                    uint16_t* send_rows, uint32_t* send_routes, uint32_t* send_index, uint32_t* send_source,
+                    uint32_t* dest_counts, uint32_t* total, const SortScratch& scratch, cudaStream_t stream) {
+    const uint32_t count = tokens * K;
+    DestKey key{routes, owner, num_experts, world, self};
+    PackEmit emit{routes, send_routes, send_index, send_source};
+    if (count <= kSmallSortLimit) {
+        ep_pack_small_kernel<<<1, count <= 256u ? 256u : 1024u, (world + 1u) * sizeof(uint32_t), stream>>>(key, emit, count,
+                                                                                                           dest_counts);
+    } else {
+        const uint32_t blocks = (count + kSortChunk - 1u) / kSortChunk;
+        ep_pack_hist_kernel<<<blocks, 256, world * sizeof(uint32_t), stream>>>(key, count, scratch.block_hist, send_index);
+        phase_scan_kernel<<<1, 1024, world * sizeof(uint32_t), stream>>>(scratch.block_hist, scratch.bucket_base, blocks, world);
+        ep_pack_scatter_kernel<<<blocks, 256, world * sizeof(uint32_t), stream>>>(key, emit, count, scratch.block_hist,
+                                                                                 scratch.bucket_base, dest_counts);
+    }
+    sum_counts_kernel<<<1, 32, 0, stream>>>(dest_counts, world, total);
+    const uint32_t row_vec = hidden_size / 8u;  // uint4 per bf16 row
+    uint32_t blocks = (count + 7u) / 8u;
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    ep_gather_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(hidden), reinterpret_cast<uint4*>(send_rows),
+                                                      send_source, total, count, K, row_vec);
+}
+
+void launch_ep_unpack(const uint16_t* returned_rows, const uint32_t* send_index, uint32_t tokens, uint32_t K,
+                      uint32_t hidden_size, uint16_t* expert_outputs, cudaStream_t stream) {
+    const uint32_t count = tokens * K;
+    uint32_t blocks = (count + 7u) / 8u;
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    // expert_outputs[t][r] = returned_rows[send_index[t*K + r]]; routes that were dropped give zeros
+    ep_gather_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(returned_rows),
+                                                      reinterpret_cast<uint4*>(expert_outputs), send_index, nullptr, count,
+                                                      1u, hidden_size / 8u);
+}
 
 void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const uint32_t* slots,
                           uint32_t slot_words, uint32_t params_per_resource, uint32_t* control,

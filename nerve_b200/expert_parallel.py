@@ -1,0 +1,310 @@
+"""Expert-parallel MoE layer: one process per GPU, experts sharded by rank, tokens data-parallel.
+
+The reference shards this node pair by whole-expert ownership with the hidden frame replicated
+on every participant and the routed outputs collected afterwards
+(nerve/physical_execution_contracts.py:690-757,
+runtime-rs/src/vulkan_distributed/execution_plans.rs:1201-1205,2318-2322).  Here the same
+ownership vocabulary (an owner rank per resource, contiguous ``expert_range`` by default, "every
+resource owned exactly once") drives an all-to-all exchange over NCCL/NVLink instead:
+
+    route locally -> pack routes by owner rank -> all-to-all(rows, route words)
+      -> grouped gate/up + down on the owner -> all-to-all back -> unpack -> moe_reduce
+
+Every per-route row is computed by the same kernels, on the same operands, as on one GPU, and the
+combine sums them in the same order, so the result is bit-identical to the single-GPU layer.
+
+The exchange protocol (:func:`exchange`) is backend-neutral: the GPU path plugs in the CUDA
+operators, the CPU tests plug in stand-ins and run it over gloo.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import numpy as np
+
+UNOWNED = 0xFFFFFFFF
+
+
+def contiguous_owner_table(total_experts: int, routed_experts: int, world: int) -> np.ndarray:
+    """expert -> owner rank with contiguous ranges (expert_start = rank * E / G); resources past the
+    routed ones (always-selected, i.e. shared experts) are replicated and stay on the token's rank."""
+    if routed_experts % world:
+        raise ValueError(f"{routed_experts} routed experts do not split evenly over {world} ranks")
+    per = routed_experts // world
+    table = np.full(total_experts, UNOWNED, dtype=np.uint32)
+    table[:routed_experts] = np.arange(routed_experts, dtype=np.uint32) // per
+    return table
+
+
+def validate_owner_table(table: np.ndarray, routed_experts: int, world: int) -> None:
+    """The reference's placement rule: every routed resource is owned exactly once, by a real rank."""
+    if table.dtype != np.uint32 or table.ndim != 1 or table.size < routed_experts:
+        raise ValueError("owner table must be a uint32 vector covering every resource")
+    routed = table[:routed_experts]
+    if np.any(routed >= world):
+        raise ValueError("a routed expert has no owner among the ranks")
+
+
+def owned_experts(table: np.ndarray, rank: int) -> list[int]:
+    return [int(e) for e in np.nonzero((table == rank) | (table == UNOWNED))[0]]
+
+
+@dataclass
+class ExchangeOps:
+    """What :func:`exchange` needs from a backend. Tensors are torch tensors on the backend's device."""
+
+    route: callable        # () -> None: fills the local routes
+    pack: callable         # () -> (send_rows [R,H] int16, send_routes [R] int32, dest_counts [G] int32)
+    compute: callable      # (recv_rows [N,H], recv_routes [N], n) -> rows [N,H] int16 (first n valid)
+    unpack_reduce: callable  # (returned_rows [R,H]) -> None: fills the output
+    capacity: int          # rows the receive buffers hold
+
+
+def exchange(ops: ExchangeOps, dist, group=None):
+    """One layer step of the all-to-all protocol. Returns (rows sent, rows received)."""
+    import torch
+
+    ops.route()
+    send_rows, send_routes, dest_counts = ops.pack()
+    world = dist.get_world_size(group)
+    # split sizes travel first; they are needed on the host to size the row exchange
+    recv_counts = torch.empty_like(dest_counts)
+    dist.all_to_all_single(recv_counts, dest_counts, group=group)
+    send_splits = [int(v) for v in dest_counts.cpu().tolist()]
+    recv_splits = [int(v) for v in recv_counts.cpu().tolist()]
+    n_send, n_recv = sum(send_splits), sum(recv_splits)
+    if len(send_splits) != world or n_send > send_rows.shape[0]:
+        raise RuntimeError(f"destination counts {send_splits} do not describe {send_rows.shape[0]} packed rows")
+    if n_recv > ops.capacity:
+        raise RuntimeError(f"{n_recv} rows arrive but the receive buffers hold {ops.capacity}")
+    hidden = send_rows.shape[1]
+    recv_rows = torch.empty((max(n_recv, 1), hidden), dtype=send_rows.dtype, device=send_rows.device)
+    recv_routes = torch.empty((max(n_recv, 1),), dtype=send_routes.dtype, device=send_routes.device)
+    # bf16 rows travel as pairs in 32-bit words (every backend moves int32; gloo has no 16-bit all-to-all)
+    as_words = lambda t: t.view(torch.int32)  # noqa: E731
+    dist.all_to_all_single(as_words(recv_rows)[:n_recv], as_words(send_rows)[:n_send], recv_splits, send_splits, group=group)
+    dist.all_to_all_single(recv_routes[:n_recv], send_routes[:n_send], recv_splits, send_splits, group=group)
+    done = ops.compute(recv_rows, recv_routes, n_recv)
+    returned = torch.empty((max(n_send, 1), hidden), dtype=send_rows.dtype, device=send_rows.device)
+    dist.all_to_all_single(as_words(returned)[:n_send], as_words(done)[:n_recv], send_splits, recv_splits, group=group)
+    ops.unpack_reduce(returned)
+    return n_send, n_recv
+
+
+class ExpertParallelLayer:
+    """The GPU backend of :func:`exchange` for one rank."""
+
+    def __init__(self, cfg, tokens_per_rank: int, rank: int, world: int, device_index: int, seed: int = 0,
+                 owner_table: np.ndarray | None = None, expert_path: int = 0):
+        import torch
+
+        from . import synthetic
+        from .backend import CudaComputeDevice, ExpertBank, MoePlan, ResidentBuffer, geometry_from_config
+
+        self.torch = torch
+        self.cfg, self.rank, self.world, self.tokens = cfg, rank, world, tokens_per_rank
+        self.owner = contiguous_owner_table(cfg.total_experts, cfg.experts, world) if owner_table is None else owner_table
+        validate_owner_table(self.owner, cfg.experts, world)
+        torch.cuda.set_device(device_index)
+        self.tdev = torch.device("cuda", device_index)
+        self.device = CudaComputeDevice(device_index)
+        # all launches share the stream NCCL orders against: no events between kernels and collectives
+        self.stream = torch.cuda.current_stream(self.tdev)
+        self.device.set_stream(self.stream.cuda_stream)
+        T, K, H, G = tokens_per_rank, cfg.total_k, cfg.hidden, world
+        self.capacity = T * K * G
+        # this rank's tokens: rank r owns tokens [r*T, (r+1)*T) of the global batch
+        case = synthetic.make_case(cfg, T * G, seed=seed, with_weights=False)
+        self.case = case
+        local = slice(rank * T, (rank + 1) * T)
+        self.hidden_host = np.ascontiguousarray(case.hidden[local])
+        mine = owned_experts(self.owner, rank)
+        empty = [None] * cfg.total_experts
+        w = {k: list(empty) for k in ("w1", "s1", "w3", "s3", "w2", "s2")}
+        I = cfg.intermediate
+        for e in mine:
+            g = synthetic._stream(seed, f"expert{e}")
+            w["w1"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
+            w["s1"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
+            w["w3"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
+            w["s3"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
+            w["w2"][e] = g.integers(0, 256, (H, I // 2), dtype=np.uint8)
+            w["s2"][e] = g.integers(121, 128, (H, I // 32), dtype=np.uint8)
+        self.bank = ExpertBank.upload(self.device, w["w1"], w["s1"], w["w3"], w["s3"], w["w2"], w["s2"], present=mine)
+        self.home = MoePlan.for_config(self.device, cfg, T)
+        work_cfg = synthetic.MoeConfig(
+            cfg.name + "-work", cfg.hidden, cfg.intermediate, cfg.total_experts, 1, swiglu_limit=cfg.swiglu_limit,
+            swiglu_alpha=cfg.swiglu_alpha, swiglu_up_offset=cfg.swiglu_up_offset, act_block=cfg.act_block)
+        self.work = MoePlan.for_config(self.device, work_cfg, self.capacity)
+        for plan in (self.home, self.work):
+            if expert_path:
+                plan.set_expert_path(expert_path)
+
+        def dev_tensor(shape, dtype):
+            return torch.zeros(shape, dtype=dtype, device=self.tdev)
+
+        def wrap(t):
+            return ResidentBuffer.wrap(self.device, t.data_ptr(), t.numel() * t.element_size())
+
+        i16, i32 = torch.int16, torch.int32
+        self.t_hidden = torch.from_numpy(self.hidden_host.view(np.int16)).to(self.tdev)
+        self.t_router_w = torch.from_numpy(case.router_w.view(np.int16)).to(self.tdev)
+        self.t_logits = dev_tensor((T, (cfg.experts + 1) // 2), i32)
+        self.t_routes = dev_tensor((T, K), i32)
+        self.t_send_rows = dev_tensor((T * K, H), i16)
+        self.t_send_routes = dev_tensor((T * K,), i32)
+        self.t_send_index = dev_tensor((T * K,), i32)
+        self.t_dest_counts = dev_tensor((G,), i32)
+        self.t_owner = torch.from_numpy(self.owner.view(np.int32)).to(self.tdev)
+        self.t_frames = dev_tensor((self.capacity, self.work.frame_words), i32)
+        self.t_work_out = dev_tensor((self.capacity, H), i16)
+        self.t_controls = dev_tensor((16,), i32)
+        self.t_expert_outputs = dev_tensor((T, K, H), i16)
+        self.t_output = dev_tensor((T, H), i16)
+        self.b = {name: wrap(getattr(self, "t_" + name)) for name in (
+            "hidden", "router_w", "logits", "routes", "send_rows", "send_routes", "send_index", "dest_counts",
+            "owner", "frames", "work_out", "expert_outputs", "output")}
+        self.b["gate_control"] = ResidentBuffer.wrap(self.device, self.t_controls.data_ptr(), 28)
+        self.b["down_control"] = ResidentBuffer.wrap(self.device, self.t_controls.data_ptr() + 32, 28)
+        self.router_bias = self.device.resident_buffer_from(case.router_bias) if case.router_bias is not None else None
+        self.select_bias = self.device.resident_buffer_from(case.select_bias) if case.select_bias is not None else None
+        self.telemetry = self.device.create_resident_buffer(self.home.telemetry_words() * 4)
+        self.ops = ExchangeOps(self._route, self._pack, self._compute, self._unpack_reduce, self.capacity)
+
+    # -- backend pieces ------------------------------------------------------------------------
+    def _route(self):
+        b, T = self.b, self.tokens
+        self.home.linear(T, b["hidden"], b["logits"], b["router_w"], self.router_bias)
+        self.home.moe_route(T, b["logits"], b["routes"], self.select_bias, self.telemetry)
+
+    def _pack(self):
+        b = self.b
+        self.home.ep_pack(self.tokens, b["hidden"], b["routes"], b["owner"], self.world, self.rank, b["send_rows"],
+                          b["send_routes"], b["send_index"], b["dest_counts"])
+        return self.t_send_rows, self.t_send_routes, self.t_dest_counts
+
+    def _compute(self, recv_rows, recv_routes, n):
+        from .backend import ResidentBuffer
+
+        if n == 0:
+            return self.t_work_out
+        b = self.b
+        rows = ResidentBuffer.wrap(self.device, recv_rows.data_ptr(), n * recv_rows.shape[1] * 2)
+        routes = ResidentBuffer.wrap(self.device, recv_routes.data_ptr(), n * 4)
+        control = self.torch.tensor([n, 0, 0, 0, 0, 0, 0, 0, n, 0, 0, 0, 0, 0, 0, 0], dtype=self.torch.int32)
+        self.t_controls.copy_(control, non_blocking=False)
+        w = self.work
+        w.moe_route_compact(n, routes, b["frames"], b["gate_control"], self.bank.gate_up_slots)
+        w.independent_sparse_moe_gate_up(n, rows, routes, b["frames"], self.bank.gate_up_addresses,
+                                         self.bank.gate_up_slots, b["gate_control"])
+        w.moe_route_count(n, routes, b["down_control"], self.bank.down_slots)
+        w.independent_sparse_moe_down(n, b["frames"], routes, b["work_out"], self.bank.down_addresses,
+                                      self.bank.down_slots, b["down_control"])
+        rows.destroy()
+        routes.destroy()
+        return self.t_work_out
+
+    def _unpack_reduce(self, returned):
+        from .backend import ResidentBuffer
+
+        T = self.tokens
+        rb = ResidentBuffer.wrap(self.device, returned.data_ptr(), returned.numel() * 2)
+        if returned.shape[0] < T * self.cfg.total_k:
+            raise RuntimeError("fewer rows came back than routes were sent: a route had no owner")
+        self.home.ep_unpack(T, rb, self.b["send_index"], self.b["expert_outputs"])
+        self.home.moe_reduce(T, self.b["expert_outputs"], self.b["output"])
+        rb.destroy()
+
+    def step(self, dist, group=None):
+        return exchange(self.ops, dist, group)
+
+    def output(self) -> np.ndarray:
+        self.torch.cuda.synchronize()
+        return self.t_output.cpu().numpy().view(np.uint16)
+
+
+def bench_main(args, cfg, tokens, metric, unit):
+    """bench.py --gpus N: the layer expert-sharded over N ranks, tokens per rank fixed (weak scaling)."""
+    import json
+    import statistics
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path)
+    scratch = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device=f"cuda:{local}")
+    for _ in range(max(args.warmup, 3)):
+        layer.step(dist)
+    torch.cuda.synchronize()
+    dist.barrier()
+    times = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = None
+    if rank == 0:
+        import sys
+        from pathlib import Path
+
+        sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+        from bench import ClockSampler
+
+        sampler = ClockSampler(local)
+        sampler.start()
+    for _ in range(args.steps):
+        scratch.add_(1)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        layer.step(dist)
+        stop.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times.append(float(t.item()))
+    clocks = sampler.stop() if sampler else None
+    # end to end: tokens start in pinned host memory, the result is read back
+    host_in = torch.from_numpy(layer.hidden_host.view(np.int16)).pin_memory()
+    host_out = torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory()
+    e2e = []
+    for _ in range(args.steps):
+        scratch.add_(1)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        layer.t_hidden.copy_(host_in, non_blocking=True)
+        layer.step(dist)
+        host_out.copy_(layer.t_output, non_blocking=True)
+        stop.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e.append(float(t.item()))
+    ms = statistics.mean(times)
+    if rank == 0:
+        total_tokens = tokens * world
+        line = {
+            "metric": metric, "value": total_tokens / (ms * 1e-3), "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x mxfp4_e2m1 -> f32", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_per_rank": tokens, "global_tokens": total_tokens,
+                       "hidden": cfg.hidden, "intermediate": cfg.intermediate, "experts": cfg.experts, "k": cfg.total_k,
+                       "experts_per_rank": cfg.experts // world,
+                       "parallelism": f"ep{world}: experts sharded by contiguous range, tokens data-parallel, "
+                                      "NCCL all-to-all dispatch and combine",
+                       "l2": "256 MB buffer rewritten between timed steps"},
+            "clocks": clocks,
+            "e2e": {"value": total_tokens / (statistics.mean(e2e) * 1e-3), "unit": unit,
+                    "h2d_bytes_per_step": tokens * cfg.hidden * 2, "d2h_bytes_per_step": tokens * cfg.hidden * 2,
+                    "ms_per_step": statistics.mean(e2e)},
+            "gpu_launches": int(layer.home.launches() + layer.work.launches()),
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()

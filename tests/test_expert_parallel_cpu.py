@@ -1,0 +1,165 @@
+"""The expert-parallel exchange protocol over gloo, world size 2, on CPU.
+
+The protocol code (split sizes, the three all-to-alls, the return order) is the product's
+``nerve_b200.expert_parallel.exchange``; the per-rank operators are CPU stand-ins built from the
+checker, so the test pins the host logic: sharded execution must reproduce the unsharded layer
+bit for bit, a bad owner table is rejected, and an undersized receive buffer is an error rather
+than a hang.
+"""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from nerve_b200 import expert_parallel as ep  # noqa: E402
+from nerve_b200 import synthetic  # noqa: E402
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class CpuOps:
+    """Stand-ins for the CUDA operators: same buffer contracts, numpy + the CPU checker."""
+
+    def __init__(self, cfg, case, rank, world, tokens, capacity):
+        import torch
+
+        from oracle import moe_oracle as mo
+
+        self.torch, self.mo = torch, mo
+        self.cfg, self.rank, self.world, self.T = cfg, rank, world, tokens
+        self.hidden = np.ascontiguousarray(case.hidden[rank * tokens:(rank + 1) * tokens])
+        self.case = case
+        self.owner = ep.contiguous_owner_table(cfg.total_experts, cfg.experts, world)
+        self.capacity = capacity
+        self.output = None
+
+    def route(self):
+        mo, cfg = self.mo, self.cfg
+        logits = mo.linear_bf16(self.hidden, self.case.router_w, self.case.router_bias)
+        self.routes, bad = mo.route(mo.router_params_from(cfg), logits, self.case.select_bias)
+        assert bad == 0
+
+    def pack(self):
+        torch = self.torch
+        K = self.cfg.total_k
+        flat = self.routes.reshape(-1)
+        dest = self.owner[flat & 0xFFFF].astype(np.int64)
+        dest[dest == ep.UNOWNED] = self.rank
+        order = np.argsort(dest, kind="stable")  # stable by owner rank, source order within
+        self.send_index = np.empty_like(order)
+        self.send_index[order] = np.arange(order.size)
+        rows = self.hidden[order // K]
+        counts = np.bincount(dest, minlength=self.world).astype(np.int32)
+        return (torch.from_numpy(rows.view(np.int16).copy()), torch.from_numpy(flat[order].view(np.int32).copy()),
+                torch.from_numpy(counts))
+
+    def compute(self, recv_rows, recv_routes, n):
+        mo, cfg, torch = self.mo, self.cfg, self.torch
+        out = np.zeros((max(n, 1), cfg.hidden), dtype=np.uint16)
+        if n == 0:
+            return torch.from_numpy(out.view(np.int16))
+        rows = recv_rows[:n].numpy().view(np.uint16)
+        routes = recv_routes[:n].numpy().view(np.uint32).reshape(n, 1)
+        p = mo.ExpertParams(cfg.hidden, cfg.intermediate, cfg.total_experts, 1, swiglu_limit=cfg.swiglu_limit,
+                            swiglu_alpha=cfg.swiglu_alpha, swiglu_up_offset=cfg.swiglu_up_offset,
+                            act_block=cfg.act_block, tier=1)
+        weights = mo.ExpertWeights(self.case.w1, self.case.s1, self.case.w3, self.case.s3, self.case.w2, self.case.s2)
+        mine = ep.owned_experts(self.owner, self.rank)
+        ga, gs = weights.gate_up_tables(mine)
+        da, ds = weights.down_tables(mine)
+        inter = np.zeros((n, p.frame_words), dtype=np.uint32)
+        control = np.array([n, 0, 0, 0, 0, 0, 0], dtype=np.uint32)
+        mo.route_compact(routes, inter, control, cfg.intermediate, 1, -(-cfg.intermediate // 32), slots=gs)
+        mo.gate_up(p, rows, routes, inter, ga, gs, control)
+        dc = np.array([n, 0, 0, 0, 0, 0, 0], dtype=np.uint32)
+        mo.route_count(routes, dc, 1, -(-cfg.hidden // 64), slots=ds)
+        outs = np.zeros((n, 1, cfg.hidden), dtype=np.uint16)
+        mo.down(p, inter, routes, outs, da, ds, dc)
+        out[:n] = outs[:, 0]
+        return torch.from_numpy(out.view(np.int16))
+
+    def unpack_reduce(self, returned):
+        cfg = self.cfg
+        rows = returned.numpy().view(np.uint16)
+        expert_outputs = rows[self.send_index].reshape(self.T, cfg.total_k, cfg.hidden)
+        self.output = self.mo.reduce(expert_outputs, self.T, cfg.total_k, cfg.hidden, 1.0)
+
+
+def _worker(rank, world, port, cfg_name, small, tokens, mode, result_dir):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = synthetic.small_variant(synthetic.CONFIGS[cfg_name], *small)
+        case = synthetic.make_case(cfg, tokens * world, seed=1)
+        capacity = 1 if mode == "undersized" else tokens * cfg.total_k * world
+        backend = CpuOps(cfg, case, rank, world, tokens, capacity)
+        ops = ep.ExchangeOps(backend.route, backend.pack, backend.compute, backend.unpack_reduce, capacity)
+        if mode == "undersized":
+            try:
+                ep.exchange(ops, dist)
+            except RuntimeError as error:
+                np.save(Path(result_dir) / f"err{rank}.npy", np.array([1]))
+                assert "receive buffers hold" in str(error)
+            return
+        sent, received = ep.exchange(ops, dist)
+        np.save(Path(result_dir) / f"out{rank}.npy", backend.output)
+        np.save(Path(result_dir) / f"counts{rank}.npy", np.array([sent, received]))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(cfg_name, small, tokens, mode, tmp_path):
+    import torch.multiprocessing as mp
+
+    mp.spawn(_worker, args=(2, _free_port(), cfg_name, small, tokens, mode, str(tmp_path)), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("cfg_name,small", [("gpt-oss-120b", (64, 96, 8)), ("deepseek-v3", (128, 128, 16))])
+def test_sharded_layer_equals_unsharded_layer(tmp_path, cfg_name, small):
+    pytest.importorskip("torch")
+    from oracle import moe_oracle as mo
+    from tests.helpers import oracle_layer
+
+    tokens = 6
+    _spawn(cfg_name, small, tokens, "run", tmp_path)
+    cfg = synthetic.small_variant(synthetic.CONFIGS[cfg_name], *small)
+    case = synthetic.make_case(cfg, tokens * 2, seed=1)
+    want = oracle_layer(case, tier=1)["output"]
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(2)])
+    np.testing.assert_array_equal(got, want)
+    counts = [np.load(tmp_path / f"counts{r}.npy") for r in range(2)]
+    assert sum(c[0] for c in counts) == sum(c[1] for c in counts) == tokens * 2 * cfg.total_k
+    assert mo.lib() is not None
+
+
+def test_undersized_receive_buffer_is_an_error_not_a_hang(tmp_path):
+    pytest.importorskip("torch")
+    _spawn("gpt-oss-120b", (64, 96, 8), 6, "undersized", tmp_path)
+    assert (tmp_path / "err0.npy").exists() or (tmp_path / "err1.npy").exists()
+
+
+def test_owner_tables():
+    table = ep.contiguous_owner_table(257, 256, 8)
+    assert table[0] == 0 and table[31] == 0 and table[32] == 1 and table[255] == 7 and table[256] == ep.UNOWNED
+    assert ep.owned_experts(table, 3) == list(range(96, 128)) + [256]
+    ep.validate_owner_table(table, 256, 8)
+    with pytest.raises(ValueError):
+        ep.contiguous_owner_table(32, 30, 4)
+    bad = table.copy()
+    bad[5] = 9
+    with pytest.raises(ValueError):
+        ep.validate_owner_table(bad, 256, 8)

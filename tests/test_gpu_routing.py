@@ -1,6 +1,8 @@
 """GPU parity of the integer-exact part of the path: router projection, the three router forms,
 route scheduling and activation quantisation — all bit-exact against the CPU checker, through the
 C ABI."""
+import zlib
+
 import numpy as np
 import pytest
 
@@ -33,7 +35,7 @@ def test_router_projection_is_bit_exact(device, tokens, hidden, experts, bias):
     w = synthetic.f32_to_bf16(0.02 * rng.standard_normal((experts, hidden), dtype=np.float32))
     b = synthetic.f32_to_bf16(0.1 * rng.standard_normal(experts).astype(np.float32)) if bias else None
     want = mo.linear_bf16(x, w, b)
-    plan = MoePlan(device, geometry_from_config(_cfg(experts, 1, hidden=hidden, intermediate=128), tokens))
+    plan = MoePlan(device, geometry_from_config(_cfg(experts, 1, hidden=hidden, intermediate=128, act_block=32), tokens))
     xb, wb = device.resident_buffer_from(x), device.resident_buffer_from(w)
     bb = device.resident_buffer_from(b) if bias else None
     lb = device.create_resident_buffer(want.nbytes)
@@ -70,7 +72,7 @@ ROUTER_CASES = [
 def test_routes_and_telemetry_are_bit_exact(device, case, tokens):
     cfg = _cfg(**case)
     rp = router_params(cfg)
-    rng = np.random.default_rng(hash(str(sorted(case.items()))) % (2 ** 31) + tokens)
+    rng = np.random.default_rng(zlib.crc32(str(sorted(case.items())).encode()) + tokens)
     # coarse logits give plenty of exact ties, which must go to the lower expert index
     logits_f = np.round(rng.standard_normal((tokens, cfg.experts)) * 4) / 4
     lw = np.zeros((tokens, (cfg.experts + 1) // 2 * 2), dtype=np.uint16)
