@@ -93,6 +93,7 @@ struct nvmoe_plan {
     // scratch every expert call needs
     DeviceArray status, gu_ptrs, down_ptrs, grouped[2], offsets[2], block_hist, bucket_base;
     DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list, ep_source;
+    DeviceArray derived[2], stamps[2];  // tiled scale copies for the tensor path and what they were built from
     // scratch of the fused layer call
     DeviceArray logits, routes, frames, expert_outputs, controls, hidden_dev, output_dev;
     void* pinned_in = nullptr;
@@ -413,6 +414,14 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
     want(p->i_scales, sizeof(float) * R * (I / g.act_block));
     want(p->i_e8m0, sizeof(uint32_t) * R * ((I + 127u) / 128u));
     want(p->tile_list, sizeof(uint32_t) * (R / 16u + p->experts + 1u) + 256u);
+    if (tc_shape_supported(g)) {
+        want(p->derived[0], (size_t)p->experts * 2u * tc_derived_scale_bytes(g.intermediate_size, g.hidden_size));
+        want(p->derived[1], (size_t)p->experts * tc_derived_scale_bytes(g.hidden_size, g.intermediate_size));
+        want(p->stamps[0], (size_t)p->experts * 2u * 16u);
+        want(p->stamps[1], (size_t)p->experts * 16u);
+        if (err == cudaSuccess) err = cudaMemsetAsync(p->stamps[0].ptr, 0, p->stamps[0].bytes, d->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(p->stamps[1].ptr, 0, p->stamps[1].bytes, d->stream);
+    }
     if (err == cudaSuccess) err = cudaMemsetAsync(p->status.ptr, 0, 256, d->stream);
     for (int i = 0; i <= kStageCount && err == cudaSuccess; i++) err = cudaEventCreate(&p->ev[i]);
     for (int i = 0; i < 4 && err == cudaSuccess; i++) err = cudaEventCreate(&p->kernel_ev[i / 2][i % 2]);
@@ -434,7 +443,8 @@ void nvmoe_plan_destroy(nvmoe_plan* p) {
     cudaStreamSynchronize(p->device->stream);
     DeviceArray* all[] = {&p->status, &p->gu_ptrs, &p->down_ptrs, &p->grouped[0], &p->grouped[1], &p->offsets[0],
                           &p->offsets[1], &p->block_hist, &p->bucket_base, &p->xq, &p->x_scales, &p->x_e8m0, &p->iq,
-                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
+                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->derived[0], &p->derived[1], &p->stamps[0],
+                          &p->stamps[1], &p->logits, &p->routes, &p->frames, &p->expert_outputs,
                           &p->controls, &p->hidden_dev, &p->output_dev};
     for (DeviceArray* a : all) a->release();
     if (p->pinned_in) cudaFreeHost(p->pinned_in);
@@ -589,7 +599,8 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
     const uint64_t cols = gate_up ? g.hidden_size : g.intermediate_size;
     launch_resolve_experts((const uint32_t*)addresses->ptr, (uint32_t)(addresses->bytes / 4u), (const uint32_t*)slots->ptr,
                            (uint32_t)(slots->bytes / 4u), gate_up ? 4u : 2u, p->experts, rows * (cols / 2u),
-                           rows * (cols / 32u), ptrs, st);
+                           rows * (cols / 32u), p->derived[set].as<uint8_t>(),
+                           tc_derived_scale_bytes((uint32_t)rows, (uint32_t)cols), ptrs, st);
     launch_group_slots(routes, intermediates, control, ptrs, p->experts, T, p->K, g.intermediate_size,
                        p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->status.as<uint32_t>(),
                        sort_scratch(p), st);
@@ -603,12 +614,17 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
     el.intermediates = intermediates;
     el.outputs = outputs;
     el.status = p->status.as<uint32_t>();
+    el.scale_stamps = p->stamps[set].as<uint64_t>();
     el.tile_count = p->tile_list.as<uint32_t>();  // first word; the list follows at a 256-byte offset
     el.tile_list = p->tile_list.as<uint32_t>() + 64;
     el.tokens = T;
     el.g = g;
     const bool tensor = allow_tensor_path && use_tensor_path(p);
-    if (tensor) launch_build_tiles_tc(el, st);
+    if (tensor) {
+        launch_derive_scales_tc(el, gate_up, st);
+        launch_build_tiles_tc(el, st);
+        p->launches += 3;
+    }
     if (p->profile_stages) cudaEventRecord(p->kernel_ev[set][0], st);
     if (tensor) {
         if (gate_up) {

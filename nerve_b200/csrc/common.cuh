@@ -21,8 +21,10 @@ constexpr uint32_t kSortChunk = 256u;    // routes per block in the multi-block 
 // runtime-rs/shaders/independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:120-228).
 // A null w pointer means "not resident": every route to that expert is skipped.
 struct ExpertPtrs {
-    const uint8_t* w[2];  // gate/up: w1, w3;  down: w2, unused
-    const uint8_t* s[2];  // matching E8M0 scale rows
+    const uint8_t* w[2];   // gate/up: w1, w3;  down: w2, unused
+    const uint8_t* s[2];   // matching E8M0 scale rows as packaged: [rows][cols/32]
+    const uint8_t* ts[2];  // derived copy of the scales, tiled for tcgen05.cp: [row tile][K block][512 bytes]
+    uint64_t gen[2];       // generation word of the scale records (what the derived copy is keyed on)
 };
 
 // Everything a grouped expert kernel needs to find its work, produced by group_slots().
@@ -87,8 +89,8 @@ void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t 
 // validates the address/slot tables of every expert once per call
 void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                             uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
-                            uint64_t weight_bytes, uint64_t scale_bytes, ExpertPtrs* out,
-                            cudaStream_t stream);
+                            uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
+                            size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream);
 // groups the compact slots the expert shaders would visit by expert (stable), skipping what the
 // shaders skip; writes grouped_routes and expert_offsets
 void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,
@@ -129,6 +131,7 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     uint32_t* intermediates;     // gate/up output frames
     uint16_t* outputs;           // down output [T][K][H]
     uint32_t* status;
+    uint64_t* scale_stamps;      // tensor path: {scale pointer, generation} the derived tiles were built from
     uint32_t* tile_list;         // tensor path scratch: routes / 16 + experts + 1 words
     uint32_t* tile_count;        // tensor path scratch: one word
     uint32_t tokens;             // upper bound (max over what control may hold)

@@ -15,13 +15,14 @@
 // a handful of tokens per expert still fills an MMA (N = 16), and every weight byte is read once.
 // One CTA per SM walks a list of (expert, token tile) x weight-row tiles.
 //
-// Roles (320 threads): warps 0-3 epilogue (TMEM lane quadrant = warp), warp 4 allocates TMEM and
+// Roles (288 threads): warps 0-3 epilogue (TMEM lane quadrant = warp), warp 4 allocates TMEM and
 // one of its lanes issues the scale copies and MMAs, warps 5-8 stage operands into shared memory
-// with cp.async whose completion arrives on the stage's mbarrier without stalling the issuer, and
-// warp 9 moves the scale bytes.  E2M1 codes travel as 8-byte pieces into the low half of 16-byte
-// slots (the padded 4-bit format the f8f6f4 kinds read), rows are gathered through the
-// expert-grouped route list, and E8M0 scales are laid out in the 32x16-byte blocks tcgen05.cp
-// expands into TMEM.  Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
+// with cp.async whose completion arrives on the stage's mbarrier without stalling the issuer.
+// E2M1 codes travel as 8-byte pieces into the low half of 16-byte slots (the padded 4-bit format
+// the f8f6f4 kinds read), rows are gathered through the expert-grouped route list, and E8M0 scales
+// come as ready 32x16-byte blocks (the layout tcgen05.cp expands into TMEM) from a derived copy of
+// the packaged scale tensors that is rebuilt whenever a scale record's address or generation
+// changes.  Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
 #include "experts_tc.cuh"
 #include "tcgen05.cuh"
 
@@ -34,12 +35,11 @@ constexpr uint32_t kBlockM = 128u;   // weight rows per tile
 constexpr uint32_t kBlockK = 128u;   // K elements per pipeline stage = 4 MMAs of K = 32
 constexpr uint32_t kProducerThreads = 128u;
 constexpr uint32_t kEpilogueThreads = 128u;
-constexpr uint32_t kThreads = 320u;
+constexpr uint32_t kThreads = 288u;
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
 constexpr uint32_t kSmemBudget = 215u * 1024u;
 constexpr uint32_t kMaxStages = 8u;
-constexpr uint32_t kSfPrefetch = 2u;               // stages of scale loads the scale warp keeps in registers
 
 struct TileList {
     const uint32_t* tiles;   // (expert << 16) | token tile within the expert
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
     // ---- one-time setup ---------------------------------------------------------------------
     if (threadIdx.x == 0u) {
         for (uint32_t s = 0; s < C::kStages; s++) {
-            mbar_init(&bars->full[s], kProducerThreads + 32u);  // 128 copy threads + the scale warp
+            mbar_init(&bars->full[s], kProducerThreads);
             mbar_init(&bars->empty[s], 1u);
         }
         for (uint32_t a = 0; a < 2u; a++) {
@@ -145,6 +145,11 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
                 const uint32_t ri = n < valid ? __ldg(p.work.grouped_routes + first + n) : 0u;
                 code_rows[i] = GATE_UP ? ri / K : ri;
             }
+            uint32_t scale_row = 0u;  // activation row whose scale word this thread gathers
+            if (pt < valid) {
+                const uint32_t ri = __ldg(p.work.grouped_routes + first + pt);
+                scale_row = GATE_UP ? ri / K : ri;
+            }
             const uint32_t row0 = m_tile * kBlockM;
             for (uint32_t kb = 0; kb < k_blocks; kb++, it++) {
                 const uint32_t slot = it % C::kStages;
@@ -176,95 +181,25 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
                     const uint8_t* src = ok ? p.act_q + (size_t)code_rows[i] * k_dim + kb * kBlockK + c * 16u : p.act_q;
                     cp_async_16(b_base + swizzle128_offset(n, c), src, ok ? 16u : 0u);
                 }
+                // scales: the derived copy already has the 32x16-byte layout tcgen05.cp reads, one 512-byte
+                // block per (row tile, K block); token scales are gathered four bytes (one K block) a row
+                unsigned char* sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
+                if (pt < 32u * C::kMatrices) {
+                    const uint32_t mx = pt >> 5, l = pt & 31u;
+                    const uint8_t* src = ptrs.ts[mx] + ((size_t)m_tile * k_blocks + kb) * kScaleBlockBytes + l * 16u;
+                    cp_async_16(smem_u32(sf + mx * kScaleBlockBytes + l * 16u), src, 16u);
+                }
+                if (pt < N_TILE) {
+                    const bool ok = pt < valid;
+                    const uint32_t* src = ok ? p.act_e8m0 + (size_t)scale_row * k_blocks + kb : p.act_e8m0;
+                    cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + (pt & 31u) * 16u + (pt >> 5) * 4u), src,
+                               ok ? 4u : 0u);
+                }
                 // the arrival fires when this thread's copies have landed; the thread moves on at once
                 cp_async_arrive_noinc(&bars->full[slot]);
             }
         }
         cp_async_wait_all();  // nothing of this thread may still be landing when the CTA retires
-    } else if (warp == 9u) {
-        // ===== scale producer: E8M0 bytes through registers into the 32x16-byte scale blocks ==========
-        // Weight scale rows are only 2-byte aligned (K/32 bytes per row), so they go through registers;
-        // lane l serves rows l, l+32, l+64, l+96 of the tile, loads run kSfPrefetch stages ahead.
-        uint32_t it = 0u;
-        bool alive = true;
-        const uint32_t scale_row_bytes = k_dim / 32u;
-        for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
-            const uint32_t pair = list.tiles[tile / m_tiles];
-            const uint32_t m_tile = tile % m_tiles;
-            const uint32_t expert = pair >> 16, n_tile = pair & 0xffffu;
-            const uint32_t e_begin = p.work.expert_offsets[expert], e_end = p.work.expert_offsets[expert + 1u];
-            const uint32_t first = e_begin + n_tile * N_TILE;
-            const uint32_t valid = min(N_TILE, e_end - first);
-            const ExpertPtrs ptrs = p.work.experts[expert];
-            const uint32_t row0 = m_tile * kBlockM;
-            constexpr uint32_t kTokenGroups = (N_TILE + 31u) / 32u;
-            uint32_t token_rows[kTokenGroups];
-#pragma unroll
-            for (uint32_t q = 0; q < kTokenGroups; q++) {
-                const uint32_t n = lane + 32u * q;
-                const uint32_t ri = n < valid ? __ldg(p.work.grouped_routes + first + n) : kUnboundSlot;
-                token_rows[q] = ri == kUnboundSlot ? kUnboundSlot : (GATE_UP ? ri / K : ri);
-            }
-            uint32_t wreg[kSfPrefetch][C::kMatrices][4];
-            uint32_t treg[kSfPrefetch][kTokenGroups];
-            auto load = [&](uint32_t kb, uint32_t (&w)[C::kMatrices][4], uint32_t (&t)[kTokenGroups]) {
-                const uint32_t have = kb < k_blocks ? min(4u, scale_row_bytes - kb * 4u) : 0u;
-#pragma unroll
-                for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
-#pragma unroll
-                    for (uint32_t q = 0; q < 4u; q++) {
-                        const uint32_t row = row0 + lane + 32u * q;
-                        uint32_t word = 0x7f7f7f7fu;
-                        if (have != 0u && row < out_rows) {
-                            const uint8_t* src = ptrs.s[mx] + (size_t)row * scale_row_bytes + kb * 4u;
-                            if ((scale_row_bytes & 1u) == 0u) {
-                                // even row length: every group of four starts on a 2-byte boundary
-                                const uint16_t* src16 = reinterpret_cast<const uint16_t*>(src);
-                                const uint32_t lo = __ldg(src16);
-                                const uint32_t hi = have > 2u ? __ldg(src16 + 1) : 0x7f7fu;
-                                word = lo | (hi << 16);
-                            } else {
-                                word = 0u;
-#pragma unroll
-                                for (uint32_t j = 0; j < 4u; j++) word |= (uint32_t)(j < have ? __ldg(src + j) : 127u) << (8u * j);
-                            }
-                        }
-                        w[mx][q] = word;
-                    }
-                }
-#pragma unroll
-                for (uint32_t q = 0; q < kTokenGroups; q++)
-                    t[q] = (kb < k_blocks && token_rows[q] != kUnboundSlot) ? __ldg(p.act_e8m0 + (size_t)token_rows[q] * k_blocks + kb) : 0u;
-            };
-#pragma unroll
-            for (uint32_t f = 0; f < kSfPrefetch; f++) load(f, wreg[f], treg[f]);
-            for (uint32_t kb0 = 0; kb0 < k_blocks && alive; kb0 += kSfPrefetch) {
-#pragma unroll
-                for (uint32_t f = 0; f < kSfPrefetch; f++) {
-                    const uint32_t kb = kb0 + f;
-                    if (kb >= k_blocks) break;
-                    const uint32_t slot = it % C::kStages;
-                    if (!mbar_wait(&bars->empty[slot], ((it / C::kStages) & 1u) ^ 1u, abort_flag)) {
-                        alive = false;
-                        break;
-                    }
-                    unsigned char* sf = smem + slot * C::kStageBytes + C::kMatrices * kATileBytes + C::kBTileBytes;
-                    // row r of a block sits at (r % 32) * 16 + (r / 32) * 4: lane l owns one 16-byte line
-#pragma unroll
-                    for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                        *reinterpret_cast<uint4*>(sf + mx * kScaleBlockBytes + lane * 16u) =
-                            make_uint4(wreg[f][mx][0], wreg[f][mx][1], wreg[f][mx][2], wreg[f][mx][3]);
-                    uint32_t t4[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                    for (uint32_t q = 0; q < kTokenGroups; q++) t4[q] = treg[f][q];
-                    *reinterpret_cast<uint4*>(sf + C::kMatrices * kScaleBlockBytes + lane * 16u) = make_uint4(t4[0], t4[1], t4[2], t4[3]);
-                    fence_proxy_async();  // this warp has no copies in flight: the fence is cheap
-                    mbar_arrive(&bars->full[slot]);
-                    it++;
-                    load(kb + kSfPrefetch, wreg[f], treg[f]);
-                }
-            }
-        }
     } else if (warp == 4u) {
         // ===== MMA issue (one elected lane) ======================================================
         if (elect_one()) {
@@ -406,6 +341,44 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const uint32_t* exper
     if (threadIdx.x == 0u) *count = carry;
 }
 
+// Re-tiles the packaged [rows][cols/32] scale bytes of one expert matrix into 512-byte blocks, one
+// per (128-row tile, 128-column block): row r of the tile sits at (r % 32) * 16 + (r / 32) * 4 and
+// holds the four scales of the block; positions past the matrix edge hold 127 (1.0) and are never
+// multiplied with anything but zeros.  A block re-tiles only when the stamp differs.
+__global__ void __launch_bounds__(128) derive_scales_kernel(const ExpertPtrs* experts, const uint64_t* stamps,
+                                                           uint32_t matrices, uint32_t rows, uint32_t cols) {
+    const uint32_t m_tiles = (rows + kBlockM - 1u) / kBlockM, k_blocks = (cols + kBlockK - 1u) / kBlockK;
+    const uint32_t e = blockIdx.x / (matrices * m_tiles);
+    const uint32_t mx = (blockIdx.x / m_tiles) % matrices, m_tile = blockIdx.x % m_tiles;
+    const ExpertPtrs ptrs = experts[e];
+    if (ptrs.w[0] == nullptr || ptrs.ts[mx] == nullptr) return;
+    const uint64_t* stamp = stamps + ((size_t)e * matrices + mx) * 2u;
+    if (stamp[0] == (uint64_t)(uintptr_t)ptrs.s[mx] && stamp[1] == ptrs.gen[mx]) return;
+    const uint32_t r = threadIdx.x, row = m_tile * kBlockM + r, row_bytes = cols / 32u;
+    uint8_t* out = const_cast<uint8_t*>(ptrs.ts[mx]) + (size_t)m_tile * k_blocks * kScaleBlockBytes + (r & 31u) * 16u + (r >> 5) * 4u;
+    for (uint32_t kb = 0; kb < k_blocks; kb++) {
+        uint32_t word = 0x7f7f7f7fu;
+        if (row < rows) {
+            word = 0u;
+            for (uint32_t j = 0; j < 4u; j++) {
+                const uint32_t c = kb * 4u + j;
+                word |= (uint32_t)(c < row_bytes ? ptrs.s[mx][(size_t)row * row_bytes + c] : 127u) << (8u * j);
+            }
+        }
+        *reinterpret_cast<uint32_t*>(out + (size_t)kb * kScaleBlockBytes) = word;
+    }
+}
+
+__global__ void commit_stamps_kernel(const ExpertPtrs* experts, uint64_t* stamps, uint32_t matrices, uint32_t count) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const ExpertPtrs ptrs = experts[i / matrices];
+    const uint32_t mx = i % matrices;
+    if (ptrs.w[0] == nullptr) return;
+    stamps[(size_t)i * 2u] = (uint64_t)(uintptr_t)ptrs.s[mx];
+    stamps[(size_t)i * 2u + 1u] = ptrs.gen[mx];
+}
+
 int g_sm_count[16] = {0};
 
 template <bool GATE_UP, uint32_t N_TILE>
@@ -447,6 +420,21 @@ uint32_t tc_token_tile(const ExpertLaunch& p) {
     const uint32_t routes = p.tokens * (p.g.routed_k + p.g.always_count);
     const uint32_t per_expert = (routes + p.work.num_experts - 1u) / p.work.num_experts;
     return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : 128u;
+}
+
+size_t tc_derived_scale_bytes(uint32_t rows, uint32_t cols) {
+    return (size_t)((rows + kBlockM - 1u) / kBlockM) * ((cols + kBlockK - 1u) / kBlockK) * kScaleBlockBytes;
+}
+
+void launch_derive_scales_tc(const ExpertLaunch& p, bool gate_up, cudaStream_t stream) {
+    const uint32_t matrices = gate_up ? 2u : 1u;
+    const uint32_t rows = gate_up ? p.g.intermediate_size : p.g.hidden_size;
+    const uint32_t cols = gate_up ? p.g.hidden_size : p.g.intermediate_size;
+    const uint32_t m_tiles = (rows + kBlockM - 1u) / kBlockM;
+    derive_scales_kernel<<<p.work.num_experts * matrices * m_tiles, 128, 0, stream>>>(p.work.experts, p.scale_stamps,
+                                                                                      matrices, rows, cols);
+    const uint32_t count = p.work.num_experts * matrices;
+    commit_stamps_kernel<<<(count + 127u) / 128u, 128, 0, stream>>>(p.work.experts, p.scale_stamps, matrices, count);
 }
 
 void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream) {

@@ -13,6 +13,10 @@ void tc_configure_kernels();
 // token tile size for this call, and the (expert, token tile) list the kernels walk
 uint32_t tc_token_tile(const ExpertLaunch& p);
 void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream);
+// bytes of the derived (tiled) scale copy of one expert matrix with `rows` x `cols` elements
+size_t tc_derived_scale_bytes(uint32_t rows, uint32_t cols);
+// re-tiles the scales of every expert whose scale record changed since the last call
+void launch_derive_scales_tc(const ExpertLaunch& p, bool gate_up, cudaStream_t stream);
 void launch_gate_up_tc(const ExpertLaunch& p, cudaStream_t stream);
 void launch_down_tc(const ExpertLaunch& p, cudaStream_t stream);
 

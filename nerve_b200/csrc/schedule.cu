@@ -342,12 +342,14 @@ __global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* route
 // address_record_is_resident + dynamic_parameter_record_is_valid for every expert, once per call
 __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                                        uint32_t slot_words, uint32_t params, uint32_t num_experts,
-                                       uint64_t weight_bytes, uint64_t scale_bytes, ExpertPtrs* out) {
+                                       uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
+                                       size_t derived_matrix_bytes, ExpertPtrs* out) {
     uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= num_experts) return;
-    ExpertPtrs r{{nullptr, nullptr}, {nullptr, nullptr}};
+    ExpertPtrs r{{nullptr, nullptr}, {nullptr, nullptr}, {nullptr, nullptr}, {0u, 0u}};
     bool ok = true;
     const uint8_t* ptrs[4] = {nullptr, nullptr, nullptr, nullptr};
+    uint64_t gens[4] = {0u, 0u, 0u, 0u};
     for (uint32_t j = 0; j < params && ok; j++) {
         uint64_t index = (uint64_t)e * params + j;
         if (index >= slot_words) {
@@ -371,12 +373,20 @@ __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t addre
             break;
         }
         ptrs[j] = reinterpret_cast<const uint8_t*>(address);
+        gens[j] = (uint64_t)rec[4] | ((uint64_t)rec[5] << 32);
     }
     if (ok) {
+        const uint32_t matrices = params / 2u;
         r.w[0] = ptrs[0];
         r.s[0] = ptrs[1];
+        r.gen[0] = gens[1];
         r.w[1] = params == 4u ? ptrs[2] : nullptr;
         r.s[1] = params == 4u ? ptrs[3] : nullptr;
+        r.gen[1] = params == 4u ? gens[3] : 0u;
+        if (derived_scales) {
+            r.ts[0] = derived_scales + ((size_t)e * matrices) * derived_matrix_bytes;
+            r.ts[1] = params == 4u ? r.ts[0] + derived_matrix_bytes : nullptr;
+        }
     }
     out[e] = r;
 }
@@ -570,11 +580,11 @@ void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t 
 
 void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                             uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
-                            uint64_t weight_bytes, uint64_t scale_bytes, ExpertPtrs* out,
-                            cudaStream_t stream) {
+                            uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
+                            size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream) {
     resolve_experts_kernel<<<(num_experts + 127u) / 128u, 128, 0, stream>>>(
         addresses, address_words, slots, slot_words, params_per_resource, num_experts, weight_bytes,
-        scale_bytes, out);
+        scale_bytes, derived_scales, derived_matrix_bytes, out);
 }
 
 void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,
