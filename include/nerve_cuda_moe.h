@@ -286,6 +286,11 @@ typedef struct nvmoe_work_report {
     uint64_t weight_bytes_touched;
 } nvmoe_work_report;
 int nvmoe_plan_last_report(nvmoe_plan* plan, nvmoe_work_report* report);
+/* Diagnostics of the last tensor-core expert kernels: cycle counters of CTA 0, eight words for
+ * gate/up then eight for down: {producer wait, producer total, MMA wait-operands, MMA
+ * wait-accumulator, MMA total, stages, epilogue wait, epilogue total}. Synchronises the stream.
+ * No reference counterpart. */
+int nvmoe_plan_debug_counters(nvmoe_plan* plan, uint64_t* out16);
 /* Kernels launched through this plan since it was created. */
 uint64_t nvmoe_plan_launch_count(const nvmoe_plan* plan);
 

@@ -94,6 +94,8 @@ struct nvmoe_plan {
     DeviceArray status, gu_ptrs, down_ptrs, grouped[2], offsets[2], block_hist, bucket_base;
     DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list, ep_source;
     DeviceArray derived[2], stamps[2];  // tiled scale copies for the tensor path and what they were built from
+    DeviceArray tmap_templates, tmaps[2];  // tensor maps of the weight matrices: one template per stage, one map per expert matrix
+    bool tma[2] = {false, false};
     // scratch of the fused layer call
     DeviceArray logits, routes, frames, expert_outputs, controls, hidden_dev, output_dev;
     void* pinned_in = nullptr;
@@ -421,6 +423,16 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
         want(p->stamps[1], (size_t)p->experts * 16u);
         if (err == cudaSuccess) err = cudaMemsetAsync(p->stamps[0].ptr, 0, p->stamps[0].bytes, d->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(p->stamps[1].ptr, 0, p->stamps[1].bytes, d->stream);
+        want(p->tmap_templates, 256);
+        want(p->tmaps[0], (size_t)p->experts * 2u * 128u);
+        want(p->tmaps[1], (size_t)p->experts * 128u);
+        if (err == cudaSuccess) {
+            unsigned char maps[256];
+            p->tma[0] = tc_encode_weight_map(maps, p->tmaps[0].ptr, g.intermediate_size, g.hidden_size);
+            p->tma[1] = tc_encode_weight_map(maps + 128, p->tmaps[1].ptr, g.hidden_size, g.intermediate_size);
+            err = cudaMemcpyAsync(p->tmap_templates.ptr, maps, 256, cudaMemcpyHostToDevice, d->stream);
+            if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer
+        }
     }
     if (err == cudaSuccess) err = cudaMemsetAsync(p->status.ptr, 0, 256, d->stream);
     for (int i = 0; i <= kStageCount && err == cudaSuccess; i++) err = cudaEventCreate(&p->ev[i]);
@@ -444,7 +456,7 @@ void nvmoe_plan_destroy(nvmoe_plan* p) {
     DeviceArray* all[] = {&p->status, &p->gu_ptrs, &p->down_ptrs, &p->grouped[0], &p->grouped[1], &p->offsets[0],
                           &p->offsets[1], &p->block_hist, &p->bucket_base, &p->xq, &p->x_scales, &p->x_e8m0, &p->iq,
                           &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->derived[0], &p->derived[1], &p->stamps[0],
-                          &p->stamps[1], &p->logits, &p->routes, &p->frames, &p->expert_outputs,
+                          &p->stamps[1], &p->tmap_templates, &p->tmaps[0], &p->tmaps[1], &p->logits, &p->routes, &p->frames, &p->expert_outputs,
                           &p->controls, &p->hidden_dev, &p->output_dev};
     for (DeviceArray* a : all) a->release();
     if (p->pinned_in) cudaFreeHost(p->pinned_in);
@@ -615,6 +627,7 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
     el.outputs = outputs;
     el.status = p->status.as<uint32_t>();
     el.scale_stamps = p->stamps[set].as<uint64_t>();
+    el.tmaps = p->tma[set] ? p->tmaps[set].as<uint8_t>() : nullptr;
     el.tile_count = p->tile_list.as<uint32_t>();  // first word; the list follows at a 256-byte offset
     el.tile_list = p->tile_list.as<uint32_t>() + 64;
     el.tokens = T;
@@ -622,6 +635,10 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
     const bool tensor = allow_tensor_path && use_tensor_path(p);
     if (tensor) {
         launch_derive_scales_tc(el, gate_up, st);
+        if (el.tmaps) {
+            launch_build_tensormaps_tc(el, gate_up, p->tmap_templates.as<uint8_t>() + set * 128, st);
+            p->launches++;
+        }
         launch_build_tiles_tc(el, st);
         p->launches += 3;
     }
@@ -907,6 +924,16 @@ int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hi
 }
 
 uint64_t nvmoe_plan_launch_count(const nvmoe_plan* p) { return p ? p->launches : 0u; }
+
+int nvmoe_plan_debug_counters(nvmoe_plan* p, uint64_t* out16) {
+    uint64_t* out8 = out16;
+    if (!p || !out8) return NVMOE_ERR_INVALID_ARGUMENT;
+    nvmoe_device* d = p->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
+    NVMOE_CUDA(d, cudaMemcpy(out8, p->tile_list.as<uint32_t>() + 16, 128, cudaMemcpyDeviceToHost));
+    return NVMOE_OK;
+}
 
 int nvmoe_plan_last_report(nvmoe_plan* p, nvmoe_work_report* report) {
     if (!p || !report) return NVMOE_ERR_INVALID_ARGUMENT;

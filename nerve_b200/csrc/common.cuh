@@ -131,6 +131,7 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     uint32_t* intermediates;     // gate/up output frames
     uint16_t* outputs;           // down output [T][K][H]
     uint32_t* status;
+    const uint8_t* tmaps;        // tensor path: 128-byte tensor maps [expert][matrix], null = move weights with cp.async
     uint64_t* scale_stamps;      // tensor path: {scale pointer, generation} the derived tiles were built from
     uint32_t* tile_list;         // tensor path scratch: routes / 16 + experts + 1 words
     uint32_t* tile_count;        // tensor path scratch: one word

@@ -15,14 +15,22 @@
 // a handful of tokens per expert still fills an MMA (N = 16), and every weight byte is read once.
 // One CTA per SM walks a list of (expert, token tile) x weight-row tiles.
 //
-// Roles (288 threads): warps 0-3 epilogue (TMEM lane quadrant = warp), warp 4 allocates TMEM and
-// one of its lanes issues the scale copies and MMAs, warps 5-8 stage operands into shared memory
-// with cp.async whose completion arrives on the stage's mbarrier without stalling the issuer.
-// E2M1 codes travel as 8-byte pieces into the low half of 16-byte slots (the padded 4-bit format
-// the f8f6f4 kinds read), rows are gathered through the expert-grouped route list, and E8M0 scales
+// Roles: warps 0-3 epilogue (TMEM lane quadrant = warp); warp 4 allocates TMEM and one of its lanes
+// issues the scale copies and MMAs; one lane of warp 5 issues TMA loads of whole 128 x 128 boxes of
+// weight codes through a per-expert tensor map (the template map with the expert's address patched in
+// on the device; the padded 4-bit tensor-map type spreads the codes into the 16-byte slots the f8f6f4
+// kinds read and applies the 128-byte swizzle); warps 6.. stage the token rows, the scales and any
+// trailing partial K block with cp.async whose completion arrives on the stage's mbarrier without
+// stalling the issuer.  Shapes the tensor map cannot describe (K % 64 != 0) move the weights with
+// cp.async too: 8-byte pieces into the low half of the 16-byte slots.  Token rows are gathered
+// through the expert-grouped route list (the permutation costs no pass of its own), and E8M0 scales
 // come as ready 32x16-byte blocks (the layout tcgen05.cp expands into TMEM) from a derived copy of
 // the packaged scale tensors that is rebuilt whenever a scale record's address or generation
 // changes.  Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
+#include <cuda.h>
+
+#include <cstring>
+
 #include "experts_tc.cuh"
 #include "tcgen05.cuh"
 
@@ -33,9 +41,9 @@ using namespace tc;
 
 constexpr uint32_t kBlockM = 128u;   // weight rows per tile
 constexpr uint32_t kBlockK = 128u;   // K elements per pipeline stage = 4 MMAs of K = 32
-constexpr uint32_t kProducerThreads = 128u;
 constexpr uint32_t kEpilogueThreads = 128u;
-constexpr uint32_t kThreads = 288u;
+constexpr uint32_t kFirstProducerThread = 192u;    // warps 0-3 epilogue, 4 MMA, 5 TMA, 6.. cp.async
+constexpr uint32_t kTmaBoxBytes = kBlockM * 64u;   // global bytes of one 128 x 128 box of 4-bit codes
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
 constexpr uint32_t kSmemBudget = 215u * 1024u;
@@ -46,9 +54,15 @@ struct TileList {
     const uint32_t* count;   // number of entries
 };
 
-template <bool GATE_UP, uint32_t N_TILE>
+template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
 struct Config {
     static constexpr uint32_t kMatrices = GATE_UP ? 2u : 1u;
+    // cp.async producers: one warp sustains only about one copy instruction every 60-130 cycles, so the
+    // path that moves the weights with them takes eight warps; with TMA they only move tokens and scales
+    static constexpr uint32_t kProducerWarps = USE_TMA ? 4u : 8u;
+    static constexpr uint32_t kProducerThreads = 32u * kProducerWarps;
+    static constexpr uint32_t kRowsPerPass = kProducerThreads / 8u;  // eight threads cover the 128 bytes of one row
+    static constexpr uint32_t kThreads = kFirstProducerThread + kProducerThreads;
     static constexpr uint32_t kBTileBytes = N_TILE * 128u;
     // every stage starts on a 1024-byte boundary: the 128-byte swizzle is a function of the address
     static constexpr uint32_t kStageBytes =
@@ -75,9 +89,10 @@ struct Barriers {
     uint32_t abort;
 };
 
-template <bool GATE_UP, uint32_t N_TILE>
-__global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p, TileList list) {
-    using C = Config<GATE_UP, N_TILE>;
+template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
+__global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 1) experts_tc_kernel(ExpertLaunch p, TileList list) {
+    using C = Config<GATE_UP, N_TILE, USE_TMA>;
+    constexpr uint32_t kThreads = C::kThreads, kProducerThreads = C::kProducerThreads, kRowsPerPass = C::kRowsPerPass;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023u));
@@ -92,12 +107,14 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
     const uint32_t k_blocks = (k_dim + kBlockK - 1u) / kBlockK;
     const uint32_t m_tiles = (out_rows + kBlockM - 1u) / kBlockM;
     const uint32_t pair_count = *list.count;
+    // cycle counters of CTA 0, one writer per role (diagnostics; words 16.. of the tile-count block)
+    uint64_t* trace = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(list.count) + 16) + (GATE_UP ? 0 : 8);
     const uint32_t tile_count = pair_count * m_tiles;
 
     // ---- one-time setup ---------------------------------------------------------------------
     if (threadIdx.x == 0u) {
         for (uint32_t s = 0; s < C::kStages; s++) {
-            mbar_init(&bars->full[s], kProducerThreads);
+            mbar_init(&bars->full[s], kProducerThreads + (USE_TMA ? 1u : 0u));
             mbar_init(&bars->empty[s], 1u);
         }
         for (uint32_t a = 0; a < 2u; a++) {
@@ -123,133 +140,233 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_scales = tmem_base + C::kAccStages * C::kAccColumns;
 
-    if (warp >= 5u && warp <= 8u) {
-        // ===== operand producers: cp.async into the swizzled tiles, completion arrives on `full` =====
-        const uint32_t pt = threadIdx.x - 160u;  // 0..127
-        uint32_t it = 0u;
-        bool alive = true;
-        for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
-            const uint32_t pair = list.tiles[tile / m_tiles];
-            const uint32_t m_tile = tile % m_tiles;
-            const uint32_t expert = pair >> 16, n_tile = pair & 0xffffu;
-            const uint32_t e_begin = p.work.expert_offsets[expert], e_end = p.work.expert_offsets[expert + 1u];
-            const uint32_t first = e_begin + n_tile * N_TILE;
-            const uint32_t valid = min(N_TILE, e_end - first);
-            const ExpertPtrs ptrs = p.work.experts[expert];
-            // activation rows this thread gathers: token (pt / 8) + 16 i of the tile
-            // (gate/up reads the token's hidden row, down the route's own row)
-            uint32_t code_rows[N_TILE / 16u];
+    if (warp == 5u) {
+        // ===== TMA issue (one lane): whole 128 x 128 boxes of weight codes, padded and swizzled by the unit =====
+        if (USE_TMA && lane == 0u) {
+            uint32_t slot = 0u, empty_parity = 1u;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
+                const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
+                const int row0 = (int)((tile % m_tiles) * kBlockM);
+                const uint8_t* maps = p.tmaps + (size_t)(pair >> 16) * C::kMatrices * 128u;
 #pragma unroll
-            for (uint32_t i = 0; i < N_TILE / 16u; i++) {
-                const uint32_t n = (pt >> 3) + 16u * i;
-                const uint32_t ri = n < valid ? __ldg(p.work.grouped_routes + first + n) : 0u;
-                code_rows[i] = GATE_UP ? ri / K : ri;
+                for (uint32_t mx = 0; mx < C::kMatrices; mx++) tensormap_acquire(maps + mx * 128u);
+                for (uint32_t kb = 0; kb < k_blocks; kb++) {
+                    if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag)) {
+                        alive = false;
+                        break;
+                    }
+                    if ((kb + 1u) * kBlockK <= k_dim) {
+                        const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
+                        mbar_arrive_expect_tx(&bars->full[slot], C::kMatrices * kTmaBoxBytes);
+#pragma unroll
+                        for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+                            tma_load_3d(stage + mx * kATileBytes, maps + mx * 128u, 0, (int)kb, row0, &bars->full[slot]);
+                    } else {
+                        mbar_arrive(&bars->full[slot]);  // a partial K block is staged by the cp.async warps
+                    }
+                    if (++slot == C::kStages) {
+                        slot = 0u;
+                        empty_parity ^= 1u;
+                    }
+                }
             }
-            uint32_t scale_row = 0u;  // activation row whose scale word this thread gathers
-            if (pt < valid) {
-                const uint32_t ri = __ldg(p.work.grouped_routes + first + pt);
-                scale_row = GATE_UP ? ri / K : ri;
+        }
+    } else if (warp >= 6u) {
+        // ===== operand producers: cp.async into the swizzled tiles, completion arrives on `full` =====
+        const uint32_t pt = threadIdx.x - kFirstProducerThread;  // 0..kProducerThreads-1
+        const uint32_t my_r = pt >> 3, my_c = pt & 7u;  // this thread's row (plus kRowsPerPass i) and 16-element chunk
+        constexpr uint32_t kTokenPasses = (N_TILE + kRowsPerPass - 1u) / kRowsPerPass;
+        const uint32_t row_bytes = k_dim / 2u;
+        // What a thread needs to know about a tile; the next tile's copy is fetched while the current
+        // tile streams, so that the dependent loads (tile list -> offsets -> routes) never stall the pipe.
+        struct Meta {
+            const uint8_t* w[C::kMatrices];
+            const uint8_t* ts[C::kMatrices];
+            uint32_t code_rows[kTokenPasses];  // activation row of token my_r + kRowsPerPass i
+            uint32_t scale_row;                // activation row of token pt
+            uint32_t valid, m_tile;
+        };
+        auto load_meta = [&](uint32_t tile, Meta& m) {
+            const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
+            m.m_tile = tile % m_tiles;
+            const uint32_t expert = pair >> 16, n_tile = pair & 0xffffu;
+            const uint32_t e_begin = __ldg(p.work.expert_offsets + expert), e_end = __ldg(p.work.expert_offsets + expert + 1u);
+            const uint32_t first = e_begin + n_tile * N_TILE;
+            m.valid = min(N_TILE, e_end - first);
+            const ExpertPtrs* ptrs = p.work.experts + expert;
+#pragma unroll
+            for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
+                m.w[mx] = ptrs->w[mx];
+                m.ts[mx] = ptrs->ts[mx];
             }
-            const uint32_t row0 = m_tile * kBlockM;
+            // gate/up reads the token's hidden row, down the route's own row
+#pragma unroll
+            for (uint32_t i = 0; i < kTokenPasses; i++) {
+                const uint32_t n = my_r + kRowsPerPass * i;
+                const uint32_t ri = n < m.valid ? __ldg(p.work.grouped_routes + first + n) : 0u;
+                m.code_rows[i] = GATE_UP ? ri / K : ri;
+            }
+            const uint32_t ri = pt < m.valid ? __ldg(p.work.grouped_routes + first + pt) : 0u;
+            m.scale_row = GATE_UP ? ri / K : ri;
+        };
+        uint32_t it = 0u, slot = 0u, empty_parity = 1u;  // a fresh barrier passes a wait on parity 1
+        long long trace_wait = 0;
+        const long long trace_begin = clock64();
+        const uint32_t my_dst = swizzle128_offset(my_r, my_c);
+        bool alive = true;
+        Meta cur, nxt;
+        if (blockIdx.x < tile_count) load_meta(blockIdx.x, cur);
+        for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
+            if (tile + gridDim.x < tile_count) load_meta(tile + gridDim.x, nxt);
+            const uint32_t row0 = cur.m_tile * kBlockM;
+            const uint32_t rows_here = min(kBlockM, out_rows - row0);
+            // this thread's first weight row of the tile; its other rows are 16 rows apart
+            const uint8_t* wcol[C::kMatrices];
+#pragma unroll
+            for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+                wcol[mx] = cur.w[mx] + (size_t)(row0 + my_r) * row_bytes + my_c * 8u;
+            const size_t row_step = (size_t)kRowsPerPass * row_bytes;
             for (uint32_t kb = 0; kb < k_blocks; kb++, it++) {
-                const uint32_t slot = it % C::kStages;
-                if (!mbar_wait(&bars->empty[slot], ((it / C::kStages) & 1u) ^ 1u, abort_flag)) {
+                const long long w0 = clock64();
+                if (!mbar_wait_warp(&bars->empty[slot], empty_parity, abort_flag)) {
                     alive = false;
                     break;
                 }
+                trace_wait += clock64() - w0;
                 unsigned char* stage = smem + slot * C::kStageBytes;
                 const uint32_t k_left = k_dim - kb * kBlockK;  // elements of K from this block on
+                const bool chunk_ok = my_c * 16u < k_left;
                 // weights: 8-byte pieces of 16 codes into the low half of 16-byte slots
+                // (with TMA only the trailing partial K block comes this way)
+                if (!USE_TMA || k_left < kBlockK) {
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
-                    const uint32_t a_base = smem_u32(stage + mx * kATileBytes);
-                    const uint8_t* wbase = ptrs.w[mx];
+                    const uint32_t a_dst = smem_u32(stage + mx * kATileBytes) + my_dst;
+                    const uint8_t* src = wcol[mx] + kb * 64u;
 #pragma unroll
-                    for (uint32_t i = 0; i < 8u; i++) {
-                        const uint32_t r = (pt >> 3) + 16u * i, c = pt & 7u;
-                        const bool ok = (row0 + r < out_rows) && (c * 16u < k_left);
-                        const uint8_t* src = ok ? wbase + (size_t)(row0 + r) * (k_dim / 2u) + kb * 64u + c * 8u : wbase;
-                        cp_async_8(a_base + swizzle128_offset(r, c), src, ok ? 8u : 0u);
+                    for (uint32_t i = 0; i < kBlockM / kRowsPerPass; i++) {
+                        // rows my_r + kRowsPerPass i share (row & 7), so the swizzled offset only moves by whole rows
+                        const bool ok = chunk_ok && (my_r + kRowsPerPass * i < rows_here);
+                        cp_async_8(a_dst + i * (kRowsPerPass * 128u), ok ? src + i * row_step : cur.w[mx], ok ? 8u : 0u);
                     }
                 }
+                }
                 // activations: 16-byte pieces of 16 E4M3 codes, rows gathered through the route list
-                const uint32_t b_base = smem_u32(stage + C::kMatrices * kATileBytes);
+                const uint32_t b_dst = smem_u32(stage + C::kMatrices * kATileBytes) + my_dst;
 #pragma unroll
-                for (uint32_t i = 0; i < N_TILE / 16u; i++) {
-                    const uint32_t n = (pt >> 3) + 16u * i, c = pt & 7u;
-                    const bool ok = (n < valid) && (c * 16u < k_left);
-                    const uint8_t* src = ok ? p.act_q + (size_t)code_rows[i] * k_dim + kb * kBlockK + c * 16u : p.act_q;
-                    cp_async_16(b_base + swizzle128_offset(n, c), src, ok ? 16u : 0u);
+                for (uint32_t i = 0; i < kTokenPasses; i++) {
+                    const uint32_t n = my_r + kRowsPerPass * i;
+                    if (n < N_TILE) {
+                        const bool ok = chunk_ok && (n < cur.valid);
+                        const uint8_t* src = ok ? p.act_q + (size_t)cur.code_rows[i] * k_dim + kb * kBlockK + my_c * 16u : p.act_q;
+                        cp_async_16(b_dst + i * (kRowsPerPass * 128u), src, ok ? 16u : 0u);
+                    }
                 }
                 // scales: the derived copy already has the 32x16-byte layout tcgen05.cp reads, one 512-byte
                 // block per (row tile, K block); token scales are gathered four bytes (one K block) a row
                 unsigned char* sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
                 if (pt < 32u * C::kMatrices) {
                     const uint32_t mx = pt >> 5, l = pt & 31u;
-                    const uint8_t* src = ptrs.ts[mx] + ((size_t)m_tile * k_blocks + kb) * kScaleBlockBytes + l * 16u;
+                    const uint8_t* src = cur.ts[mx] + ((size_t)cur.m_tile * k_blocks + kb) * kScaleBlockBytes + l * 16u;
                     cp_async_16(smem_u32(sf + mx * kScaleBlockBytes + l * 16u), src, 16u);
                 }
                 if (pt < N_TILE) {
-                    const bool ok = pt < valid;
-                    const uint32_t* src = ok ? p.act_e8m0 + (size_t)scale_row * k_blocks + kb : p.act_e8m0;
+                    const bool ok = pt < cur.valid;
+                    const uint32_t* src = ok ? p.act_e8m0 + (size_t)cur.scale_row * k_blocks + kb : p.act_e8m0;
                     cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + (pt & 31u) * 16u + (pt >> 5) * 4u), src,
                                ok ? 4u : 0u);
                 }
                 // the arrival fires when this thread's copies have landed; the thread moves on at once
                 cp_async_arrive_noinc(&bars->full[slot]);
+                if (++slot == C::kStages) {
+                    slot = 0u;
+                    empty_parity ^= 1u;
+                }
             }
+            cur = nxt;
         }
         cp_async_wait_all();  // nothing of this thread may still be landing when the CTA retires
+        if (blockIdx.x == 0u && pt == 0u) {
+            trace[0] = (uint64_t)trace_wait;                    // producer: cycles waiting for a free stage
+            trace[1] = (uint64_t)(clock64() - trace_begin);     // producer: cycles in its loop
+        }
     } else if (warp == 4u) {
         // ===== MMA issue (one elected lane) ======================================================
         if (elect_one()) {
-            const uint32_t idesc = idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, kBlockM, N_TILE);
-            uint32_t it = 0u, acc_it = 0u;
+            // One thread feeds the tensor pipe, and a lone thread retires an instruction every few
+            // cycles at best: everything that does not depend on the stage is computed once, the four
+            // K steps of a stage are unrolled with compile-time descriptors offsets and scale ids.
+            constexpr uint32_t kIdesc = idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, kBlockM, N_TILE);
+            constexpr uint32_t kStageUnits = C::kStageBytes >> 4;  // descriptor start addresses count 16 bytes
+            const uint32_t base = smem_u32(smem);
+            const uint64_t a_desc0 = desc_k_major_sw128(base);
+            const uint64_t b_desc0 = desc_k_major_sw128(base + C::kMatrices * kATileBytes);
+            const uint64_t sf_desc0 = desc_scale_block(base + C::kMatrices * kATileBytes + C::kBTileBytes);
+            const uint32_t tail_groups = (k_dim % kBlockK) / 32u;  // K steps of a trailing partial block, 0 = none
+            const uint32_t sfb_tmem = tmem_scales + 4u * C::kMatrices;
+            uint32_t it = 0u, acc_it = 0u, slot = 0u, full_parity = 0u;
             bool alive = true;
+            long long trace_full = 0, trace_acc = 0;
+            const long long trace_begin = clock64();
             for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x, acc_it++) {
                 const uint32_t acc = acc_it % C::kAccStages;
+                const long long a0 = clock64();
                 if (!mbar_wait(&bars->acc_empty[acc], ((acc_it / C::kAccStages) & 1u) ^ 1u, abort_flag)) break;
+                trace_acc += clock64() - a0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccColumns;
                 for (uint32_t kb = 0; kb < k_blocks; kb++, it++) {
-                    const uint32_t slot = it % C::kStages;
-                    if (!mbar_wait(&bars->full[slot], (it / C::kStages) & 1u, abort_flag)) {
+                    const long long f0 = clock64();
+                    if (!mbar_wait(&bars->full[slot], full_parity, abort_flag)) {
                         alive = false;
                         break;
                     }
+                    trace_full += clock64() - f0;
                     tc_fence_after();
-                    fence_proxy_async();  // the stage was written through the generic proxy
-                    const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
-                    const uint32_t sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
+                    const uint64_t off = (uint64_t)(slot * kStageUnits);
+                    const uint64_t a_desc = a_desc0 + off, b_desc = b_desc0 + off, sf_desc = sf_desc0 + off;
 #pragma unroll
                     for (uint32_t mx = 0; mx <= C::kMatrices; mx++)
-                        tc_copy_scales(tmem_scales + 4u * mx, desc_scale_block(sf + mx * kScaleBlockBytes));
-                    const uint64_t b_desc = desc_k_major_sw128(stage + C::kMatrices * kATileBytes);
-                    const uint32_t groups = min(4u, (k_dim - kb * kBlockK) / 32u);
-                    for (uint32_t j = 0; j < groups; j++) {
-                        const uint32_t id = idesc_with_scale_ids(idesc, j, j);
+                        tc_copy_scales(tmem_scales + 4u * mx, sf_desc + mx * (kScaleBlockBytes >> 4));
+                    const uint32_t groups = (kb + 1u == k_blocks && tail_groups != 0u) ? tail_groups : 4u;
 #pragma unroll
-                        for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
-                            const uint64_t a_desc = desc_k_major_sw128(stage + mx * kATileBytes);
-                            // a K step of 32 elements is 32 bytes: two 16-byte units of the start address
-                            tc_mma_block_scaled(d_tmem + mx * N_TILE, a_desc + 2u * j, b_desc + 2u * j, id,
-                                                tmem_scales + 4u * mx, tmem_scales + 4u * C::kMatrices,
-                                                (kb | j) != 0u ? 1u : 0u);
+                    for (uint32_t j = 0; j < 4u; j++) {
+                        if (j < groups) {
+#pragma unroll
+                            for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
+                                // a K step of 32 elements is 32 bytes: two 16-byte units of the start address
+                                tc_mma_block_scaled(d_tmem + mx * N_TILE, a_desc + (mx * (kATileBytes >> 4) + 2u * j),
+                                                    b_desc + 2u * j, kIdesc | (j << 4) | (j << 29), tmem_scales + 4u * mx,
+                                                    sfb_tmem, j == 0u ? (kb != 0u ? 1u : 0u) : 1u);
+                            }
                         }
                     }
                     tc_commit(&bars->empty[slot]);  // the stage may be refilled once these MMAs retire
+                    if (++slot == C::kStages) {
+                        slot = 0u;
+                        full_parity ^= 1u;
+                    }
                 }
                 if (alive) tc_commit(&bars->acc_full[acc]);
             }
             // nothing of this CTA may still be using tensor memory when it is released
             tc_commit(&bars->drain);
             mbar_wait(&bars->drain, 0u, abort_flag);
+            if (blockIdx.x == 0u) {
+                trace[2] = (uint64_t)trace_full;                 // MMA thread: cycles waiting for operands
+                trace[3] = (uint64_t)trace_acc;                  // MMA thread: cycles waiting for a free accumulator
+                trace[4] = (uint64_t)(clock64() - trace_begin);  // MMA thread: cycles in its loop
+                trace[5] = it;                                   // stages consumed
+            }
         }
         __syncwarp();
     } else {
         // ===== epilogue: TMEM -> registers -> global =============================================
         const uint32_t frame_words = K * (I / 2u) + K;
         uint32_t acc_it = 0u;
+        long long trace_epi_wait = 0;
+        const long long trace_begin = clock64();
         for (uint32_t tile = blockIdx.x; tile < tile_count; tile += gridDim.x, acc_it++) {
             const uint32_t pair = list.tiles[tile / m_tiles];
             const uint32_t m_tile = tile % m_tiles;
@@ -258,7 +375,9 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
             const uint32_t first = e_begin + n_tile * N_TILE;
             const uint32_t valid = min(N_TILE, e_end - first);
             const uint32_t acc = acc_it % C::kAccStages;
-            if (!mbar_wait(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag)) break;
+            const long long e0 = clock64();
+            if (!mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag)) break;
+            trace_epi_wait += clock64() - e0;
             tc_fence_after();
             const uint32_t row = m_tile * kBlockM + warp * 32u + lane;
             const bool row_ok = row < out_rows;
@@ -288,6 +407,10 @@ __global__ void __launch_bounds__(kThreads, 1) experts_tc_kernel(ExpertLaunch p,
             }
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[acc]);
+        }
+        if (blockIdx.x == 0u && threadIdx.x == 0u) {
+            trace[6] = (uint64_t)trace_epi_wait;                 // epilogue: cycles waiting for an accumulator
+            trace[7] = (uint64_t)(clock64() - trace_begin);      // epilogue: cycles in its loop
         }
     }
 
@@ -379,32 +502,58 @@ __global__ void commit_stamps_kernel(const ExpertPtrs* experts, uint64_t* stamps
     stamps[(size_t)i * 2u + 1u] = ptrs.gen[mx];
 }
 
+// One warp per (expert, matrix): the template map with the expert's weight address patched in.
+__global__ void __launch_bounds__(32) build_tensormaps_kernel(const ExpertPtrs* experts, const uint8_t* templ,
+                                                             uint8_t* maps, uint32_t matrices) {
+    __shared__ __align__(128) unsigned char sm[128];
+    const uint32_t e = blockIdx.x / matrices, mx = blockIdx.x % matrices;
+    const uint8_t* w = experts[e].w[mx];
+    if (experts[e].w[0] == nullptr || w == nullptr) return;
+    reinterpret_cast<uint32_t*>(sm)[threadIdx.x] = reinterpret_cast<const uint32_t*>(templ)[threadIdx.x];
+    __syncwarp();
+    if (threadIdx.x == 0u) tensormap_replace_address(sm, w);
+    __syncwarp();
+    tensormap_publish(maps + (size_t)blockIdx.x * 128u, sm);
+}
+
 int g_sm_count[16] = {0};
 
-template <bool GATE_UP, uint32_t N_TILE>
+template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
 void launch_n(const ExpertLaunch& p, cudaStream_t stream) {
-    using C = Config<GATE_UP, N_TILE>;
+    using C = Config<GATE_UP, N_TILE, USE_TMA>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (g_sm_count[dev & 15] == 0) cudaDeviceGetAttribute(&g_sm_count[dev & 15], cudaDevAttrMultiProcessorCount, dev);
-    experts_tc_kernel<GATE_UP, N_TILE><<<g_sm_count[dev & 15], kThreads, C::kSmemBytes, stream>>>(
+    experts_tc_kernel<GATE_UP, N_TILE, USE_TMA><<<g_sm_count[dev & 15], C::kThreads, C::kSmemBytes, stream>>>(
         p, TileList{p.tile_list, p.tile_count});
 }
 
 template <bool GATE_UP>
 void launch(const ExpertLaunch& p, cudaStream_t stream) {
-    switch (tc_token_tile(p)) {
-        case 16u: launch_n<GATE_UP, 16u>(p, stream); break;
-        case 32u: launch_n<GATE_UP, 32u>(p, stream); break;
-        case 64u: launch_n<GATE_UP, 64u>(p, stream); break;
-        default: launch_n<GATE_UP, 128u>(p, stream); break;
+    const uint32_t n = tc_token_tile(p);
+    if (p.tmaps != nullptr) {
+        switch (n) {
+            case 16u: launch_n<GATE_UP, 16u, true>(p, stream); break;
+            case 32u: launch_n<GATE_UP, 32u, true>(p, stream); break;
+            case 64u: launch_n<GATE_UP, 64u, true>(p, stream); break;
+            default: launch_n<GATE_UP, 128u, true>(p, stream); break;
+        }
+    } else {
+        switch (n) {
+            case 16u: launch_n<GATE_UP, 16u, false>(p, stream); break;
+            case 32u: launch_n<GATE_UP, 32u, false>(p, stream); break;
+            case 64u: launch_n<GATE_UP, 64u, false>(p, stream); break;
+            default: launch_n<GATE_UP, 128u, false>(p, stream); break;
+        }
     }
 }
 
 template <bool GATE_UP, uint32_t N_TILE>
 void configure_one() {
-    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)Config<GATE_UP, N_TILE>::kSmemBytes);
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Config<GATE_UP, N_TILE, true>::kSmemBytes);
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Config<GATE_UP, N_TILE, false>::kSmemBytes);
 }
 
 }  // namespace
@@ -435,6 +584,42 @@ void launch_derive_scales_tc(const ExpertLaunch& p, bool gate_up, cudaStream_t s
                                                                                       matrices, rows, cols);
     const uint32_t count = p.work.num_experts * matrices;
     commit_stamps_kernel<<<(count + 127u) / 128u, 128, 0, stream>>>(p.work.experts, p.scale_stamps, matrices, count);
+}
+
+bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows, uint32_t cols) {
+    // The packaged [rows][cols/2] bytes seen as a 3-D tensor of 4-bit elements
+    // {128 elements, cols/128 K blocks, rows}: a box {128, 1, 128} is one operand tile. The padded 4-bit
+    // type wants 32-byte strides (cols % 64 == 0); a trailing partial K block is not part of the map.
+    if (cols < kBlockK || cols % 64u != 0u) return false;
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        cudaDriverEntryPointQueryResult q;
+        void* fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !fn)
+            return false;
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const cuuint64_t dims[3] = {kBlockK, cols / kBlockK, rows};
+    const cuuint64_t strides[2] = {kBlockK / 2u, cols / 2u};
+    const cuuint32_t box[3] = {kBlockK, 1u, kBlockM};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUtensorMap map;
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, any_device_address, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::memcpy(map128, &map, 128);
+    return true;
+}
+
+void launch_build_tensormaps_tc(const ExpertLaunch& p, bool gate_up, const uint8_t* templ, cudaStream_t stream) {
+    const uint32_t matrices = gate_up ? 2u : 1u;
+    build_tensormaps_kernel<<<p.work.num_experts * matrices, 32, 0, stream>>>(p.work.experts, templ,
+                                                                              const_cast<uint8_t*>(p.tmaps), matrices);
 }
 
 void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream) {

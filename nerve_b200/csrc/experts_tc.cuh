@@ -10,6 +10,11 @@ bool tc_shape_supported(const nvmoe_geometry& g);
 // Whether "automatic" picks the tensor-core path.
 bool tc_enabled_by_default();
 void tc_configure_kernels();
+// Encodes the template tensor map of a [rows][cols] weight matrix (any 32-byte aligned device address
+// will do: it is replaced per expert). False when the shape cannot use TMA.
+bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows, uint32_t cols);
+// per-expert tensor maps = template + the expert's weight address (p.tmaps must be set)
+void launch_build_tensormaps_tc(const ExpertLaunch& p, bool gate_up, const uint8_t* templ, cudaStream_t stream);
 // token tile size for this call, and the (expert, token tile) list the kernels walk
 uint32_t tc_token_tile(const ExpertLaunch& p);
 void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream);

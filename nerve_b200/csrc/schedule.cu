@@ -366,8 +366,8 @@ __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t addre
         uint64_t bytes = (uint64_t)rec[2] | ((uint64_t)rec[3] << 32);
         uint64_t required = (j & 1u) ? scale_bytes : weight_bytes;
         // representation 0 (compact MXFP4) is the only one built; anything else fails closed
-        // and the kernels read rows with 16-byte loads, so the shader's 4-byte rule becomes 16
-        if (address == 0u || (address & 15u) != 0u || bytes < required || (rec[4] | rec[5]) == 0u ||
+        // and the kernels read rows with 16-byte loads and TMA boxes, so the shader's 4-byte rule becomes 32
+        if (address == 0u || (address & 31u) != 0u || bytes < required || (rec[4] | rec[5]) == 0u ||
             rec[6] != 1u || rec[7] != 0u) {
             ok = false;
             break;

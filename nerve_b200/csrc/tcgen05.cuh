@@ -63,6 +63,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// The same wait for a whole warp: one lane polls, the verdict is shared, so that a waiting warp
+// costs one polling thread instead of thirty-two.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    uint32_t ok = 0u;
+    if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0u;
+}
+
 // ---- generic-proxy staging into shared memory ---------------------------------------------------
 
 // src_bytes < size zero-fills the rest (src_bytes == 0 reads nothing)
@@ -88,6 +97,37 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 // makes this thread's generic-proxy writes to shared memory visible to the async proxy (tcgen05)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- TMA (async proxy) --------------------------------------------------------------------------------
+
+// one arrival that also announces `bytes` of bulk-copy traffic the barrier must see before it completes
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// 3-D tiled load; the box lands swizzled (and, for the padded 4-bit type, spread into 16-byte slots)
+// and the barrier is credited with the GLOBAL bytes of the box
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+// a tensor map that a kernel wrote (tensormap_publish) must be acquired by the thread that uses it
+__device__ __forceinline__ void tensormap_acquire(const void* tensor_map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tensor_map) : "memory");
+}
+// patch the global address of a 128-byte tensor map held in shared memory (one thread)
+__device__ __forceinline__ void tensormap_replace_address(void* smem_map, const void* global_address) {
+    asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(smem_u32(smem_map)),
+                 "l"(global_address)
+                 : "memory");
+}
+// copy the patched map to global memory with the release the TMA unit needs (whole warp)
+__device__ __forceinline__ void tensormap_publish(void* global_map, const void* smem_map) {
+    asm volatile("tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;"
+                 ::"l"(global_map), "r"(smem_u32(smem_map))
+                 : "memory");
+}
 
 // ---- tensor memory ----------------------------------------------------------------------------------
 
