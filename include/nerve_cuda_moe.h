@@ -195,6 +195,25 @@ int nvmoe_route_compact(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buff
                         nvmoe_buffer* intermediates, const nvmoe_buffer* gate_up_slots,
                         nvmoe_buffer* control);
 
+/* nvmoe_route_compact for callers that must not reach the device allocator (no counterpart in the
+ * reference, whose scheduler shader needs no scratch). Same arguments, outputs and errors as
+ * nvmoe_route_compact; the scratch of the multi-block counting sort is a fixed array in the library's
+ * own device memory instead of the plan's allocation, so the call allocates and frees nothing on the
+ * device. Use it where free device memory has been handed to something else (a key/value cache that
+ * takes all of it), where the caller holds the allocator's lock, or where an allocation would
+ * synchronise the device.
+ * Limits: ceil(batch_width * top_k / 256) * (num_experts + 1) <= 65536 and num_experts <= 1022;
+ * larger calls return NVMOE_ERR_INVALID_ARGUMENT with the sizes in nvmoe_last_error.
+ * The first call on a device looks up the array's address (no allocation, but a runtime call that is
+ * not a stream operation): make one call on each device before starting any stream capture.
+ * Every plan and every call on a device shares the one array. Nothing in it has to start at zero
+ * (each call writes every word it later reads), so calls that follow one another on one stream need
+ * no clearing; calls that overlap on different streams of one device race on it and must be
+ * serialised by the caller. */
+int nvmoe_route_compact_static(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* routes,
+                               nvmoe_buffer* intermediates, const nvmoe_buffer* gate_up_slots,
+                               nvmoe_buffer* control);
+
 /* Route counter in front of down (runtime-rs/shaders/moe_route_count_batch1.comp.template:21-58).
  * bindings: 1 routes, 3 slots (optional), 31 control. */
 int nvmoe_route_count(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* routes,

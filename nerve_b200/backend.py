@@ -252,6 +252,10 @@ class MoePlan:
     def moe_route_compact(self, batch_width, routes, intermediates, control, slots=None):
         self._call("nvmoe_route_compact", batch_width, _h(routes), _h(intermediates), _h(slots), _h(control))
 
+    def moe_route_compact_static(self, batch_width, routes, intermediates, control, slots=None):
+        """moe_route_compact with the sort scratch in the library's fixed device array: no device allocation."""
+        self._call("nvmoe_route_compact_static", batch_width, _h(routes), _h(intermediates), _h(slots), _h(control))
+
     def moe_route_count(self, batch_width, routes, control, slots=None):
         self._call("nvmoe_route_count", batch_width, _h(routes), _h(slots), _h(control))
 

@@ -71,6 +71,7 @@ PROTOTYPES = {
     "nvmoe_router_linear": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route_compact": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvmoe_route_compact_static": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route_count": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "nvmoe_quantize_fp8": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
     "nvmoe_gate_up": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <thread>
@@ -963,3 +964,75 @@ int nvmoe_plan_last_report(nvmoe_plan* p, nvmoe_work_report* report) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Route scheduler that allocates nothing.
+//
+// Some callers cannot let a call reach the device allocator: a serving loop that has handed all free
+// device memory to a key/value cache, a library whose caller holds the allocator's lock, or code that runs
+// where an allocation would synchronise the device. For them the scratch of the multi-block counting
+// sort (per-block histograms and bucket bases) lives in a fixed array in the module's own device
+// memory, which the loader places when the library is loaded on a device; its address comes from the
+// runtime's symbol table once per device and is then handed to the kernels as an ordinary pointer.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr uint32_t kStaticHistWords = 65536u;  // per-block histograms: blocks * (experts + 1) words
+constexpr uint32_t kStaticBaseWords = 1024u;   // bucket bases: experts + 2 words
+static __device__ __align__(256) uint32_t g_static_sort_scratch[kStaticHistWords + kStaticBaseWords];
+
+constexpr int kStaticScratchDevices = 64;
+std::mutex g_static_scratch_mutex;
+uint32_t* g_static_scratch_address[kStaticScratchDevices] = {nullptr};
+
+// Device address of the array on the plan's device (which must be current). Looked up on the first
+// call for a device and remembered.
+int static_scratch_for(nvmoe_plan* p, uint32_t** out) {
+    nvmoe_device* d = p->device;
+    if (d->ordinal < 0 || d->ordinal >= kStaticScratchDevices)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "device ordinal beyond the static scratch table");
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_address[d->ordinal]) {
+        void* address = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress(&address, g_static_sort_scratch);
+        if (err != cudaSuccess || address == nullptr)
+            return fail(d, NVMOE_ERR_CUDA, "static sort scratch: address lookup failed: %s", cudaGetErrorString(err));
+        g_static_scratch_address[d->ordinal] = static_cast<uint32_t*>(address);
+    }
+    *out = g_static_scratch_address[d->ordinal];
+    return NVMOE_OK;
+}
+
+}  // namespace
+
+extern "C" int nvmoe_route_compact_static(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* routes,
+                                          nvmoe_buffer* intermediates, const nvmoe_buffer* gate_up_slots,
+                                          nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, intermediates, (size_t)T * p->frame_words * 4u, "intermediates"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_slots(p, gate_up_slots));
+    const uint64_t count = (uint64_t)T * p->K;
+    const uint64_t blocks = (count + kSortChunk - 1u) / kSortChunk;
+    const uint64_t buckets = (uint64_t)p->experts + 1u;
+    if (blocks * buckets > kStaticHistWords || buckets + 1u > kStaticBaseWords)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT,
+                    "route compact (static scratch): %llu routes in %llu blocks x %llu buckets exceed the fixed scratch of "
+                    "%u histogram words / %u bucket words",
+                    (unsigned long long)count, (unsigned long long)blocks, (unsigned long long)buckets, kStaticHistWords,
+                    kStaticBaseWords);
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    uint32_t* scratch = nullptr;
+    NVMOE_TRY(static_scratch_for(p, &scratch));
+    const nvmoe_geometry& g = p->g;
+    const uint32_t tiles = (g.intermediate_size + g.gate_tile_rows - 1u) / g.gate_tile_rows;
+    const SortScratch fixed{scratch, scratch + kStaticHistWords, (uint32_t)(kStaticHistWords / buckets), (uint32_t)buckets};
+    launch_route_compact((const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr,
+                         gate_up_slots ? (const uint32_t*)gate_up_slots->ptr : nullptr,
+                         gate_up_slots ? (uint32_t)(gate_up_slots->bytes / 4u) : 0u, 4u, (uint32_t*)control->ptr, T, p->K,
+                         g.intermediate_size, tiles, p->experts, fixed, p->device->stream);
+    p->launches += count <= 4096u ? 1u : 3u;
+    return post_launch(p, "route compact (static scratch)");
+}
