@@ -305,11 +305,17 @@ typedef struct nvmoe_work_report {
     uint64_t weight_bytes_touched;
 } nvmoe_work_report;
 int nvmoe_plan_last_report(nvmoe_plan* plan, nvmoe_work_report* report);
-/* Diagnostics of the last tensor-core expert kernels: cycle counters of CTA 0, eight words for
- * gate/up then eight for down: {producer wait, producer total, MMA wait-operands, MMA
- * wait-accumulator, MMA total, stages, epilogue wait, epilogue total}. Synchronises the stream.
- * No reference counterpart. */
-int nvmoe_plan_debug_counters(nvmoe_plan* plan, uint64_t* out16);
+/* Diagnostics of the last tensor-core expert kernels: counters of CTA 0, twelve words for
+ * gate/up then twelve for down: cycles {producer wait, producer total, MMA wait-operands, MMA
+ * wait-accumulator, MMA total}, stages, cycles {epilogue wait, epilogue total}, then global-timer
+ * nanoseconds {kernel entry, MMA loop begin, MMA loop end, latest exit of any CTA}. Synchronises
+ * the stream. No reference counterpart. */
+int nvmoe_plan_debug_counters(nvmoe_plan* plan, uint64_t* out24);
+/* Per-CTA diagnostics of the tensor-core expert kernels. The first call arms the trace (and writes
+ * the CTA count); later calls copy [2 stages][ctas][4] words {loop begin ns, loop end ns, stages
+ * consumed, SM id} of the most recent kernels into `out` (room for max_ctas CTAs per stage).
+ * Synchronises the stream. No reference counterpart. */
+int nvmoe_plan_debug_cta_trace(nvmoe_plan* plan, uint64_t* out, uint32_t max_ctas, uint32_t* ctas);
 /* Kernels launched through this plan since it was created. */
 uint64_t nvmoe_plan_launch_count(const nvmoe_plan* plan);
 

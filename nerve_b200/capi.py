@@ -83,6 +83,7 @@ PROTOTYPES = {
     "nvmoe_layer_host": (c_int, [c_void_p, POINTER(LayerArgs), c_void_p, c_void_p]),
     "nvmoe_plan_last_report": (c_int, [c_void_p, POINTER(WorkReport)]),
     "nvmoe_plan_launch_count": (c_uint64, [c_void_p]),
+    "nvmoe_plan_debug_cta_trace": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p]),
     "nvmoe_plan_debug_counters": (c_int, [c_void_p, POINTER(c_uint64)]),
     "nvmoe_buffer_wrap": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_void_p)]),
     "nvmoe_device_set_stream": (c_int, [c_void_p, c_void_p]),

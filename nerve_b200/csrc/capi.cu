@@ -1,11 +1,13 @@
 // C ABI of the CUDA MoE backend (declared in include/nerve_cuda_moe.h): device, resident buffers,
 // plans, the node-granular operators and the fused layer call.  Host code only; the kernels live
 // in the other .cu files of this folder.
+#include <atomic>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <memory>
 #include <new>
 #include <string>
 #include <thread>
@@ -29,11 +31,17 @@ struct nvmoe_buffer {
     void* ptr = nullptr;
     size_t bytes = 0;
     bool owned = true;  // false for handles over memory the caller allocated
+    // identity and content version: what a plan resolved from an address or slot table stays valid
+    // while both are unchanged. Every write through this interface bumps the version; memory the
+    // caller owns can change behind the handle, so tables in wrapped buffers are resolved on every call.
+    uint64_t uid = 0;
+    uint64_t version = 0;
 };
 
 namespace {
 
 thread_local std::string g_open_error;
+std::atomic<uint64_t> g_next_buffer_uid{1};
 
 int fail(nvmoe_device* d, int code, const char* fmt, ...) {
     char text[512];
@@ -80,6 +88,25 @@ struct DeviceArray {  // plan-owned scratch
     }
 };
 
+// What one (address table, slot table) pair resolves to for one expert stage: validated weight and
+// scale pointers per expert and, for the tensor path, the re-tiled scale copies and the per-expert
+// tensor maps. Kept per pair so that a model's layers (one table pair each) resolve once, not per call.
+struct ExpertSet {
+    uint64_t key[4] = {0, 0, 0, 0};  // address table uid, version, slot table uid, version
+    bool cacheable = false;
+    bool resolved = false;
+    bool tensor_ready = false;
+    uint64_t last_use = 0;
+    DeviceArray ptrs, derived, stamps, tmaps;
+    void release() {
+        ptrs.release();
+        derived.release();
+        stamps.release();
+        tmaps.release();
+    }
+};
+constexpr size_t kMaxExpertSets = 64;
+
 enum Stage { kStageLinear, kStageRoute, kStageSchedule, kStageQuantX, kStageGateUp, kStageQuantI, kStageDown, kStageReduce, kStageCount };
 
 }  // namespace
@@ -92,10 +119,12 @@ struct nvmoe_plan {
     uint32_t frame_words = 0;
     int expert_path = 0;
     // scratch every expert call needs
-    DeviceArray status, gu_ptrs, down_ptrs, grouped[2], offsets[2], block_hist, bucket_base;
+    DeviceArray status, grouped[2], offsets[2], block_hist, bucket_base;
+    std::vector<std::unique_ptr<ExpertSet>> sets[2];  // [gate/up, down], least recently used replaced
+    uint64_t use_clock = 0;
     DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list, ep_source;
-    DeviceArray derived[2], stamps[2];  // tiled scale copies for the tensor path and what they were built from
-    DeviceArray tmap_templates, tmaps[2];  // tensor maps of the weight matrices: one template per stage, one map per expert matrix
+    DeviceArray cta_trace;       // per-CTA diagnostics of the tensor-path kernels, allocated on first request
+    DeviceArray tmap_templates;  // tensor maps of the two weight matrix shapes; each expert's map is one with its address patched in
     bool tma[2] = {false, false};
     // scratch of the fused layer call
     DeviceArray logits, routes, frames, expert_outputs, controls, hidden_dev, output_dev;
@@ -111,6 +140,12 @@ struct nvmoe_plan {
 };
 
 namespace {
+
+// One region per expert stage: 64 header words (entry count, diagnostics) and the (expert, token tile) list.
+size_t tile_region_words(const nvmoe_plan* p) {
+    const size_t list = (size_t)p->g.max_tokens * p->K / 16u + p->experts + 1u;
+    return (64u + list + 63u) / 64u * 64u;
+}
 
 size_t scratch_blocks(const nvmoe_plan* p) { return ((size_t)p->g.max_tokens * p->K + kSortChunk - 1u) / kSortChunk; }
 
@@ -291,6 +326,7 @@ int nvmoe_buffer_create(nvmoe_device* d, size_t bytes, nvmoe_buffer** out) {
     }
     b->device = d;
     b->bytes = bytes;
+    b->uid = g_next_buffer_uid.fetch_add(1);
     *out = b;
     return NVMOE_OK;
 }
@@ -310,6 +346,7 @@ int nvmoe_buffer_wrap(nvmoe_device* d, void* device_ptr, size_t bytes, nvmoe_buf
     b->ptr = device_ptr;
     b->bytes = bytes;
     b->owned = false;
+    b->uid = g_next_buffer_uid.fetch_add(1);
     *out = b;
     return NVMOE_OK;
 }
@@ -337,6 +374,7 @@ int nvmoe_buffer_write(nvmoe_buffer* b, size_t offset, const void* src, size_t b
     NVMOE_TRY(range_ok(b, offset, bytes, src));
     if (bytes == 0) return NVMOE_OK;
     nvmoe_device* d = b->device;
+    b->version++;
     NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
     NVMOE_CUDA(d, cudaMemcpyAsync((char*)b->ptr + offset, src, bytes, cudaMemcpyHostToDevice, d->stream));
     NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));  // the caller may reuse src at once
@@ -357,6 +395,7 @@ int nvmoe_buffer_fill(nvmoe_buffer* b, size_t offset, int byte_value, size_t byt
     NVMOE_TRY(range_ok(b, offset, bytes, b));
     if (bytes == 0) return NVMOE_OK;
     nvmoe_device* d = b->device;
+    b->version++;
     NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
     NVMOE_CUDA(d, cudaMemsetAsync((char*)b->ptr + offset, byte_value, bytes, d->stream));
     return NVMOE_OK;
@@ -402,8 +441,6 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
         if (err == cudaSuccess) err = a.ensure(bytes);
     };
     want(p->status, 256);
-    want(p->gu_ptrs, sizeof(ExpertPtrs) * p->experts);
-    want(p->down_ptrs, sizeof(ExpertPtrs) * p->experts);
     for (int i = 0; i < 2; i++) {
         want(p->grouped[i], sizeof(uint32_t) * R);
         want(p->offsets[i], sizeof(uint32_t) * (p->experts + 2u));
@@ -416,21 +453,13 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
     want(p->iq, R * I);
     want(p->i_scales, sizeof(float) * R * (I / g.act_block));
     want(p->i_e8m0, sizeof(uint32_t) * R * ((I + 127u) / 128u));
-    want(p->tile_list, sizeof(uint32_t) * (R / 16u + p->experts + 1u) + 256u);
+    want(p->tile_list, sizeof(uint32_t) * 2u * tile_region_words(p));
     if (tc_shape_supported(g)) {
-        want(p->derived[0], (size_t)p->experts * 2u * tc_derived_scale_bytes(g.intermediate_size, g.hidden_size));
-        want(p->derived[1], (size_t)p->experts * tc_derived_scale_bytes(g.hidden_size, g.intermediate_size));
-        want(p->stamps[0], (size_t)p->experts * 2u * 16u);
-        want(p->stamps[1], (size_t)p->experts * 16u);
-        if (err == cudaSuccess) err = cudaMemsetAsync(p->stamps[0].ptr, 0, p->stamps[0].bytes, d->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(p->stamps[1].ptr, 0, p->stamps[1].bytes, d->stream);
         want(p->tmap_templates, 256);
-        want(p->tmaps[0], (size_t)p->experts * 2u * 128u);
-        want(p->tmaps[1], (size_t)p->experts * 128u);
         if (err == cudaSuccess) {
             unsigned char maps[256];
-            p->tma[0] = tc_encode_weight_map(maps, p->tmaps[0].ptr, g.intermediate_size, g.hidden_size);
-            p->tma[1] = tc_encode_weight_map(maps + 128, p->tmaps[1].ptr, g.hidden_size, g.intermediate_size);
+            p->tma[0] = tc_encode_weight_map(maps, p->tmap_templates.ptr, g.intermediate_size, g.hidden_size);
+            p->tma[1] = tc_encode_weight_map(maps + 128, p->tmap_templates.ptr, g.hidden_size, g.intermediate_size);
             err = cudaMemcpyAsync(p->tmap_templates.ptr, maps, 256, cudaMemcpyHostToDevice, d->stream);
             if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer
         }
@@ -454,10 +483,11 @@ void nvmoe_plan_destroy(nvmoe_plan* p) {
     if (!p) return;
     cudaSetDevice(p->device->ordinal);
     cudaStreamSynchronize(p->device->stream);
-    DeviceArray* all[] = {&p->status, &p->gu_ptrs, &p->down_ptrs, &p->grouped[0], &p->grouped[1], &p->offsets[0],
+    for (auto& stage_sets : p->sets)
+        for (auto& es : stage_sets) es->release();
+    DeviceArray* all[] = {&p->status, &p->grouped[0], &p->grouped[1], &p->offsets[0],
                           &p->offsets[1], &p->block_hist, &p->bucket_base, &p->xq, &p->x_scales, &p->x_e8m0, &p->iq,
-                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->derived[0], &p->derived[1], &p->stamps[0],
-                          &p->stamps[1], &p->tmap_templates, &p->tmaps[0], &p->tmaps[1], &p->logits, &p->routes, &p->frames, &p->expert_outputs,
+                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->tmap_templates, &p->cta_trace, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
                           &p->controls, &p->hidden_dev, &p->output_dev};
     for (DeviceArray* a : all) a->release();
     if (p->pinned_in) cudaFreeHost(p->pinned_in);
@@ -599,25 +629,109 @@ int nvmoe_quantize_fp8(nvmoe_plan* p, uint32_t rows, uint32_t columns, const nvm
     return post_launch(p, "quantize");
 }
 
+// The resolved state for this pair of tables: the cached one when neither table has been written
+// since, else a (re)built one in the least recently used place.
+static int expert_set_for(nvmoe_plan* p, int set, const nvmoe_buffer* addresses, const nvmoe_buffer* slots, bool tensor,
+                          ExpertSet** out) {
+    const uint64_t key[4] = {addresses->uid, addresses->version, slots->uid, slots->version};
+    const bool cacheable = addresses->owned && slots->owned;
+    auto& sets = p->sets[set];
+    ExpertSet* found = nullptr;
+    for (auto& es : sets)
+        if (es->key[0] == key[0] && es->key[2] == key[2]) found = es.get();  // same tables: same place, maybe stale
+    if (!found) {
+        if (sets.size() < kMaxExpertSets) {
+            sets.emplace_back(new (std::nothrow) ExpertSet());
+            if (!sets.back()) {
+                sets.pop_back();
+                return fail(p->device, NVMOE_ERR_OUT_OF_MEMORY, "out of host memory");
+            }
+            found = sets.back().get();
+        } else {
+            found = sets[0].get();
+            for (auto& es : sets)
+                if (es->last_use < found->last_use) found = es.get();
+            // kernels of earlier calls may still read the place that is being reused
+            NVMOE_CUDA(p->device, cudaStreamSynchronize(p->device->stream));
+        }
+        found->resolved = found->tensor_ready = false;
+    }
+    if (!cacheable || found->key[1] != key[1] || found->key[3] != key[3]) found->resolved = found->tensor_ready = false;
+    for (int i = 0; i < 4; i++) found->key[i] = key[i];
+    found->cacheable = cacheable;
+    found->last_use = ++p->use_clock;
+    const nvmoe_geometry& g = p->g;
+    const uint32_t matrices = set == 0 ? 2u : 1u;
+    NVMOE_CUDA(p->device, found->ptrs.ensure(sizeof(ExpertPtrs) * p->experts));
+    if (tensor && !found->derived.ptr) {
+        const size_t per_matrix = set == 0 ? tc_derived_scale_bytes(g.intermediate_size, g.hidden_size)
+                                           : tc_derived_scale_bytes(g.hidden_size, g.intermediate_size);
+        NVMOE_CUDA(p->device, found->derived.ensure((size_t)p->experts * matrices * per_matrix));
+        NVMOE_CUDA(p->device, found->stamps.ensure((size_t)p->experts * matrices * 16u));
+        NVMOE_CUDA(p->device, found->tmaps.ensure((size_t)p->experts * matrices * 128u));
+        NVMOE_CUDA(p->device, cudaMemsetAsync(found->stamps.ptr, 0, found->stamps.bytes, p->device->stream));
+        found->resolved = found->tensor_ready = false;  // the resolved pointers name the derived copies
+    }
+    *out = found;
+    return NVMOE_OK;
+}
+
 // shared tail of the two gate/up entry points and of down
-static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* act_q, const float* act_scales,
-                       const uint32_t* act_e8m0, const uint32_t* routes, uint32_t* intermediates, uint16_t* outputs,
-                       const nvmoe_buffer* addresses, const nvmoe_buffer* slots, const uint32_t* control,
-                       bool allow_tensor_path) {
+// The resolved expert set of a table pair, with everything the kernels of this call need from it on
+// the device: validated pointers and, for the tensor path, re-tiled scales and tensor maps. Launches
+// only what the cached state lacks.
+static int prepare_expert_set(nvmoe_plan* p, bool gate_up, const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
+                              bool tensor, ExpertSet** out) {
     const nvmoe_geometry& g = p->g;
     cudaStream_t st = p->device->stream;
     const int set = gate_up ? 0 : 1;
-    ExpertPtrs* ptrs = (gate_up ? p->gu_ptrs : p->down_ptrs).as<ExpertPtrs>();
+    ExpertSet* es = nullptr;
+    NVMOE_TRY(expert_set_for(p, set, addresses, slots, tensor, &es));
     const uint64_t rows = gate_up ? g.intermediate_size : g.hidden_size;
     const uint64_t cols = gate_up ? g.hidden_size : g.intermediate_size;
-    launch_resolve_experts((const uint32_t*)addresses->ptr, (uint32_t)(addresses->bytes / 4u), (const uint32_t*)slots->ptr,
-                           (uint32_t)(slots->bytes / 4u), gate_up ? 4u : 2u, p->experts, rows * (cols / 2u),
-                           rows * (cols / 32u), p->derived[set].as<uint8_t>(),
-                           tc_derived_scale_bytes((uint32_t)rows, (uint32_t)cols), ptrs, st);
-    launch_group_slots(routes, intermediates, control, ptrs, p->experts, T, p->K, g.intermediate_size,
-                       p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->status.as<uint32_t>(),
-                       sort_scratch(p), st);
-    p->launches += 1u + ((size_t)T * p->K <= 4096u ? 1u : 3u);
+    if (!es->resolved) {
+        launch_resolve_experts((const uint32_t*)addresses->ptr, (uint32_t)(addresses->bytes / 4u), (const uint32_t*)slots->ptr,
+                               (uint32_t)(slots->bytes / 4u), gate_up ? 4u : 2u, p->experts, rows * (cols / 2u),
+                               rows * (cols / 32u), es->derived.as<uint8_t>(),
+                               tc_derived_scale_bytes((uint32_t)rows, (uint32_t)cols), es->ptrs.as<ExpertPtrs>(), st);
+        p->launches++;
+        es->resolved = es->cacheable;
+    }
+    if (tensor && !es->tensor_ready) {
+        ExpertLaunch el{};
+        el.work = GroupedWork{nullptr, nullptr, es->ptrs.as<ExpertPtrs>(), p->experts};
+        el.scale_stamps = es->stamps.as<uint64_t>();
+        el.tmaps = p->tma[set] ? es->tmaps.as<uint8_t>() : nullptr;
+        el.g = g;
+        launch_derive_scales_tc(el, gate_up, st);
+        p->launches += 2;
+        if (el.tmaps) {
+            launch_build_tensormaps_tc(el, gate_up, p->tmap_templates.as<uint8_t>() + set * 128, st);
+            p->launches++;
+        }
+        es->tensor_ready = es->cacheable;
+    }
+    *out = es;
+    return post_launch(p, gate_up ? "gate/up expert tables" : "down expert tables");
+}
+
+static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* act_q, const float* act_scales,
+                       const uint32_t* act_e8m0, const uint32_t* routes, uint32_t* intermediates, uint16_t* outputs,
+                       const nvmoe_buffer* addresses, const nvmoe_buffer* slots, const uint32_t* control,
+                       bool allow_tensor_path, ExpertSet* prepared = nullptr, bool scheduled = false) {
+    const nvmoe_geometry& g = p->g;
+    cudaStream_t st = p->device->stream;
+    const int set = gate_up ? 0 : 1;
+    const bool tensor = allow_tensor_path && use_tensor_path(p);
+    ExpertSet* es = prepared;
+    if (!es) NVMOE_TRY(prepare_expert_set(p, gate_up, addresses, slots, tensor, &es));
+    ExpertPtrs* ptrs = es->ptrs.as<ExpertPtrs>();
+    if (!scheduled) {
+        launch_group_slots(routes, intermediates, control, ptrs, p->experts, T, p->K, g.intermediate_size,
+                           p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->status.as<uint32_t>(),
+                           sort_scratch(p), st);
+        p->launches += (size_t)T * p->K <= 4096u ? 1u : 3u;
+    }
     ExpertLaunch el{};
     el.work = GroupedWork{p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), ptrs, p->experts};
     el.act_q = act_q;
@@ -627,21 +741,16 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
     el.intermediates = intermediates;
     el.outputs = outputs;
     el.status = p->status.as<uint32_t>();
-    el.scale_stamps = p->stamps[set].as<uint64_t>();
-    el.tmaps = p->tma[set] ? p->tmaps[set].as<uint8_t>() : nullptr;
-    el.tile_count = p->tile_list.as<uint32_t>();  // first word; the list follows at a 256-byte offset
-    el.tile_list = p->tile_list.as<uint32_t>() + 64;
+    el.scale_stamps = es->stamps.as<uint64_t>();
+    el.cta_trace = p->cta_trace.as<uint64_t>();
+    el.tmaps = tensor && p->tma[set] ? es->tmaps.as<uint8_t>() : nullptr;
+    el.tile_count = p->tile_list.as<uint32_t>() + set * tile_region_words(p);  // first word of the stage's region
+    el.tile_list = el.tile_count + 64;
     el.tokens = T;
     el.g = g;
-    const bool tensor = allow_tensor_path && use_tensor_path(p);
-    if (tensor) {
-        launch_derive_scales_tc(el, gate_up, st);
-        if (el.tmaps) {
-            launch_build_tensormaps_tc(el, gate_up, p->tmap_templates.as<uint8_t>() + set * 128, st);
-            p->launches++;
-        }
+    if (tensor && !scheduled) {
         launch_build_tiles_tc(el, st);
-        p->launches += 3;
+        p->launches++;
     }
     if (p->profile_stages) cudaEventRecord(p->kernel_ev[set][0], st);
     if (tensor) {
@@ -857,11 +966,48 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     mark(kStageRoute);
     NVMOE_TRY(nvmoe_route(p, T, logits, routes, a->bias, a->telemetry));
     mark(kStageSchedule);
-    write_control_kernel<<<1, 32, 0, st>>>((uint32_t*)gate_control.ptr, T, a->expert_start, a->expert_count);
-    write_control_kernel<<<1, 32, 0, st>>>((uint32_t*)down_control.ptr, T, a->expert_start, a->expert_count);
-    p->launches += 2;
-    NVMOE_TRY(nvmoe_route_compact(p, T, routes, &frames, a->gate_up_slots, &gate_control));
-    NVMOE_TRY(nvmoe_route_count(p, T, routes, a->down_slots, &down_control));
+    const bool tensor = use_tensor_path(p);
+    ExpertSet* sets[2] = {nullptr, nullptr};
+    NVMOE_TRY(prepare_expert_set(p, true, a->gate_up_addresses, a->gate_up_slots, tensor, &sets[0]));
+    NVMOE_TRY(prepare_expert_set(p, false, a->down_addresses, a->down_slots, tensor, &sets[1]));
+    const bool scheduled = layer_schedule_is_small(T, p->K);
+    if (scheduled) {
+        LayerSchedule ls{};
+        ls.routes = (const uint32_t*)routes->ptr;
+        ls.intermediates = (uint32_t*)frames.ptr;
+        ls.slots[0] = (const uint32_t*)a->gate_up_slots->ptr;
+        ls.slots[1] = (const uint32_t*)a->down_slots->ptr;
+        ls.slot_words[0] = (uint32_t)(a->gate_up_slots->bytes / 4u);
+        ls.slot_words[1] = (uint32_t)(a->down_slots->bytes / 4u);
+        ls.control[0] = (uint32_t*)gate_control.ptr;
+        ls.control[1] = (uint32_t*)down_control.ptr;
+        for (int i = 0; i < 2; i++) {
+            ls.experts[i] = sets[i]->ptrs.as<ExpertPtrs>();
+            ls.grouped[i] = p->grouped[i].as<uint32_t>();
+            ls.offsets[i] = p->offsets[i].as<uint32_t>();
+            ls.tile_count[i] = tensor ? p->tile_list.as<uint32_t>() + i * tile_region_words(p) : nullptr;
+            ls.tiles[i] = tensor ? ls.tile_count[i] + 64 : nullptr;
+        }
+        ls.status = p->status.as<uint32_t>();
+        ls.tokens = T;
+        ls.expert_start = a->expert_start;
+        ls.expert_count = a->expert_count;
+        ls.K = p->K;
+        ls.I = g.intermediate_size;
+        ls.tiles_per_route[0] = (g.intermediate_size + g.gate_tile_rows - 1u) / g.gate_tile_rows;
+        ls.tiles_per_route[1] = (g.hidden_size + g.down_tile_rows - 1u) / g.down_tile_rows;
+        ls.num_experts = p->experts;
+        ls.n_tile = tc_token_tile_for(T, p->K, p->experts);
+        launch_layer_schedule_small(ls, st);
+        p->launches++;
+        NVMOE_TRY(post_launch(p, "layer schedule"));
+    } else {
+        write_control_kernel<<<1, 32, 0, st>>>((uint32_t*)gate_control.ptr, T, a->expert_start, a->expert_count);
+        write_control_kernel<<<1, 32, 0, st>>>((uint32_t*)down_control.ptr, T, a->expert_start, a->expert_count);
+        p->launches += 2;
+        NVMOE_TRY(nvmoe_route_compact(p, T, routes, &frames, a->gate_up_slots, &gate_control));
+        NVMOE_TRY(nvmoe_route_count(p, T, routes, a->down_slots, &down_control));
+    }
     mark(kStageQuantX);
     // nvmoe_gate_up quantises then runs the experts; the stage marks split the two for the report
     launch_quantize((const uint16_t*)a->hidden->ptr, T, g.hidden_size, g.act_block, g.hidden_size, p->xq.as<uint8_t>(),
@@ -871,7 +1017,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     mark(kStageGateUp);
     NVMOE_TRY(run_experts(p, true, T, p->xq.as<uint8_t>(), p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(),
                           (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, nullptr, a->gate_up_addresses,
-                          a->gate_up_slots, (const uint32_t*)gate_control.ptr, true));
+                          a->gate_up_slots, (const uint32_t*)gate_control.ptr, true, sets[0], scheduled));
     mark(kStageQuantI);
     launch_quantize_frames((const uint32_t*)frames.ptr, T, p->K, g.intermediate_size, g.act_block, p->iq.as<uint8_t>(),
                            p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), st);
@@ -883,7 +1029,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     cudaMemsetAsync(outs.ptr, 0, (size_t)T * p->K * g.hidden_size * 2u, st);
     NVMOE_TRY(run_experts(p, false, T, p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(),
                           (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, (uint16_t*)outs.ptr, a->down_addresses,
-                          a->down_slots, (const uint32_t*)down_control.ptr, true));
+                          a->down_slots, (const uint32_t*)down_control.ptr, true, sets[1], scheduled));
     mark(kStageReduce);
     NVMOE_TRY(nvmoe_reduce(p, T, &outs, a->output));
     mark(kStageCount);
@@ -926,13 +1072,32 @@ int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hi
 
 uint64_t nvmoe_plan_launch_count(const nvmoe_plan* p) { return p ? p->launches : 0u; }
 
-int nvmoe_plan_debug_counters(nvmoe_plan* p, uint64_t* out16) {
-    uint64_t* out8 = out16;
+int nvmoe_plan_debug_counters(nvmoe_plan* p, uint64_t* out24) {
+    uint64_t* out8 = out24;
     if (!p || !out8) return NVMOE_ERR_INVALID_ARGUMENT;
     nvmoe_device* d = p->device;
     NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
     NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
-    NVMOE_CUDA(d, cudaMemcpy(out8, p->tile_list.as<uint32_t>() + 16, 128, cudaMemcpyDeviceToHost));
+    NVMOE_CUDA(d, cudaMemcpy(out8, p->tile_list.as<uint32_t>() + 16, 96, cudaMemcpyDeviceToHost));
+    NVMOE_CUDA(d, cudaMemcpy(out8 + 12, p->tile_list.as<uint32_t>() + tile_region_words(p) + 16 + 24, 96, cudaMemcpyDeviceToHost));
+    return NVMOE_OK;
+}
+
+int nvmoe_plan_debug_cta_trace(nvmoe_plan* p, uint64_t* out, uint32_t max_ctas, uint32_t* ctas) {
+    if (!p || !ctas) return NVMOE_ERR_INVALID_ARGUMENT;
+    nvmoe_device* d = p->device;
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    int sms = 0;
+    NVMOE_CUDA(d, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->ordinal));
+    *ctas = (uint32_t)sms;
+    const size_t bytes = (size_t)sms * 2u * 4u * sizeof(uint64_t);
+    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
+    if (!p->cta_trace.ptr) {  // first request: arm the trace, the next calls fill it
+        NVMOE_CUDA(d, p->cta_trace.ensure(bytes));
+        NVMOE_CUDA(d, cudaMemset(p->cta_trace.ptr, 0, bytes));
+        return NVMOE_OK;
+    }
+    if (out && max_ctas >= (uint32_t)sms) NVMOE_CUDA(d, cudaMemcpy(out, p->cta_trace.ptr, bytes, cudaMemcpyDeviceToHost));
     return NVMOE_OK;
 }
 

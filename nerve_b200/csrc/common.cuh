@@ -86,6 +86,28 @@ void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const
 void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t slot_words,
                         uint32_t params_per_resource, uint32_t* control, uint32_t max_tokens, uint32_t K,
                         uint32_t tiles_per_route, cudaStream_t stream);
+// (expert, token tile) list of the tensor-core expert kernels from the expert offsets
+void launch_build_tiles(const uint32_t* expert_offsets, uint32_t num_experts, uint32_t n_tile, uint32_t* tiles,
+                        uint32_t* count, cudaStream_t stream);
+// One-launch schedule of a whole layer call for small T*K (layer_schedule_is_small): control words,
+// compact list, owned count, and per expert stage [gate/up, down] the grouped routes, expert offsets
+// and (when tiles[stage] is set) the tile list. experts[stage] must already be resolved.
+struct LayerSchedule {
+    const uint32_t* routes;
+    uint32_t* intermediates;
+    const uint32_t* slots[2];
+    uint32_t slot_words[2];
+    uint32_t* control[2];
+    const ExpertPtrs* experts[2];
+    uint32_t* grouped[2];
+    uint32_t* offsets[2];
+    uint32_t* tiles[2];
+    uint32_t* tile_count[2];
+    uint32_t* status;
+    uint32_t tokens, expert_start, expert_count, K, I, tiles_per_route[2], num_experts, n_tile;
+};
+bool layer_schedule_is_small(uint32_t tokens, uint32_t K);
+void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream);
 // validates the address/slot tables of every expert once per call
 void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                             uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
@@ -132,6 +154,7 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     uint16_t* outputs;           // down output [T][K][H]
     uint32_t* status;
     const uint8_t* tmaps;        // tensor path: 128-byte tensor maps [expert][matrix], null = move weights with cp.async
+    uint64_t* cta_trace;         // tensor path diagnostics: [2][grid][4] words per CTA, or null
     uint64_t* scale_stamps;      // tensor path: {scale pointer, generation} the derived tiles were built from
     uint32_t* tile_list;         // tensor path scratch: routes / 16 + experts + 1 words
     uint32_t* tile_count;        // tensor path scratch: one word

@@ -108,8 +108,9 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
     const uint32_t m_tiles = (out_rows + kBlockM - 1u) / kBlockM;
     const uint32_t pair_count = *list.count;
     // cycle counters of CTA 0, one writer per role (diagnostics; words 16.. of the tile-count block)
-    uint64_t* trace = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(list.count) + 16) + (GATE_UP ? 0 : 8);
+    uint64_t* trace = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(list.count) + 16) + (GATE_UP ? 0 : 12);
     const uint32_t tile_count = pair_count * m_tiles;
+    if (blockIdx.x == 0u && threadIdx.x == 0u) trace[8] = global_timer_ns();  // kernel entry of CTA 0
 
     // ---- one-time setup ---------------------------------------------------------------------
     if (threadIdx.x == 0u) {
@@ -309,6 +310,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             bool alive = true;
             long long trace_full = 0, trace_acc = 0;
             const long long trace_begin = clock64();
+            if (blockIdx.x == 0u) trace[9] = global_timer_ns();  // MMA loop begins
+            const uint64_t cta_begin = p.cta_trace ? global_timer_ns() : 0u;
             for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x, acc_it++) {
                 const uint32_t acc = acc_it % C::kAccStages;
                 const long long a0 = clock64();
@@ -353,11 +356,21 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             // nothing of this CTA may still be using tensor memory when it is released
             tc_commit(&bars->drain);
             mbar_wait(&bars->drain, 0u, abort_flag);
+            if (p.cta_trace) {  // per-CTA diagnostics: loop begin, loop end, stages, SM id
+                uint32_t smid;
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                uint64_t* mine = p.cta_trace + (size_t)((GATE_UP ? 0u : gridDim.x) + blockIdx.x) * 4u;
+                mine[0] = cta_begin;
+                mine[1] = global_timer_ns();
+                mine[2] = it;
+                mine[3] = smid;
+            }
             if (blockIdx.x == 0u) {
                 trace[2] = (uint64_t)trace_full;                 // MMA thread: cycles waiting for operands
                 trace[3] = (uint64_t)trace_acc;                  // MMA thread: cycles waiting for a free accumulator
                 trace[4] = (uint64_t)(clock64() - trace_begin);  // MMA thread: cycles in its loop
                 trace[5] = it;                                   // stages consumed
+                trace[10] = global_timer_ns();                   // MMA loop ends
             }
         }
         __syncwarp();
@@ -387,21 +400,32 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 uint32_t d0[16], d1[16];
                 tmem_ld16(lane_addr + c0, d0);
                 if (GATE_UP) tmem_ld16(lane_addr + N_TILE + c0, d1);
+                // lane j < 16 works out where token c0 + j of the tile goes (and its route weight)
+                // while the accumulators arrive; the sixteen results are then handed round by shuffles
+                uint64_t my_row = 0u;
+                float my_weight = 0.0f;
+                if (lane < 16u && c0 + lane < valid) {
+                    const uint32_t ri = __ldg(p.work.grouped_routes + first + c0 + lane);
+                    if (GATE_UP) {
+                        my_row = reinterpret_cast<uint64_t>(reinterpret_cast<uint16_t*>(p.intermediates + (size_t)(ri / K) * frame_words) +
+                                                            (size_t)(ri % K) * I);
+                    } else {
+                        my_row = reinterpret_cast<uint64_t>(p.outputs + (size_t)ri * H);
+                        my_weight = nvmoe_bf16_to_f32(__ldg(p.routes + ri) >> 16);
+                    }
+                }
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t j = 0; j < 16u; j++) {
-                    const uint32_t n = c0 + j;
-                    if (n >= valid || !row_ok) continue;
-                    const uint32_t ri = __ldg(p.work.grouped_routes + first + n);
+                    uint16_t* out = reinterpret_cast<uint16_t*>(__shfl_sync(0xffffffffu, my_row, j));
+                    const float weight = __shfl_sync(0xffffffffu, my_weight, j);
+                    if (c0 + j >= valid || !row_ok) continue;
                     if (GATE_UP) {
                         const float a = nvmoe_swiglu(__uint_as_float(d0[j]), __uint_as_float(d1[j]), p.g.swiglu_limit,
                                                      p.g.swiglu_alpha, p.g.swiglu_up_offset);
-                        uint16_t* out = reinterpret_cast<uint16_t*>(p.intermediates + (size_t)(ri / K) * frame_words) +
-                                        (size_t)(ri % K) * I;
                         out[row] = (uint16_t)nvmoe_f32_to_bf16(a);
                     } else {
-                        const float weight = nvmoe_bf16_to_f32(__ldg(p.routes + ri) >> 16);
-                        p.outputs[(size_t)ri * H + row] = (uint16_t)nvmoe_f32_to_bf16(__fmul_rn(__uint_as_float(d0[j]), weight));
+                        out[row] = (uint16_t)nvmoe_f32_to_bf16(__fmul_rn(__uint_as_float(d0[j]), weight));
                     }
                 }
             }
@@ -421,47 +445,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemColumns);
     }
-}
-
-// (expert, token tile) pairs in expert order; one block, experts <= 4096
-__global__ void __launch_bounds__(1024) build_tiles_kernel(const uint32_t* expert_offsets, uint32_t num_experts,
-                                                          uint32_t n_tile, uint32_t* tiles, uint32_t* count) {
-    __shared__ uint32_t warp_sums[32];
-    __shared__ uint32_t carry;
-    if (threadIdx.x == 0u) carry = 0u;
-    __syncthreads();
-    for (uint32_t base = 0; base < num_experts; base += blockDim.x) {
-        const uint32_t e = base + threadIdx.x;
-        uint32_t mine = 0u;
-        if (e < num_experts) mine = (expert_offsets[e + 1u] - expert_offsets[e] + n_tile - 1u) / n_tile;
-        // block-wide exclusive scan
-        uint32_t incl = mine;
-        const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
-            if ((int)lane >= o) incl += n;
-        }
-        if (lane == 31u) warp_sums[warp] = incl;
-        __syncthreads();
-        if (warp == 0u) {
-            uint32_t v = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0u;
-            uint32_t s = v;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                uint32_t n = __shfl_up_sync(0xffffffffu, s, o);
-                if ((int)lane >= o) s += n;
-            }
-            warp_sums[lane] = s - v;
-        }
-        __syncthreads();
-        const uint32_t start = carry + warp_sums[warp] + incl - mine;
-        for (uint32_t j = 0; j < mine; j++) tiles[start + j] = (e << 16) | j;
-        __syncthreads();
-        if (threadIdx.x == blockDim.x - 1u) carry = start + mine;
-        __syncthreads();
-    }
-    if (threadIdx.x == 0u) *count = carry;
+    // latest exit over all CTAs (the timer only grows, so the last launch wins)
+    if (threadIdx.x == 0u) atomicMax(reinterpret_cast<unsigned long long*>(trace + 11), (unsigned long long)global_timer_ns());
 }
 
 // Re-tiles the packaged [rows][cols/32] scale bytes of one expert matrix into 512-byte blocks, one
@@ -562,13 +547,17 @@ bool tc_shape_supported(const nvmoe_geometry& g) {
     return g.hidden_size % 32u == 0u && g.intermediate_size % 32u == 0u && g.act_block % 32u == 0u;
 }
 
-bool tc_enabled_by_default() { return false; }
+bool tc_enabled_by_default() { return true; }
+
+uint32_t tc_token_tile_for(uint32_t tokens, uint32_t routes_per_token, uint32_t num_experts) {
+    // tokens per expert if routing were uniform; skew only adds token tiles
+    const uint32_t routes = tokens * routes_per_token;
+    const uint32_t per_expert = (routes + num_experts - 1u) / num_experts;
+    return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : 128u;
+}
 
 uint32_t tc_token_tile(const ExpertLaunch& p) {
-    // tokens per expert if routing were uniform; skew only adds token tiles
-    const uint32_t routes = p.tokens * (p.g.routed_k + p.g.always_count);
-    const uint32_t per_expert = (routes + p.work.num_experts - 1u) / p.work.num_experts;
-    return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : 128u;
+    return tc_token_tile_for(p.tokens, p.g.routed_k + p.g.always_count, p.work.num_experts);
 }
 
 size_t tc_derived_scale_bytes(uint32_t rows, uint32_t cols) {
@@ -623,9 +612,7 @@ void launch_build_tensormaps_tc(const ExpertLaunch& p, bool gate_up, const uint8
 }
 
 void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream) {
-    // tile_list holds routes / 16 + experts + 1 entries: enough for any token tile size
-    build_tiles_kernel<<<1, 1024, 0, stream>>>(p.work.expert_offsets, p.work.num_experts, tc_token_tile(p),
-                                               p.tile_list, p.tile_count);
+    launch_build_tiles(p.work.expert_offsets, p.work.num_experts, tc_token_tile(p), p.tile_list, p.tile_count, stream);
 }
 
 void tc_configure_kernels() {

@@ -294,19 +294,31 @@ __global__ void __launch_bounds__(64) router_linear_kernel(const uint16_t* __res
 #pragma unroll
         for (int b = 0; b < ET; b++) acc[a][b] = 0.0f;
 
-    for (uint32_t cw = v; cw < words; cw += 64u) {
-        uint32_t xr[TT], wr[ET];
+    // The sum order of a lane is fixed (its words in ascending order), the load order is not: the
+    // loads of kDepth steps are issued together so that their latencies overlap.
+    constexpr int kDepth = TT * ET <= 16 ? 4 : 1;
+    for (uint32_t cw0 = v; cw0 < words; cw0 += 64u * kDepth) {
+        uint32_t xr[kDepth][TT], wr[kDepth][ET];
 #pragma unroll
-        for (int a = 0; a < TT; a++) xr[a] = (t0 + a < tokens) ? xw[(size_t)(t0 + a) * words + cw] : 0u;
+        for (int u = 0; u < kDepth; u++) {
+            const uint32_t cw = cw0 + 64u * u;
+            const bool in = cw < words;
 #pragma unroll
-        for (int b = 0; b < ET; b++) wr[b] = (e0 + b < outputs) ? ww[(size_t)(e0 + b) * words + cw] : 0u;
+            for (int a = 0; a < TT; a++) xr[u][a] = (in && t0 + a < tokens) ? __ldg(xw + (size_t)(t0 + a) * words + cw) : 0u;
 #pragma unroll
-        for (int a = 0; a < TT; a++) {
-            float xl = nvmoe_bf16_to_f32(xr[a]), xh = nvmoe_bf16_to_f32(xr[a] >> 16);
+            for (int b = 0; b < ET; b++) wr[u][b] = (in && e0 + b < outputs) ? __ldg(ww + (size_t)(e0 + b) * words + cw) : 0u;
+        }
 #pragma unroll
-            for (int b = 0; b < ET; b++) {
-                acc[a][b] = __fmaf_rn(xl, nvmoe_bf16_to_f32(wr[b]), acc[a][b]);
-                acc[a][b] = __fmaf_rn(xh, nvmoe_bf16_to_f32(wr[b] >> 16), acc[a][b]);
+        for (int u = 0; u < kDepth; u++) {
+            if (cw0 + 64u * u >= words) break;  // a step past the end must not even add zeros (-0 + 0 = +0)
+#pragma unroll
+            for (int a = 0; a < TT; a++) {
+                float xl = nvmoe_bf16_to_f32(xr[u][a]), xh = nvmoe_bf16_to_f32(xr[u][a] >> 16);
+#pragma unroll
+                for (int b = 0; b < ET; b++) {
+                    acc[a][b] = __fmaf_rn(xl, nvmoe_bf16_to_f32(wr[u][b]), acc[a][b]);
+                    acc[a][b] = __fmaf_rn(xh, nvmoe_bf16_to_f32(wr[u][b] >> 16), acc[a][b]);
+                }
             }
         }
     }

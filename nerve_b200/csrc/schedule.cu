@@ -165,12 +165,10 @@ __device__ __forceinline__ uint32_t min_u32(uint32_t a, uint32_t b) { return a <
 
 // Single-block compact (T*K small).  `control` is read for batch_width / expert range and the
 // owned count and indirect-dispatch words are written back exactly as the shader does.
-__global__ void __launch_bounds__(1024) compact_small_kernel(const uint32_t* routes, uint32_t* intermediates,
-                                                            const uint32_t* slots, uint32_t slot_words,
-                                                            uint32_t params, uint32_t* control,
-                                                            uint32_t max_tokens, uint32_t K, uint32_t I,
-                                                            uint32_t tiles_per_route, uint32_t num_experts) {
-    extern __shared__ uint32_t hist[];
+__device__ void compact_small_body(const uint32_t* routes, uint32_t* intermediates, const uint32_t* slots,
+                                   uint32_t slot_words, uint32_t params, uint32_t* control, uint32_t max_tokens,
+                                   uint32_t K, uint32_t I, uint32_t tiles_per_route, uint32_t num_experts,
+                                   uint32_t* hist) {
     const uint32_t T = min_u32(control[0], max_tokens);
     const uint32_t count = T * K;
     const uint32_t data_words = K * (I / 2u);
@@ -196,6 +194,16 @@ __global__ void __launch_bounds__(1024) compact_small_kernel(const uint32_t* rou
             }
         });
     }
+}
+
+__global__ void __launch_bounds__(1024) compact_small_kernel(const uint32_t* routes, uint32_t* intermediates,
+                                                            const uint32_t* slots, uint32_t slot_words,
+                                                            uint32_t params, uint32_t* control,
+                                                            uint32_t max_tokens, uint32_t K, uint32_t I,
+                                                            uint32_t tiles_per_route, uint32_t num_experts) {
+    extern __shared__ uint32_t hist[];
+    compact_small_body(routes, intermediates, slots, slot_words, params, control, max_tokens, K, I, tiles_per_route,
+                       num_experts, hist);
 }
 
 // Multi-block sort, phase 1: per-block histograms.
@@ -307,12 +315,14 @@ __global__ void __launch_bounds__(256) compact_scatter_kernel(const uint32_t* ro
 }
 
 // moe_route_count: the owned count only (one block; a grid-stride count is plenty here)
-__global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* routes, const uint32_t* slots,
-                                                          uint32_t slot_words, uint32_t params, uint32_t* control,
-                                                          uint32_t max_tokens, uint32_t K, uint32_t tiles_per_route) {
+// (every thread of the block calls it; the branch is uniform)
+__device__ void route_count_body(const uint32_t* routes, const uint32_t* slots, uint32_t slot_words, uint32_t params,
+                                 uint32_t* control, uint32_t max_tokens, uint32_t K, uint32_t tiles_per_route) {
     __shared__ uint32_t owned;
     const uint32_t T = min_u32(control[0], max_tokens);
-    if (control[2] == 0u) {
+    const uint32_t start = control[1], owned_experts = control[2];
+    __syncthreads();  // every thread has read the control words before one of them rewrites the tail
+    if (owned_experts == 0u) {
         if (threadIdx.x == 0u) {
             control[3] = T * K;
             control[4] = K * tiles_per_route;
@@ -323,7 +333,7 @@ __global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* route
     }
     if (threadIdx.x == 0u) owned = 0u;
     __syncthreads();
-    const uint32_t start = control[1], end = control[1] + control[2];
+    const uint32_t end = start + owned_experts;
     uint32_t mine = 0u;
     for (uint32_t i = threadIdx.x; i < T * K; i += blockDim.x) {
         uint32_t e = routes[i] & 0xffffu;
@@ -337,6 +347,12 @@ __global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* route
         control[5] = 1u;
         control[6] = 1u;
     }
+}
+
+__global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* routes, const uint32_t* slots,
+                                                          uint32_t slot_words, uint32_t params, uint32_t* control,
+                                                          uint32_t max_tokens, uint32_t K, uint32_t tiles_per_route) {
+    route_count_body(routes, slots, slot_words, params, control, max_tokens, K, tiles_per_route);
 }
 
 // address_record_is_resident + dynamic_parameter_record_is_valid for every expert, once per call
@@ -397,10 +413,8 @@ __device__ __forceinline__ uint32_t slot_count(const uint32_t* control, uint32_t
     return control[2] != 0u ? min_u32(control[3], T * K) : T * K;
 }
 
-__global__ void __launch_bounds__(1024) group_small_kernel(SlotKey key, const uint32_t* control,
-                                                          uint32_t max_tokens, uint32_t* grouped,
-                                                          uint32_t* expert_offsets) {
-    extern __shared__ uint32_t hist[];
+__device__ void group_small_body(SlotKey key, const uint32_t* control, uint32_t max_tokens, uint32_t* grouped,
+                                 uint32_t* expert_offsets, uint32_t* hist) {
     const uint32_t T = min_u32(control[0], max_tokens);
     key.capacity = T * key.K;
     const uint32_t count = slot_count(control, max_tokens, key.K);
@@ -409,6 +423,85 @@ __global__ void __launch_bounds__(1024) group_small_kernel(SlotKey key, const ui
     sort_single_block(count, buckets, hist, key, emit, [&](const uint32_t* base) {
         for (uint32_t b = threadIdx.x; b <= buckets; b += blockDim.x) expert_offsets[b] = base[b];
     });
+}
+
+__global__ void __launch_bounds__(1024) group_small_kernel(SlotKey key, const uint32_t* control,
+                                                          uint32_t max_tokens, uint32_t* grouped,
+                                                          uint32_t* expert_offsets) {
+    extern __shared__ uint32_t hist[];
+    group_small_body(key, control, max_tokens, grouped, expert_offsets, hist);
+}
+
+// (expert, token tile) pairs in expert order for the tensor-core expert kernels: entry =
+// (expert << 16) | token tile within the expert; every thread of one block calls it
+__device__ void build_tiles_body(const uint32_t* expert_offsets, uint32_t num_experts, uint32_t n_tile,
+                                 uint32_t* tiles, uint32_t* count) {
+    __shared__ uint32_t warp_sums[32];
+    __shared__ uint32_t carry;
+    if (threadIdx.x == 0u) carry = 0u;
+    __syncthreads();
+    for (uint32_t base = 0; base < num_experts; base += blockDim.x) {
+        const uint32_t e = base + threadIdx.x;
+        uint32_t mine = 0u;
+        if (e < num_experts) mine = (expert_offsets[e + 1u] - expert_offsets[e] + n_tile - 1u) / n_tile;
+        // block-wide exclusive scan
+        uint32_t incl = mine;
+        const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((int)lane >= o) incl += n;
+        }
+        if (lane == 31u) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0u) {
+            uint32_t v = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0u;
+            uint32_t sum = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t n = __shfl_up_sync(0xffffffffu, sum, o);
+                if ((int)lane >= o) sum += n;
+            }
+            warp_sums[lane] = sum - v;
+        }
+        __syncthreads();
+        const uint32_t start = carry + warp_sums[warp] + incl - mine;
+        for (uint32_t j = 0; j < mine; j++) tiles[start + j] = (e << 16) | j;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1u) carry = start + mine;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0u) *count = carry;
+}
+
+__global__ void __launch_bounds__(1024) build_tiles_kernel(const uint32_t* expert_offsets, uint32_t num_experts,
+                                                          uint32_t n_tile, uint32_t* tiles, uint32_t* count) {
+    build_tiles_body(expert_offsets, num_experts, n_tile, tiles, count);
+}
+
+// The whole schedule of one layer call in one block (T*K small): the control words the host of the
+// reference writes, the compact list in front of gate/up, the owned count in front of down, and for
+// each of the two expert stages the expert-grouped route list and the tensor-path tile list.
+__global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedule s) {
+    extern __shared__ uint32_t hist[];
+    if (threadIdx.x < 14u) {
+        const uint32_t j = threadIdx.x % 7u;
+        s.control[threadIdx.x / 7u][j] = j == 0u ? s.tokens : j == 1u ? s.expert_start : j == 2u ? s.expert_count : 0u;
+    }
+    __syncthreads();
+    compact_small_body(s.routes, s.intermediates, s.slots[0], s.slot_words[0], 4u, s.control[0], s.tokens, s.K, s.I,
+                       s.tiles_per_route[0], s.num_experts, hist);
+    __syncthreads();
+    route_count_body(s.routes, s.slots[1], s.slot_words[1], 2u, s.control[1], s.tokens, s.K, s.tiles_per_route[1]);
+    __syncthreads();
+    const uint32_t data_words = s.K * (s.I / 2u);
+    for (uint32_t stage = 0; stage < 2u; stage++) {
+        SlotKey key{s.routes, s.intermediates, s.experts[stage], s.status, s.num_experts, s.K, data_words + s.K, data_words, 0u};
+        group_small_body(key, s.control[stage], s.tokens, s.grouped[stage], s.offsets[stage], hist);
+        __syncthreads();
+        if (s.tiles[stage]) build_tiles_body(s.offsets[stage], s.num_experts, s.n_tile, s.tiles[stage], s.tile_count[stage]);
+        __syncthreads();
+    }
 }
 
 __global__ void __launch_bounds__(256) group_hist_kernel(SlotKey key, const uint32_t* control,
@@ -569,6 +662,19 @@ void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const
     compact_scatter_kernel<<<blocks, 256, buckets * sizeof(uint32_t), stream>>>(
         routes, intermediates, slots, slot_words, params_per_resource, control, max_tokens, K,
         intermediate_size, tiles_per_route, num_experts, scratch.block_hist, scratch.bucket_base);
+}
+
+bool layer_schedule_is_small(uint32_t tokens, uint32_t K) { return (uint64_t)tokens * K <= kSmallSortLimit; }
+
+void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
+    const uint32_t count = s.tokens * s.K;
+    layer_schedule_small_kernel<<<1, count <= 256u ? 256u : 1024u, (s.num_experts + 2u) * sizeof(uint32_t), stream>>>(s);
+}
+
+void launch_build_tiles(const uint32_t* expert_offsets, uint32_t num_experts, uint32_t n_tile, uint32_t* tiles,
+                        uint32_t* count, cudaStream_t stream) {
+    // tiles holds routes / 16 + experts + 1 entries: enough for any token tile size
+    build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_offsets, num_experts, n_tile, tiles, count);
 }
 
 void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t slot_words,
