@@ -313,10 +313,14 @@ def main() -> None:
     e2e_value = tokens / (statistics.mean(e2e_ms) * 1e-3)
 
     ab = algorithmic_bytes(cfg, tokens, distinct)
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised under
+    # profiles/ (taken on this workload); other workloads have no capture and report null
+    ncu_traffic = {("gpt-oss-20b-decode", 64): {"gate_up": 289202944, "down": 146564608}}.get((args.workload, tokens))
     if bound == "hbm":
         achieved = ab["gate_up"] / (gate_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "gate_up",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": ncu_traffic["gate_up"] if ncu_traffic else None,
+                    "kernel": "gate_up",
                     "peak_kind": f"{peak_kind} STREAM-style copy",
                     "algorithmic_bytes_per_launch": ab["gate_up"], "kernel_ms": gate_ms,
                     "down_kernel": {"achieved": ab["down"] / (down_ms * 1e-3) / 1e9, "kernel_ms": down_ms,
