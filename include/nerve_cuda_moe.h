@@ -260,6 +260,11 @@ int nvmoe_reduce(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* exp
  * intermediate frames held in plan-owned memory. router_weights may be null when `logits` is
  * supplied instead (then the projection is skipped). routes_out, telemetry and logits are optional.
  * expert_start/expert_count describe the experts this device owns (0,0 = all).
+ * routes_in (optional) hands in routes that were selected elsewhere, [batch_width][top_k] words in the
+ * router's output format: projection and router are skipped (the reference's preselected-route
+ * form, which an expert-parallel owner runs on the rows it received). expert_outputs (optional)
+ * receives the weighted per-route rows [batch_width][top_k][hidden] and the combine is skipped;
+ * `output` may then be null.
  */
 typedef struct nvmoe_layer_args {
     uint32_t batch_width;
@@ -277,6 +282,8 @@ typedef struct nvmoe_layer_args {
     nvmoe_buffer* output;
     nvmoe_buffer* routes_out;
     nvmoe_buffer* telemetry;
+    const nvmoe_buffer* routes_in;
+    nvmoe_buffer* expert_outputs;
 } nvmoe_layer_args;
 
 int nvmoe_layer(nvmoe_plan* plan, const nvmoe_layer_args* args);
@@ -332,11 +339,16 @@ uint64_t nvmoe_plan_launch_count(const nvmoe_plan* plan);
  *   dest_counts[rank] rows bound for each rank (the split sizes of the all-to-all)
  * nvmoe_ep_unpack puts the rows that came back (same positions) into expert_outputs [T][K][H] so
  * that moe_reduce runs unchanged.
+ * segment_rows = 0 packs the rows back to back (split sizes = dest_counts, which the host must read
+ * before the exchange). segment_rows > 0 (at least T*K) gives every destination rank its own segment
+ * of that many slots in send_rows / send_routes (world_size * segment_rows slots in all): unused
+ * slots carry the route word 0xffffffff, which no scheduler keeps, so the exchange can use equal
+ * splits and nothing has to reach the host; send_index then holds slots of that layout.
  */
 int nvmoe_ep_pack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hidden,
                   const nvmoe_buffer* routes, const nvmoe_buffer* owner_table, uint32_t world_size,
                   uint32_t rank, nvmoe_buffer* send_rows, nvmoe_buffer* send_routes,
-                  nvmoe_buffer* send_index, nvmoe_buffer* dest_counts);
+                  nvmoe_buffer* send_index, nvmoe_buffer* dest_counts, uint32_t segment_rows);
 int nvmoe_ep_unpack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* returned_rows,
                     const nvmoe_buffer* send_index, nvmoe_buffer* expert_outputs);
 

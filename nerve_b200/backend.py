@@ -280,9 +280,9 @@ class MoePlan:
 
     # -- expert-parallel exchange ------------------------------------------------------------
     def ep_pack(self, batch_width, hidden, routes, owner_table, world_size, rank, send_rows, send_routes, send_index,
-                dest_counts):
+                dest_counts, segment_rows=0):
         self._call("nvmoe_ep_pack", batch_width, _h(hidden), _h(routes), _h(owner_table), world_size, rank,
-                   _h(send_rows), _h(send_routes), _h(send_index), _h(dest_counts))
+                   _h(send_rows), _h(send_routes), _h(send_index), _h(dest_counts), segment_rows)
 
     def ep_unpack(self, batch_width, returned_rows, send_index, expert_outputs):
         self._call("nvmoe_ep_unpack", batch_width, _h(returned_rows), _h(send_index), _h(expert_outputs))
@@ -294,7 +294,7 @@ class MoePlan:
     # -- the whole chain -------------------------------------------------------------------
     def _layer_args(self, batch_width, bank: ExpertBank, hidden=None, output=None, router_weights=None,
                     router_bias=None, logits=None, bias=None, routes_out=None, telemetry=None, expert_start=0,
-                    expert_count=0) -> capi.LayerArgs:
+                    expert_count=0, routes_in=None, expert_outputs=None) -> capi.LayerArgs:
         a = capi.LayerArgs()
         a.batch_width, a.expert_start, a.expert_count = batch_width, expert_start, expert_count
         a.hidden, a.output = _h(hidden), _h(output)
@@ -302,6 +302,7 @@ class MoePlan:
         a.gate_up_addresses, a.gate_up_slots = _h(bank.gate_up_addresses), _h(bank.gate_up_slots)
         a.down_addresses, a.down_slots = _h(bank.down_addresses), _h(bank.down_slots)
         a.routes_out, a.telemetry = _h(routes_out), _h(telemetry)
+        a.routes_in, a.expert_outputs = _h(routes_in), _h(expert_outputs)
         return a
 
     def layer(self, batch_width, bank: ExpertBank, hidden, output, **kw):

@@ -36,7 +36,7 @@ class LayerArgs(ctypes.Structure):
         ("hidden", c_void_p), ("router_weights", c_void_p), ("router_bias", c_void_p), ("logits", c_void_p),
         ("bias", c_void_p), ("gate_up_addresses", c_void_p), ("gate_up_slots", c_void_p),
         ("down_addresses", c_void_p), ("down_slots", c_void_p), ("output", c_void_p),
-        ("routes_out", c_void_p), ("telemetry", c_void_p),
+        ("routes_out", c_void_p), ("telemetry", c_void_p), ("routes_in", c_void_p), ("expert_outputs", c_void_p),
     ]
 
 
@@ -88,7 +88,7 @@ PROTOTYPES = {
     "nvmoe_buffer_wrap": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_void_p)]),
     "nvmoe_device_set_stream": (c_int, [c_void_p, c_void_p]),
     "nvmoe_ep_pack": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p,
-                              c_void_p, c_void_p]),
+                              c_void_p, c_void_p, c_uint32]),
     "nvmoe_ep_unpack": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
 }
 

@@ -862,7 +862,7 @@ int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, 
 
 int nvmoe_ep_pack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const nvmoe_buffer* routes,
                   const nvmoe_buffer* owner_table, uint32_t world, uint32_t rank, nvmoe_buffer* send_rows,
-                  nvmoe_buffer* send_routes, nvmoe_buffer* send_index, nvmoe_buffer* dest_counts) {
+                  nvmoe_buffer* send_routes, nvmoe_buffer* send_index, nvmoe_buffer* dest_counts, uint32_t segment_rows) {
     if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
     NVMOE_TRY(check_tokens(p, T));
     const nvmoe_geometry& g = p->g;
@@ -872,26 +872,32 @@ int nvmoe_ep_pack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const n
     NVMOE_TRY(check_buffer(p, hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
     NVMOE_TRY(check_buffer(p, routes, R * 4u, "routes"));
     NVMOE_TRY(check_buffer(p, owner_table, (size_t)p->experts * 4u, "owner table"));
-    NVMOE_TRY(check_buffer(p, send_rows, R * g.hidden_size * 2u, "send rows"));
-    NVMOE_TRY(check_buffer(p, send_routes, R * 4u, "send routes"));
+    if (segment_rows != 0u && segment_rows < R)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "segments of %u rows cannot hold the %zu routes one rank may receive",
+                    segment_rows, R);
+    const size_t send_slots = segment_rows ? (size_t)world * segment_rows : R;
+    NVMOE_TRY(check_buffer(p, send_rows, send_slots * g.hidden_size * 2u, "send rows"));
+    NVMOE_TRY(check_buffer(p, send_routes, send_slots * 4u, "send routes"));
     NVMOE_TRY(check_buffer(p, send_index, R * 4u, "send index"));
     NVMOE_TRY(check_buffer(p, dest_counts, (size_t)world * 4u, "destination counts"));
     NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
-    cudaError_t err = p->ep_source.ensure(((size_t)p->g.max_tokens * p->K + 64u) * 4u);
+    cudaError_t err = p->ep_source.ensure(((size_t)p->g.max_tokens * p->K * 2u + 64u) * 4u);
     if (err != cudaSuccess) return fail(p->device, NVMOE_ERR_OUT_OF_MEMORY, "exchange scratch allocation failed: %s", cudaGetErrorString(err));
     if ((size_t)world > (size_t)p->experts + 1u)
         return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "more ranks (%u) than resources (%u)", world, p->experts);
     uint32_t* total = p->ep_source.as<uint32_t>();
     launch_ep_pack((const uint16_t*)hidden->ptr, (const uint32_t*)routes->ptr, (const uint32_t*)owner_table->ptr, T, p->K,
                    g.hidden_size, p->experts, world, rank, (uint16_t*)send_rows->ptr, (uint32_t*)send_routes->ptr,
-                   (uint32_t*)send_index->ptr, total + 64, (uint32_t*)dest_counts->ptr, total, sort_scratch(p),
-                   p->device->stream);
-    p->launches += 3;
+                   (uint32_t*)send_index->ptr, total + 64, (uint32_t*)dest_counts->ptr, total, segment_rows,
+                   total + 64 + (size_t)p->g.max_tokens * p->K, sort_scratch(p), p->device->stream);
+    p->launches += segment_rows ? 2 : 3;
     return post_launch(p, "expert-parallel pack");
 }
 
 int nvmoe_ep_unpack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* returned_rows, const nvmoe_buffer* send_index,
                     nvmoe_buffer* expert_outputs) {
+    // (returned_rows holds at least T*K rows; in the padded layout it holds world * segment_rows and the
+    // positions in send_index are slots of that layout)
     if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
     NVMOE_TRY(check_tokens(p, T));
     const size_t R = (size_t)T * p->K;
@@ -933,13 +939,18 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     NVMOE_TRY(check_tokens(p, T));
     const nvmoe_geometry& g = p->g;
     nvmoe_device* d = p->device;
-    if (!a->router_weights && !a->logits)
-        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "the layer needs router weights or precomputed logits");
+    if (!a->router_weights && !a->logits && !a->routes_in)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "the layer needs router weights, precomputed logits or preselected routes");
     if (a->expert_count && (uint64_t)a->expert_start + a->expert_count > p->experts)
         return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "expert range [%u, %u) exceeds %u resources", a->expert_start,
                     a->expert_start + a->expert_count, p->experts);
     NVMOE_TRY(check_buffer(p, a->hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
-    NVMOE_TRY(check_buffer(p, a->output, (size_t)T * g.hidden_size * 2u, "output"));
+    if (a->expert_outputs) {
+        NVMOE_TRY(check_buffer(p, a->expert_outputs, (size_t)T * p->K * g.hidden_size * 2u, "expert outputs"));
+    } else {
+        NVMOE_TRY(check_buffer(p, a->output, (size_t)T * g.hidden_size * 2u, "output"));
+    }
+    if (a->routes_in) NVMOE_TRY(check_buffer(p, a->routes_in, (size_t)T * p->K * 4u, "routes"));
     NVMOE_TRY(check_expert_tables(p, a->gate_up_addresses, a->gate_up_slots, 4u));
     NVMOE_TRY(check_expert_tables(p, a->down_addresses, a->down_slots, 2u));
     if (a->routes_out) NVMOE_TRY(check_buffer(p, a->routes_out, (size_t)T * p->K * 4u, "routes"));
@@ -955,16 +966,18 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     nvmoe_buffer logits_view{d, p->logits.ptr, p->logits.bytes};
     nvmoe_buffer* logits = a->logits ? a->logits : &logits_view;
     nvmoe_buffer routes_view{d, p->routes.ptr, p->routes.bytes};
-    nvmoe_buffer* routes = a->routes_out ? a->routes_out : &routes_view;
+    nvmoe_buffer* routes = a->routes_in ? const_cast<nvmoe_buffer*>(a->routes_in) : a->routes_out ? a->routes_out : &routes_view;
     nvmoe_buffer frames{d, p->frames.ptr, p->frames.bytes};
     nvmoe_buffer outs{d, p->expert_outputs.ptr, p->expert_outputs.bytes};
+    if (a->expert_outputs) outs = *a->expert_outputs;
     nvmoe_buffer gate_control{d, p->controls.ptr, 28u};
     nvmoe_buffer down_control{d, (char*)p->controls.ptr + 32u, 28u};
 
     mark(kStageLinear);
-    if (a->router_weights) NVMOE_TRY(nvmoe_router_linear(p, T, a->hidden, logits, a->router_weights, a->router_bias));
+    if (a->router_weights && !a->routes_in)
+        NVMOE_TRY(nvmoe_router_linear(p, T, a->hidden, logits, a->router_weights, a->router_bias));
     mark(kStageRoute);
-    NVMOE_TRY(nvmoe_route(p, T, logits, routes, a->bias, a->telemetry));
+    if (!a->routes_in) NVMOE_TRY(nvmoe_route(p, T, logits, routes, a->bias, a->telemetry));
     mark(kStageSchedule);
     const bool tensor = use_tensor_path(p);
     ExpertSet* sets[2] = {nullptr, nullptr};
@@ -1031,7 +1044,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
                           (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, (uint16_t*)outs.ptr, a->down_addresses,
                           a->down_slots, (const uint32_t*)down_control.ptr, true, sets[1], scheduled));
     mark(kStageReduce);
-    NVMOE_TRY(nvmoe_reduce(p, T, &outs, a->output));
+    if (!a->expert_outputs) NVMOE_TRY(nvmoe_reduce(p, T, &outs, a->output));
     mark(kStageCount);
     p->events_valid = true;
     p->report.batch_width = T;

@@ -591,6 +591,37 @@ __global__ void __launch_bounds__(256) ep_gather_rows_kernel(const uint4* __rest
     }
 }
 
+// Padded dispatch layout: destination rank d owns slots [d*cap, (d+1)*cap) of the send buffers, the
+// first dest_counts[d] of them filled in source order, the others marked with an all-ones route word
+// (expert id 0xffff: no scheduler keeps it). Every slot is written, so the buffers can be exchanged
+// with equal splits and no count has to reach the host. One warp per slot.
+__global__ void __launch_bounds__(256) ep_pad_kernel(const uint4* __restrict__ hidden, const uint32_t* __restrict__ routes,
+                                                    const uint32_t* __restrict__ dest_counts,
+                                                    const uint32_t* __restrict__ send_source, uint32_t world, uint32_t cap,
+                                                    uint32_t K, uint32_t row_vec, uint4* __restrict__ rows_out,
+                                                    uint32_t* __restrict__ routes_out, uint32_t* __restrict__ send_index) {
+    const uint32_t warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t slots = world * cap;
+    for (uint32_t slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; slot < slots; slot += warps) {
+        const uint32_t d = slot / cap, j = slot % cap;
+        if (j >= min_u32(dest_counts[d], cap)) {
+            if (lane == 0u) routes_out[slot] = kUnboundSlot;
+            continue;
+        }
+        uint32_t offset = 0u;
+        for (uint32_t x = lane; x < d; x += 32u) offset += dest_counts[x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) offset += __shfl_xor_sync(0xffffffffu, offset, o);
+        const uint32_t i = send_source[offset + j];
+        if (lane == 0u) {
+            routes_out[slot] = routes[i];
+            send_index[i] = slot;
+        }
+        const uint4* from = hidden + (size_t)(i / K) * row_vec;
+        for (uint32_t c = lane; c < row_vec; c += 32u) rows_out[(size_t)slot * row_vec + c] = from[c];
+    }
+}
+
 __global__ void sum_counts_kernel(const uint32_t* counts, uint32_t n, uint32_t* total) {
     if (threadIdx.x == 0u && blockIdx.x == 0u) {
         uint32_t s = 0u;
@@ -606,10 +637,12 @@ constexpr uint32_t kSmallSortLimit = 4096u;
 void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32_t* owner, uint32_t tokens,
                     uint32_t K, uint32_t hidden_size, uint32_t num_experts, uint32_t world, uint32_t self,
                     uint16_t* send_rows, uint32_t* send_routes, uint32_t* send_index, uint32_t* send_source,
-                    uint32_t* dest_counts, uint32_t* total, const SortScratch& scratch, cudaStream_t stream) {
+                    uint32_t* dest_counts, uint32_t* total, uint32_t segment_rows, uint32_t* contiguous_routes,
+                    const SortScratch& scratch, cudaStream_t stream) {
     const uint32_t count = tokens * K;
     DestKey key{routes, owner, num_experts, world, self};
-    PackEmit emit{routes, send_routes, send_index, send_source};
+    // the padded form packs positions only; its route words and rows are placed by ep_pad_kernel
+    PackEmit emit{routes, segment_rows ? contiguous_routes : send_routes, send_index, send_source};
     if (count <= kSmallSortLimit) {
         ep_pack_small_kernel<<<1, count <= 256u ? 256u : 1024u, (world + 1u) * sizeof(uint32_t), stream>>>(key, emit, count,
                                                                                                            dest_counts);
@@ -620,8 +653,16 @@ void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32
         ep_pack_scatter_kernel<<<blocks, 256, world * sizeof(uint32_t), stream>>>(key, emit, count, scratch.block_hist,
                                                                                  scratch.bucket_base, dest_counts);
     }
-    sum_counts_kernel<<<1, 32, 0, stream>>>(dest_counts, world, total);
     const uint32_t row_vec = hidden_size / 8u;  // uint4 per bf16 row
+    if (segment_rows) {
+        uint32_t pad_blocks = (world * segment_rows + 7u) / 8u;
+        if (pad_blocks > 148u * 8u) pad_blocks = 148u * 8u;
+        ep_pad_kernel<<<pad_blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(hidden), routes, dest_counts, send_source,
+                                                      world, segment_rows, K, row_vec, reinterpret_cast<uint4*>(send_rows),
+                                                      send_routes, send_index);
+        return;
+    }
+    sum_counts_kernel<<<1, 32, 0, stream>>>(dest_counts, world, total);
     uint32_t blocks = (count + 7u) / 8u;
     if (blocks > 148u * 8u) blocks = 148u * 8u;
     ep_gather_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(hidden), reinterpret_cast<uint4*>(send_rows),

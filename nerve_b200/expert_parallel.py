@@ -92,11 +92,44 @@ def exchange(ops: ExchangeOps, dist, group=None):
     return n_send, n_recv
 
 
+@dataclass
+class PaddedExchangeOps:
+    """What :func:`exchange_padded` needs from a backend: every buffer has ``world * segment_rows`` rows,
+    segment ``d`` holding what goes to (or came from) rank ``d``; unused slots carry the route word
+    0xffffffff. All tensors are allocated once by the backend."""
+
+    route: callable          # () -> None
+    pack: callable           # () -> (send_rows [G*S,H] int16, send_routes [G*S] int32)
+    compute: callable        # (recv_rows, recv_routes) -> rows [G*S,H] int16, slot for slot
+    unpack_reduce: callable  # (returned_rows [G*S,H]) -> None
+    recv_rows: object
+    recv_routes: object
+    returned: object
+
+
+def exchange_padded(ops: PaddedExchangeOps, dist, group=None):
+    """One layer step with fixed-size segments: three equal-split all-to-alls and no host read in between
+    (for decode-sized batches, where shipping the unused slots costs less than a device-to-host sync)."""
+    import torch
+
+    ops.route()
+    send_rows, send_routes = ops.pack()
+    as_words = lambda t: t.view(torch.int32)  # noqa: E731
+    dist.all_to_all_single(as_words(ops.recv_rows), as_words(send_rows), group=group)
+    dist.all_to_all_single(ops.recv_routes, send_routes, group=group)
+    done = ops.compute(ops.recv_rows, ops.recv_routes)
+    dist.all_to_all_single(as_words(ops.returned), as_words(done), group=group)
+    ops.unpack_reduce(ops.returned)
+
+
+PADDED_EXCHANGE_LIMIT_BYTES = 64 << 20  # send buffer size up to which fixed segments beat a host sync
+
+
 class ExpertParallelLayer:
-    """The GPU backend of :func:`exchange` for one rank."""
+    """The GPU backend of :func:`exchange` / :func:`exchange_padded` for one rank."""
 
     def __init__(self, cfg, tokens_per_rank: int, rank: int, world: int, device_index: int, seed: int = 0,
-                 owner_table: np.ndarray | None = None, expert_path: int = 0):
+                 owner_table: np.ndarray | None = None, expert_path: int = 0, mode: str = "auto", banks: int = 1):
         import torch
 
         from . import synthetic
@@ -109,11 +142,20 @@ class ExpertParallelLayer:
         torch.cuda.set_device(device_index)
         self.tdev = torch.device("cuda", device_index)
         self.device = CudaComputeDevice(device_index)
-        # all launches share the stream NCCL orders against: no events between kernels and collectives
-        self.stream = torch.cuda.current_stream(self.tdev)
+        # kernels and collectives are ordered by one stream: a torch stream of our own (torch's default
+        # stream has handle 0, which the library reads as "use your own stream"), current during step()
+        self.stream = torch.cuda.Stream(device=self.tdev)
         self.device.set_stream(self.stream.cuda_stream)
         T, K, H, G = tokens_per_rank, cfg.total_k, cfg.hidden, world
         self.capacity = T * K * G
+        self.segment = T * K  # the most rows one rank can be sent by one peer
+        if mode == "auto":
+            mode = os.environ.get("NVMOE_EP_MODE", "auto")
+        if mode == "auto":
+            mode = "padded" if self.capacity * H * 2 <= PADDED_EXCHANGE_LIMIT_BYTES else "ragged"
+        if mode not in ("padded", "ragged"):
+            raise ValueError(f"unknown exchange mode {mode!r}")
+        self.mode = mode
         # this rank's tokens: rank r owns tokens [r*T, (r+1)*T) of the global batch
         case = synthetic.make_case(cfg, T * G, seed=seed, with_weights=False)
         self.case = case
@@ -131,7 +173,12 @@ class ExpertParallelLayer:
             w["s3"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
             w["w2"][e] = g.integers(0, 256, (H, I // 2), dtype=np.uint8)
             w["s2"][e] = g.integers(121, 128, (H, I // 32), dtype=np.uint8)
-        self.bank = ExpertBank.upload(self.device, w["w1"], w["s1"], w["w3"], w["s3"], w["w2"], w["s2"], present=mine)
+        # `banks` resident copies of this rank's experts, used in turn (a benchmark's way of keeping the
+        # weights of a step out of L2, as the other layers of a model would)
+        self.banks = [ExpertBank.upload(self.device, w["w1"], w["s1"], w["w3"], w["s3"], w["w2"], w["s2"], present=mine)
+                      for _ in range(max(1, banks))]
+        self.bank = self.banks[0]
+        self.turn = 0
         self.home = MoePlan.for_config(self.device, cfg, T)
         work_cfg = synthetic.MoeConfig(
             cfg.name + "-work", cfg.hidden, cfg.intermediate, cfg.total_experts, 1, swiglu_limit=cfg.swiglu_limit,
@@ -152,8 +199,9 @@ class ExpertParallelLayer:
         self.t_router_w = torch.from_numpy(case.router_w.view(np.int16)).to(self.tdev)
         self.t_logits = dev_tensor((T, (cfg.experts + 1) // 2), i32)
         self.t_routes = dev_tensor((T, K), i32)
-        self.t_send_rows = dev_tensor((T * K, H), i16)
-        self.t_send_routes = dev_tensor((T * K,), i32)
+        send_slots = self.capacity if self.mode == "padded" else T * K
+        self.t_send_rows = dev_tensor((send_slots, H), i16)
+        self.t_send_routes = dev_tensor((send_slots,), i32)
         self.t_send_index = dev_tensor((T * K,), i32)
         self.t_dest_counts = dev_tensor((G,), i32)
         self.t_owner = torch.from_numpy(self.owner.view(np.int32)).to(self.tdev)
@@ -171,6 +219,16 @@ class ExpertParallelLayer:
         self.select_bias = self.device.resident_buffer_from(case.select_bias) if case.select_bias is not None else None
         self.telemetry = self.device.create_resident_buffer(self.home.telemetry_words() * 4)
         self.ops = ExchangeOps(self._route, self._pack, self._compute, self._unpack_reduce, self.capacity)
+        torch.cuda.synchronize(self.tdev)  # the buffers above were filled on torch's default stream
+        if self.mode == "padded":
+            self.t_recv_rows = dev_tensor((self.capacity, H), i16)
+            self.t_recv_routes = dev_tensor((self.capacity,), i32)
+            self.t_returned = dev_tensor((self.capacity, H), i16)
+            for name in ("recv_rows", "recv_routes", "returned"):
+                self.b[name] = wrap(getattr(self, "t_" + name))
+            self.padded_ops = PaddedExchangeOps(self._route, self._pack_padded, self._compute_padded,
+                                                self._unpack_reduce_padded, self.t_recv_rows, self.t_recv_routes,
+                                                self.t_returned)
 
     # -- backend pieces ------------------------------------------------------------------------
     def _route(self):
@@ -216,8 +274,33 @@ class ExpertParallelLayer:
         self.home.moe_reduce(T, self.b["expert_outputs"], self.b["output"])
         rb.destroy()
 
+    # -- fixed-segment form: nothing is read on the host between the kernels ------------------------
+    def _pack_padded(self):
+        b = self.b
+        self.home.ep_pack(self.tokens, b["hidden"], b["routes"], b["owner"], self.world, self.rank, b["send_rows"],
+                          b["send_routes"], b["send_index"], b["dest_counts"], segment_rows=self.segment)
+        return self.t_send_rows, self.t_send_routes
+
+    def _compute_padded(self, recv_rows, recv_routes):
+        # the owner's side of the layer on preselected routes: every resource in range, the slot tables
+        # (unbound for experts of other ranks) keep what this rank owns; padding slots name expert 0xffff
+        b = self.b
+        self.work.layer(self.capacity, self.bank, b["recv_rows"], None, routes_in=b["recv_routes"],
+                        expert_outputs=b["work_out"], expert_start=0, expert_count=self.cfg.total_experts)
+        return self.t_work_out
+
+    def _unpack_reduce_padded(self, returned):
+        self.home.ep_unpack(self.tokens, self.b["returned"], self.b["send_index"], self.b["expert_outputs"])
+        self.home.moe_reduce(self.tokens, self.b["expert_outputs"], self.b["output"])
+
     def step(self, dist, group=None):
-        return exchange(self.ops, dist, group)
+        self.turn += 1
+        self.bank = self.banks[self.turn % len(self.banks)]
+        with self.torch.cuda.stream(self.stream):
+            if self.mode == "padded":
+                exchange_padded(self.padded_ops, dist, group)
+                return self.tokens * self.cfg.total_k, -1
+            return exchange(self.ops, dist, group)
 
     def output(self) -> np.ndarray:
         self.torch.cuda.synchronize()
@@ -237,9 +320,13 @@ def bench_main(args, cfg, tokens, metric, unit):
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path)
-    scratch = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device=f"cuda:{local}")
-    for _ in range(max(args.warmup, 3)):
+    # enough resident copies of this rank's experts that a step's weights were last read 4 x L2 ago
+    per_expert = 3 * cfg.hidden * cfg.intermediate * 17 // 32
+    owned = cfg.experts // world + cfg.always_count
+    touched = max(1, min(tokens * world * cfg.total_k, owned)) * per_expert
+    banks = getattr(args, "banks", 0) or max(2, min(8, -(-4 * 126 * 1024 * 1024 // touched)))
+    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks)
+    for _ in range(max(args.warmup, 3, banks + 1)):
         layer.step(dist)
     torch.cuda.synchronize()
     dist.barrier()
@@ -256,13 +343,12 @@ def bench_main(args, cfg, tokens, metric, unit):
         sampler = ClockSampler(local)
         sampler.start()
     for _ in range(args.steps):
-        scratch.add_(1)
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        start.record()
+        start.record(layer.stream)
         layer.step(dist)
-        stop.record()
+        stop.record(layer.stream)
         torch.cuda.synchronize()
         dist.barrier()
         t = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local}")
@@ -274,15 +360,15 @@ def bench_main(args, cfg, tokens, metric, unit):
     host_out = torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory()
     e2e = []
     for _ in range(args.steps):
-        scratch.add_(1)
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        start.record()
-        layer.t_hidden.copy_(host_in, non_blocking=True)
-        layer.step(dist)
-        host_out.copy_(layer.t_output, non_blocking=True)
-        stop.record()
+        start.record(layer.stream)
+        with torch.cuda.stream(layer.stream):
+            layer.t_hidden.copy_(host_in, non_blocking=True)
+            layer.step(dist)
+            host_out.copy_(layer.t_output, non_blocking=True)
+        stop.record(layer.stream)
         torch.cuda.synchronize()
         t = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -299,7 +385,9 @@ def bench_main(args, cfg, tokens, metric, unit):
                        "experts_per_rank": cfg.experts // world,
                        "parallelism": f"ep{world}: experts sharded by contiguous range, tokens data-parallel, "
                                       "NCCL all-to-all dispatch and combine",
-                       "l2": "256 MB buffer rewritten between timed steps"},
+                       "exchange": layer.mode,
+                       "l2": f"inputs larger than L2: {banks} resident weight banks per rank visited in turn, "
+                             f"{touched * banks / 1e6:.0f} MB of weights read between two reads of the same bytes"},
             "clocks": clocks,
             "e2e": {"value": total_tokens / (statistics.mean(e2e) * 1e-3), "unit": unit,
                     "h2d_bytes_per_step": tokens * cfg.hidden * 2, "d2h_bytes_per_step": tokens * cfg.hidden * 2,

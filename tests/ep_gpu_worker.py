@@ -28,17 +28,18 @@ def main() -> int:
                               swiglu_limit=7.0, swiglu_alpha=1.702, swiglu_up_offset=1.0)
     failures = 0
     for path in (1, 2):
-        layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path)
-        for _ in range(2):  # the second step reuses every buffer
-            sent, received = layer.step(dist)
-        got = layer.output()
         alone = LayerRunner(cfg, tokens * world, 5, path, device_index=local, banks=1)
         alone.plan.layer(tokens * world, alone.bank, alone.hidden, alone.output, **alone.kw)
         want = alone.output.read(np.uint16).reshape(tokens * world, cfg.hidden)[rank * tokens:(rank + 1) * tokens]
-        same = np.array_equal(got, want)
-        print(f"rank {rank} path {path}: sent {sent} received {received} parity {'ok' if same else 'FAILED'} "
-              f"({int((got != want).sum())} of {got.size} values differ)", flush=True)
-        failures += 0 if same else 1
+        for mode in ("ragged", "padded"):  # split sizes read on the host / fixed segments, no host read
+            layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path, mode=mode)
+            for _ in range(2):  # the second step reuses every buffer
+                sent, received = layer.step(dist)
+            got = layer.output()
+            same = np.array_equal(got, want)
+            print(f"rank {rank} path {path} {mode}: sent {sent} received {received} parity {'ok' if same else 'FAILED'} "
+                  f"({int((got != want).sum())} of {got.size} values differ)", flush=True)
+            failures += 0 if same else 1
     flag = torch.tensor([failures], device=f"cuda:{local}")
     dist.all_reduce(flag)
     dist.destroy_process_group()

@@ -96,6 +96,46 @@ class CpuOps:
         self.output = self.mo.reduce(expert_outputs, self.T, cfg.total_k, cfg.hidden, 1.0)
 
 
+    # -- fixed-segment form -------------------------------------------------------------------
+    def padded_ops(self):
+        torch = self.torch
+        S, G, H = self.T * self.cfg.total_k, self.world, self.cfg.hidden
+        self.segment = S
+        zeros = lambda *shape: torch.zeros(shape, dtype=torch.int16)  # noqa: E731
+        return ep.PaddedExchangeOps(self.route, self.pack_padded, self.compute_padded, self.unpack_reduce_padded,
+                                    zeros(G * S, H), torch.zeros(G * S, dtype=torch.int32), zeros(G * S, H))
+
+    def pack_padded(self):
+        torch, S, G = self.torch, self.segment, self.world
+        rows, routes, counts = self.pack()
+        rows, routes, counts = rows.numpy(), routes.numpy(), counts.numpy()
+        out_rows = np.zeros((G * S, self.cfg.hidden), dtype=np.int16)
+        out_routes = np.full(G * S, -1, dtype=np.int32)  # 0xffffffff
+        slot_of = np.empty(rows.shape[0], dtype=np.int64)
+        start = 0
+        for d in range(G):
+            n = int(counts[d])
+            out_rows[d * S:d * S + n] = rows[start:start + n]
+            out_routes[d * S:d * S + n] = routes[start:start + n]
+            slot_of[start:start + n] = d * S + np.arange(n)
+            start += n
+        self.send_index = slot_of[self.send_index]
+        return torch.from_numpy(out_rows), torch.from_numpy(out_routes)
+
+    def compute_padded(self, recv_rows, recv_routes):
+        torch = self.torch
+        routes = recv_routes.numpy().view(np.uint32)
+        valid = np.nonzero(routes != 0xFFFFFFFF)[0]
+        out = np.zeros((routes.size, self.cfg.hidden), dtype=np.int16)
+        if valid.size:
+            done = self.compute(recv_rows[torch.from_numpy(valid)], recv_routes[torch.from_numpy(valid)], valid.size)
+            out[valid] = done.numpy()[:valid.size]
+        return torch.from_numpy(out)
+
+    def unpack_reduce_padded(self, returned):
+        self.unpack_reduce(returned)
+
+
 def _worker(rank, world, port, cfg_name, small, tokens, mode, result_dir):
     import torch.distributed as dist
 
@@ -115,7 +155,11 @@ def _worker(rank, world, port, cfg_name, small, tokens, mode, result_dir):
                 np.save(Path(result_dir) / f"err{rank}.npy", np.array([1]))
                 assert "receive buffers hold" in str(error)
             return
-        sent, received = ep.exchange(ops, dist)
+        if mode == "padded":
+            ep.exchange_padded(backend.padded_ops(), dist)
+            sent = received = tokens * cfg.total_k
+        else:
+            sent, received = ep.exchange(ops, dist)
         np.save(Path(result_dir) / f"out{rank}.npy", backend.output)
         np.save(Path(result_dir) / f"counts{rank}.npy", np.array([sent, received]))
     finally:
@@ -128,14 +172,15 @@ def _spawn(cfg_name, small, tokens, mode, tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), cfg_name, small, tokens, mode, str(tmp_path)), nprocs=2, join=True)
 
 
+@pytest.mark.parametrize("mode", ["run", "padded"])
 @pytest.mark.parametrize("cfg_name,small", [("gpt-oss-120b", (64, 96, 8)), ("deepseek-v3", (128, 128, 16))])
-def test_sharded_layer_equals_unsharded_layer(tmp_path, cfg_name, small):
+def test_sharded_layer_equals_unsharded_layer(tmp_path, cfg_name, small, mode):
     pytest.importorskip("torch")
     from oracle import moe_oracle as mo
     from tests.helpers import oracle_layer
 
     tokens = 6
-    _spawn(cfg_name, small, tokens, "run", tmp_path)
+    _spawn(cfg_name, small, tokens, mode, tmp_path)
     cfg = synthetic.small_variant(synthetic.CONFIGS[cfg_name], *small)
     case = synthetic.make_case(cfg, tokens * 2, seed=1)
     want = oracle_layer(case, tier=1)["output"]

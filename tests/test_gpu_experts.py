@@ -332,3 +332,52 @@ def test_expert_ranges_partition_the_layer(device, path):
     ref = mo.bf16_to_f32(want["output"]).astype(np.float64)
     assert np.abs(acc - ref).max() <= 0.05 * np.abs(ref).max()
     plan.destroy()
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_preselected_routes_form_reproduces_the_layer(device, path):
+    """The owner's side of an expert-parallel exchange: the routes of a finished router arrive as rows
+    of a top-1 plan (one hidden row and one route word per slot, unused slots marked 0xffffffff), the
+    per-route rows come back instead of the combined output, and combining them reproduces the
+    ordinary layer call bit for bit."""
+    cfg = synthetic.small_variant(synthetic.CONFIGS["gpt-oss-120b"], 256, 384, 16)
+    tokens, K, H = 24, cfg.total_k, cfg.hidden
+    case = synthetic.make_case(cfg, tokens, seed=8)
+    plan = make_plan(device, cfg, tokens, path)
+    bank = ExpertBank.upload(device, case.w1, case.s1, case.w3, case.s3, case.w2, case.s2)
+    hidden = device.resident_buffer_from(case.hidden)
+    rw = device.resident_buffer_from(case.router_w)
+    rbias = device.resident_buffer_from(case.router_bias)
+    out = device.create_resident_buffer(tokens * H * 2)
+    routes_buf = device.create_resident_buffer(tokens * K * 4)
+    plan.layer(tokens, bank, hidden, out, router_weights=rw, router_bias=rbias, routes_out=routes_buf)
+    want = out.read(np.uint16).reshape(tokens, H).copy()
+    routes = routes_buf.read(np.uint32).copy()
+
+    # slots: every route twice over with gaps (slot 3*i holds route i), the rest unused
+    slots = 3 * tokens * K + 5
+    work_cfg = synthetic.MoeConfig(name="work", hidden=H, intermediate=cfg.intermediate, experts=cfg.total_experts, k=1,
+                                   swiglu_limit=cfg.swiglu_limit, swiglu_alpha=cfg.swiglu_alpha,
+                                   swiglu_up_offset=cfg.swiglu_up_offset, act_block=cfg.act_block)
+    work = make_plan(device, work_cfg, slots, path)
+    rows = np.zeros((slots, H), dtype=np.uint16)
+    words = np.full(slots, 0xFFFFFFFF, dtype=np.uint32)
+    where = 3 * np.arange(tokens * K)
+    rows[where] = case.hidden[np.arange(tokens * K) // K]
+    words[where] = routes
+    rows_buf, words_buf = device.resident_buffer_from(rows), device.resident_buffer_from(words)
+    per_slot = device.create_resident_buffer(slots * H * 2)
+    for call in range(2):
+        per_slot.fill(0x55)
+        work.layer(slots, bank, rows_buf, None, routes_in=words_buf, expert_outputs=per_slot, expert_start=0,
+                   expert_count=cfg.total_experts)
+        got_rows = per_slot.read(np.uint16).reshape(slots, H)
+        assert work.status() == 0
+        expert_outputs = device.resident_buffer_from(np.ascontiguousarray(got_rows[where]))
+        combined = device.create_resident_buffer(tokens * H * 2)
+        plan.moe_reduce(tokens, expert_outputs, combined)
+        np.testing.assert_array_equal(combined.read(np.uint16).reshape(tokens, H), want, err_msg=f"call {call}")
+        unused = np.setdiff1d(np.arange(slots), where)
+        assert not got_rows[unused].any(), "slots without a route must come back as zero rows"
+    plan.destroy()
+    work.destroy()
