@@ -352,6 +352,48 @@ int nvmoe_ep_pack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hi
 int nvmoe_ep_unpack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* returned_rows,
                     const nvmoe_buffer* send_index, nvmoe_buffer* expert_outputs);
 
+/*
+ * The expert-parallel layer with the collectives inside the call: one process per GPU, each opening
+ * its device, creating its plans and joining the same communicator. NCCL is bound at run time (the
+ * libnccl.so.2 already in the process, else the system's).
+ *
+ *   rank 0:      nvmoe_ep_unique_id(id)        then hands the 128 bytes to every rank (any transport)
+ *   every rank:  nvmoe_ep_create(device, id, rank, world, &ep)     collective: all ranks must call it
+ *   per step:    nvmoe_ep_layer(ep, home, work, &args)             collective
+ *
+ * `home` is the plan of this rank's tokens (the layer's geometry, max_tokens the same on every
+ * rank); `work` the owner-side plan: top_k 1 over the same experts and sizes, max_tokens at least
+ * world_size * home.max_tokens * home.top_k. The slot tables name the experts this rank holds
+ * (0xffffffff for the others); owner_table[expert] is the rank holding each expert (0xffffffff =
+ * replicated, kept local). One step is: projection and router on the rank's tokens, rows placed in
+ * fixed segments per owner (nvmoe_ep_pack with segment_rows), one grouped send/receive of rows and
+ * route words, the preselected-route form of nvmoe_layer on the received rows, one grouped
+ * send/receive back, nvmoe_ep_unpack and the combine. Nothing is read on the host; everything is
+ * ordered on the device's stream. The result equals the single-device layer bit for bit.
+ * The reference shards this layer by expert range with the hidden frame replicated
+ * (runtime-rs/src/vulkan_distributed/execution_plans.rs:1201-1205); it has no counterpart of the
+ * exchange.
+ */
+typedef struct nvmoe_ep nvmoe_ep;
+typedef struct nvmoe_ep_layer_args {
+    uint32_t batch_width;               /* tokens of this rank in this step */
+    const nvmoe_buffer* hidden;         /* [batch_width][hidden] bf16 */
+    const nvmoe_buffer* router_weights;
+    const nvmoe_buffer* router_bias;    /* optional */
+    const nvmoe_buffer* bias;           /* selection bias, optional */
+    const nvmoe_buffer* owner_table;    /* [experts] u32 */
+    const nvmoe_buffer* gate_up_addresses;
+    const nvmoe_buffer* gate_up_slots;
+    const nvmoe_buffer* down_addresses;
+    const nvmoe_buffer* down_slots;
+    nvmoe_buffer* output;               /* [batch_width][hidden] bf16 */
+    nvmoe_buffer* telemetry;            /* optional */
+} nvmoe_ep_layer_args;
+int nvmoe_ep_unique_id(void* id128);
+int nvmoe_ep_create(nvmoe_device* device, const void* id128, uint32_t rank, uint32_t world_size, nvmoe_ep** out);
+void nvmoe_ep_destroy(nvmoe_ep* ep);
+int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe_ep_layer_args* args);
+
 #ifdef __cplusplus
 }
 #endif

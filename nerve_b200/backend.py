@@ -177,6 +177,41 @@ class ExpertBank:
                           address_table(device, dres), device.resident_buffer_from(dslots))
 
 
+class ExpertParallelGroup:
+    """This rank's membership of an expert-parallel communicator held by the library (NCCL)."""
+
+    @staticmethod
+    def unique_id() -> bytes:
+        """Rank 0 makes the id; every rank needs the same 128 bytes to join."""
+        buf = ctypes.create_string_buffer(128)
+        rc = capi.load().nvmoe_ep_unique_id(buf)
+        if rc != 0:
+            raise CudaError(rc, capi.load().nvmoe_last_error(None).decode(errors="replace"))
+        return buf.raw
+
+    def __init__(self, device: CudaComputeDevice, unique_id: bytes, rank: int, world_size: int):
+        assert len(unique_id) == 128
+        self.device, self.rank, self.world_size = device, rank, world_size
+        handle = ctypes.c_void_p()
+        device._check(device._lib.nvmoe_ep_create(device._h, unique_id, rank, world_size, ctypes.byref(handle)))
+        self._h = handle
+
+    def layer(self, home: "MoePlan", work: "MoePlan", batch_width, bank: "ExpertBank", hidden, output, owner_table,
+              router_weights, router_bias=None, bias=None, telemetry=None) -> None:
+        a = capi.EpLayerArgs()
+        a.batch_width = batch_width
+        a.hidden, a.output, a.owner_table = _h(hidden), _h(output), _h(owner_table)
+        a.router_weights, a.router_bias, a.bias, a.telemetry = _h(router_weights), _h(router_bias), _h(bias), _h(telemetry)
+        a.gate_up_addresses, a.gate_up_slots = _h(bank.gate_up_addresses), _h(bank.gate_up_slots)
+        a.down_addresses, a.down_slots = _h(bank.down_addresses), _h(bank.down_slots)
+        self.device._check(self.device._lib.nvmoe_ep_layer(self._h, home._h, work._h, ctypes.byref(a)))
+
+    def destroy(self) -> None:
+        if self._h:
+            self.device._lib.nvmoe_ep_destroy(self._h)
+            self._h = None
+
+
 def geometry_from_config(cfg: MoeConfig, max_tokens: int) -> capi.Geometry:
     g = capi.Geometry()
     capi.load().nvmoe_geometry_default(ctypes.byref(g), cfg.hidden, cfg.intermediate, cfg.experts, cfg.k)

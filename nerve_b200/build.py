@@ -70,7 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         sys.stderr.write("\n".join(logs) + "\n")
     if failed:
         raise RuntimeError(f"nvcc failed on {failed}")
-    link = [nvcc, "-shared", "-ccbin", host, "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH), *objs]
+    link = [nvcc, "-shared", "-ccbin", host, "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH), *objs, "-ldl"]
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
     if res.returncode != 0:
         sys.stderr.write(res.stdout)

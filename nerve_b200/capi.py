@@ -40,6 +40,14 @@ class LayerArgs(ctypes.Structure):
     ]
 
 
+class EpLayerArgs(ctypes.Structure):
+    _fields_ = [
+        ("batch_width", c_uint32), ("hidden", c_void_p), ("router_weights", c_void_p), ("router_bias", c_void_p),
+        ("bias", c_void_p), ("owner_table", c_void_p), ("gate_up_addresses", c_void_p), ("gate_up_slots", c_void_p),
+        ("down_addresses", c_void_p), ("down_slots", c_void_p), ("output", c_void_p), ("telemetry", c_void_p),
+    ]
+
+
 class WorkReport(ctypes.Structure):
     _fields_ = [
         ("total_ms", c_float), ("stage_ms", c_float * 8), ("gate_up_kernel_ms", c_float),
@@ -90,6 +98,10 @@ PROTOTYPES = {
     "nvmoe_ep_pack": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_uint32]),
     "nvmoe_ep_unpack": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "nvmoe_ep_unique_id": (c_int, [c_void_p]),
+    "nvmoe_ep_create": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, POINTER(c_void_p)]),
+    "nvmoe_ep_destroy": (None, [c_void_p]),
+    "nvmoe_ep_layer": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(EpLayerArgs)]),
 }
 
 _lib = None

@@ -11,7 +11,11 @@
 #include <new>
 #include <string>
 #include <thread>
+#include <type_traits>
 #include <vector>
+
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include "common.cuh"
 #include "experts_tc.cuh"
@@ -1139,6 +1143,210 @@ int nvmoe_plan_last_report(nvmoe_plan* p, nvmoe_work_report* report) {
     p->report.weight_bytes_touched = per_expert * distinct;
     *report = p->report;
     return NVMOE_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel layer with the collectives issued by the library.
+//
+// NCCL is bound at run time: the copy already loaded into the process (a framework's) if there is
+// one, else the system's libnccl.so.2. Only point-to-point calls inside groups are used, so the two
+// exchanges of a step are one NCCL kernel each, on the stream the compute kernels use.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct NcclApi {
+    void* lib = nullptr;
+    decltype(&ncclGetUniqueId) get_unique_id = nullptr;
+    decltype(&ncclCommInitRank) comm_init_rank = nullptr;
+    decltype(&ncclCommDestroy) comm_destroy = nullptr;
+    decltype(&ncclGroupStart) group_start = nullptr;
+    decltype(&ncclGroupEnd) group_end = nullptr;
+    decltype(&ncclSend) send = nullptr;
+    decltype(&ncclRecv) recv = nullptr;
+    decltype(&ncclGetErrorString) error_string = nullptr;
+    std::string problem;
+};
+
+const NcclApi& nccl_api() {
+    static const NcclApi api = [] {
+        NcclApi a;
+        a.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+        if (!a.lib) a.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+        if (!a.lib) {
+            a.problem = std::string("libnccl.so.2 could not be loaded: ") + dlerror();
+            return a;
+        }
+        auto bind = [&](auto& fn, const char* name) {
+            fn = reinterpret_cast<std::remove_reference_t<decltype(fn)>>(dlsym(a.lib, name));
+            if (!fn && a.problem.empty()) a.problem = std::string("libnccl.so.2 lacks ") + name;
+        };
+        bind(a.get_unique_id, "ncclGetUniqueId");
+        bind(a.comm_init_rank, "ncclCommInitRank");
+        bind(a.comm_destroy, "ncclCommDestroy");
+        bind(a.group_start, "ncclGroupStart");
+        bind(a.group_end, "ncclGroupEnd");
+        bind(a.send, "ncclSend");
+        bind(a.recv, "ncclRecv");
+        bind(a.error_string, "ncclGetErrorString");
+        return a;
+    }();
+    return api;
+}
+
+}  // namespace
+
+struct nvmoe_ep {
+    nvmoe_device* device = nullptr;
+    ncclComm_t comm = nullptr;
+    uint32_t rank = 0, world = 1;
+    // exchange buffers, sized on first use from the plans' geometry
+    DeviceArray logits, routes, send_rows, send_routes, recv_rows, recv_routes, work_out, returned, send_index,
+        dest_counts, expert_outputs;
+};
+
+namespace {
+
+#define NVMOE_NCCL(d, call)                                                                               \
+    do {                                                                                                  \
+        ncclResult_t r__ = (call);                                                                        \
+        if (r__ != ncclSuccess)                                                                           \
+            return fail((d), NVMOE_ERR_COLLECTIVE, "%s failed: %s", #call, nccl_api().error_string(r__)); \
+    } while (0)
+
+// every rank sends segment `peer` of `send` to rank `peer` and receives segment `peer` of `recv` from it
+int exchange_segments(nvmoe_ep* ep, const void* send_a, void* recv_a, size_t bytes_a, const void* send_b, void* recv_b,
+                      size_t bytes_b) {
+    const NcclApi& n = nccl_api();
+    nvmoe_device* d = ep->device;
+    NVMOE_NCCL(d, n.group_start());
+    for (uint32_t peer = 0; peer < ep->world; peer++) {
+        NVMOE_NCCL(d, n.send((const char*)send_a + peer * bytes_a, bytes_a, ncclInt8, (int)peer, ep->comm, d->stream));
+        NVMOE_NCCL(d, n.recv((char*)recv_a + peer * bytes_a, bytes_a, ncclInt8, (int)peer, ep->comm, d->stream));
+        if (send_b) {
+            NVMOE_NCCL(d, n.send((const char*)send_b + peer * bytes_b, bytes_b, ncclInt8, (int)peer, ep->comm, d->stream));
+            NVMOE_NCCL(d, n.recv((char*)recv_b + peer * bytes_b, bytes_b, ncclInt8, (int)peer, ep->comm, d->stream));
+        }
+    }
+    NVMOE_NCCL(d, n.group_end());
+    return NVMOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvmoe_ep_unique_id(void* id128) {
+    if (!id128) return NVMOE_ERR_INVALID_ARGUMENT;
+    const NcclApi& n = nccl_api();
+    if (!n.problem.empty()) return fail(nullptr, NVMOE_ERR_COLLECTIVE, "%s", n.problem.c_str());
+    static_assert(sizeof(ncclUniqueId) == 128, "the id travels as 128 bytes");
+    ncclUniqueId id;
+    ncclResult_t r = n.get_unique_id(&id);
+    if (r != ncclSuccess) return fail(nullptr, NVMOE_ERR_COLLECTIVE, "ncclGetUniqueId failed: %s", n.error_string(r));
+    std::memcpy(id128, &id, 128);
+    return NVMOE_OK;
+}
+
+int nvmoe_ep_create(nvmoe_device* d, const void* id128, uint32_t rank, uint32_t world, nvmoe_ep** out) {
+    if (!d || !id128 || !out) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (world == 0u || world > 1024u || rank >= world)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "rank %u of %u is not a valid expert-parallel position", rank, world);
+    const NcclApi& n = nccl_api();
+    if (!n.problem.empty()) return fail(d, NVMOE_ERR_COLLECTIVE, "%s", n.problem.c_str());
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    nvmoe_ep* ep = new (std::nothrow) nvmoe_ep();
+    if (!ep) return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "out of host memory");
+    ep->device = d;
+    ep->rank = rank;
+    ep->world = world;
+    ncclUniqueId id;
+    std::memcpy(&id, id128, 128);
+    ncclResult_t r = n.comm_init_rank(&ep->comm, (int)world, id, (int)rank);
+    if (r != ncclSuccess) {
+        delete ep;
+        return fail(d, NVMOE_ERR_COLLECTIVE, "ncclCommInitRank failed: %s", n.error_string(r));
+    }
+    *out = ep;
+    return NVMOE_OK;
+}
+
+void nvmoe_ep_destroy(nvmoe_ep* ep) {
+    if (!ep) return;
+    cudaSetDevice(ep->device->ordinal);
+    cudaStreamSynchronize(ep->device->stream);
+    if (ep->comm) nccl_api().comm_destroy(ep->comm);
+    DeviceArray* all[] = {&ep->logits, &ep->routes, &ep->send_rows, &ep->send_routes, &ep->recv_rows, &ep->recv_routes,
+                          &ep->work_out, &ep->returned, &ep->send_index, &ep->dest_counts, &ep->expert_outputs};
+    for (DeviceArray* a : all) a->release();
+    delete ep;
+}
+
+int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe_ep_layer_args* a) {
+    if (!ep || !home || !work || !a) return NVMOE_ERR_INVALID_ARGUMENT;
+    nvmoe_device* d = ep->device;
+    if (home->device != d || work->device != d)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "the plans belong to another device than the communicator");
+    const uint32_t T = a->batch_width, K = home->K, G = ep->world;
+    NVMOE_TRY(check_tokens(home, T));
+    const size_t H = home->g.hidden_size;
+    const size_t S = (size_t)home->g.max_tokens * K;  // slots per peer: the same on every rank
+    if (work->K != 1u || work->g.hidden_size != home->g.hidden_size || work->g.intermediate_size != home->g.intermediate_size ||
+        work->experts != home->experts || (size_t)work->g.max_tokens < S * G)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT,
+                    "the owner-side plan must be top-1 over the same experts and sizes with room for %zu rows", S * G);
+    if (!a->owner_table || !a->hidden || !a->output || !a->router_weights)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "hidden, router weights, owner table and output are required");
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    cudaError_t err = cudaSuccess;
+    auto want = [&](DeviceArray& arr, size_t bytes) {
+        if (err == cudaSuccess) err = arr.ensure(bytes);
+    };
+    const size_t Tm = home->g.max_tokens;
+    want(ep->logits, Tm * ((home->g.routed_experts + 1u) / 2u) * 4u);
+    want(ep->routes, Tm * K * 4u);
+    want(ep->send_rows, G * S * H * 2u);
+    want(ep->send_routes, G * S * 4u);
+    want(ep->recv_rows, G * S * H * 2u);
+    want(ep->recv_routes, G * S * 4u);
+    want(ep->work_out, G * S * H * 2u);
+    want(ep->returned, G * S * H * 2u);
+    want(ep->send_index, S * 4u);
+    want(ep->dest_counts, (size_t)G * 4u);
+    want(ep->expert_outputs, S * H * 2u);
+    if (err != cudaSuccess)
+        return fail(d, err == cudaErrorMemoryAllocation ? NVMOE_ERR_OUT_OF_MEMORY : NVMOE_ERR_CUDA,
+                    "exchange buffer allocation failed: %s", cudaGetErrorString(err));
+    auto view = [&](DeviceArray& arr) { return nvmoe_buffer{d, arr.ptr, arr.bytes}; };
+    nvmoe_buffer logits = view(ep->logits), routes = view(ep->routes), send_rows = view(ep->send_rows),
+                 send_routes = view(ep->send_routes), recv_rows = view(ep->recv_rows), recv_routes = view(ep->recv_routes),
+                 work_out = view(ep->work_out), returned = view(ep->returned), send_index = view(ep->send_index),
+                 dest_counts = view(ep->dest_counts), expert_outputs = view(ep->expert_outputs);
+
+    // this rank's tokens: route, then place every route's row in the segment of the rank owning its expert
+    NVMOE_TRY(nvmoe_router_linear(home, T, a->hidden, &logits, a->router_weights, a->router_bias));
+    NVMOE_TRY(nvmoe_route(home, T, &logits, &routes, a->bias, a->telemetry));
+    NVMOE_TRY(nvmoe_ep_pack(home, T, a->hidden, &routes, a->owner_table, G, ep->rank, &send_rows, &send_routes, &send_index,
+                            &dest_counts, (uint32_t)S));
+    NVMOE_TRY(exchange_segments(ep, send_rows.ptr, recv_rows.ptr, S * H * 2u, send_routes.ptr, recv_routes.ptr, S * 4u));
+    // the rows this rank owns the experts of: every resource in range, the slot tables keep the owned ones
+    nvmoe_layer_args owner{};
+    owner.batch_width = (uint32_t)(S * G);
+    owner.expert_start = 0u;
+    owner.expert_count = work->experts;
+    owner.hidden = &recv_rows;
+    owner.routes_in = &recv_routes;
+    owner.expert_outputs = &work_out;
+    owner.gate_up_addresses = a->gate_up_addresses;
+    owner.gate_up_slots = a->gate_up_slots;
+    owner.down_addresses = a->down_addresses;
+    owner.down_slots = a->down_slots;
+    NVMOE_TRY(nvmoe_layer(work, &owner));
+    NVMOE_TRY(exchange_segments(ep, work_out.ptr, returned.ptr, S * H * 2u, nullptr, nullptr, 0u));
+    NVMOE_TRY(nvmoe_ep_unpack(home, T, &returned, &send_index, &expert_outputs));
+    return nvmoe_reduce(home, T, &expert_outputs, a->output);
 }
 
 }  // extern "C"

@@ -129,7 +129,12 @@ class ExpertParallelLayer:
     """The GPU backend of :func:`exchange` / :func:`exchange_padded` for one rank."""
 
     def __init__(self, cfg, tokens_per_rank: int, rank: int, world: int, device_index: int, seed: int = 0,
-                 owner_table: np.ndarray | None = None, expert_path: int = 0, mode: str = "auto", banks: int = 1):
+                 owner_table: np.ndarray | None = None, expert_path: int = 0, mode: str = "auto", banks: int = 1,
+                 dist=None):
+        """mode: "native" = the library issues the collectives itself (one call per step, needs `dist` once to
+        hand the communicator id round); "padded" / "ragged" = the same protocol over torch.distributed with
+        fixed segments / with split sizes read on the host; "auto" = native when `dist` is given and the
+        fixed segments are small enough, else padded or ragged by size."""
         import torch
 
         from . import synthetic
@@ -152,9 +157,12 @@ class ExpertParallelLayer:
         if mode == "auto":
             mode = os.environ.get("NVMOE_EP_MODE", "auto")
         if mode == "auto":
-            mode = "padded" if self.capacity * H * 2 <= PADDED_EXCHANGE_LIMIT_BYTES else "ragged"
-        if mode not in ("padded", "ragged"):
+            small = self.capacity * H * 2 <= PADDED_EXCHANGE_LIMIT_BYTES
+            mode = ("native" if dist is not None else "padded") if small else "ragged"
+        if mode not in ("native", "padded", "ragged"):
             raise ValueError(f"unknown exchange mode {mode!r}")
+        if mode == "native" and dist is None:
+            raise ValueError("the native exchange needs torch.distributed once, to share the communicator id")
         self.mode = mode
         # this rank's tokens: rank r owns tokens [r*T, (r+1)*T) of the global batch
         case = synthetic.make_case(cfg, T * G, seed=seed, with_weights=False)
@@ -220,6 +228,14 @@ class ExpertParallelLayer:
         self.telemetry = self.device.create_resident_buffer(self.home.telemetry_words() * 4)
         self.ops = ExchangeOps(self._route, self._pack, self._compute, self._unpack_reduce, self.capacity)
         torch.cuda.synchronize(self.tdev)  # the buffers above were filled on torch's default stream
+        if self.mode == "native":
+            from .backend import ExpertParallelGroup
+
+            id_bytes = torch.zeros(128, dtype=torch.uint8, device=self.tdev)
+            if rank == 0:
+                id_bytes.copy_(torch.frombuffer(bytearray(ExpertParallelGroup.unique_id()), dtype=torch.uint8))
+            dist.broadcast(id_bytes, 0)
+            self.group = ExpertParallelGroup(self.device, bytes(id_bytes.cpu().numpy().tobytes()), rank, world)
         if self.mode == "padded":
             self.t_recv_rows = dev_tensor((self.capacity, H), i16)
             self.t_recv_routes = dev_tensor((self.capacity,), i32)
@@ -296,6 +312,11 @@ class ExpertParallelLayer:
     def step(self, dist, group=None):
         self.turn += 1
         self.bank = self.banks[self.turn % len(self.banks)]
+        if self.mode == "native":
+            b = self.b
+            self.group.layer(self.home, self.work, self.tokens, self.bank, b["hidden"], b["output"], b["owner"],
+                             b["router_w"], self.router_bias, self.select_bias, self.telemetry)
+            return self.tokens * self.cfg.total_k, -1
         with self.torch.cuda.stream(self.stream):
             if self.mode == "padded":
                 exchange_padded(self.padded_ops, dist, group)
@@ -325,7 +346,8 @@ def bench_main(args, cfg, tokens, metric, unit):
     owned = cfg.experts // world + cfg.always_count
     touched = max(1, min(tokens * world * cfg.total_k, owned)) * per_expert
     banks = getattr(args, "banks", 0) or max(2, min(8, -(-4 * 126 * 1024 * 1024 // touched)))
-    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks)
+    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks,
+                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"))
     for _ in range(max(args.warmup, 3, banks + 1)):
         layer.step(dist)
     torch.cuda.synchronize()
@@ -342,37 +364,40 @@ def bench_main(args, cfg, tokens, metric, unit):
 
         sampler = ClockSampler(local)
         sampler.start()
+    # exactly `steps` steps back to back between two events on the stream they run on, a barrier and a
+    # synchronise on both sides, the slowest rank's time
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    start.record(layer.stream)
     for _ in range(args.steps):
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        start.record(layer.stream)
         layer.step(dist)
-        stop.record(layer.stream)
-        torch.cuda.synchronize()
-        dist.barrier()
-        t = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        times.append(float(t.item()))
+    stop.record(layer.stream)
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([start.elapsed_time(stop) / args.steps], device=f"cuda:{local}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    times.append(float(t.item()))
     clocks = sampler.stop() if sampler else None
     # end to end: tokens start in pinned host memory, the result is read back
     host_in = torch.from_numpy(layer.hidden_host.view(np.int16)).pin_memory()
     host_out = torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory()
     e2e = []
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    start.record(layer.stream)
     for _ in range(args.steps):
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        start.record(layer.stream)
         with torch.cuda.stream(layer.stream):
             layer.t_hidden.copy_(host_in, non_blocking=True)
             layer.step(dist)
             host_out.copy_(layer.t_output, non_blocking=True)
-        stop.record(layer.stream)
-        torch.cuda.synchronize()
-        t = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e.append(float(t.item()))
+    stop.record(layer.stream)
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([start.elapsed_time(stop) / args.steps], device=f"cuda:{local}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e.append(float(t.item()))
     ms = statistics.mean(times)
     if rank == 0:
         total_tokens = tokens * world

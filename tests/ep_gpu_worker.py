@@ -31,8 +31,9 @@ def main() -> int:
         alone = LayerRunner(cfg, tokens * world, 5, path, device_index=local, banks=1)
         alone.plan.layer(tokens * world, alone.bank, alone.hidden, alone.output, **alone.kw)
         want = alone.output.read(np.uint16).reshape(tokens * world, cfg.hidden)[rank * tokens:(rank + 1) * tokens]
-        for mode in ("ragged", "padded"):  # split sizes read on the host / fixed segments, no host read
-            layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path, mode=mode)
+        # split sizes read on the host / fixed segments over torch.distributed / the library's own collectives
+        for mode in ("ragged", "padded", "native"):
+            layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path, mode=mode, dist=dist)
             for _ in range(2):  # the second step reuses every buffer
                 sent, received = layer.step(dist)
             got = layer.output()
