@@ -153,29 +153,27 @@ NVMOE_HD uint32_t nvmoe_rounded_fp8_scale_e8m0(float block_max) {
 
 /* 2^n * y for integer n in [-300, 300], done as two exact-or-once-rounded multiplies. */
 NVMOE_HD float nvmoe_scalbn(float y, int n) {
-    if (n > 254) n = 254;
-    if (n < -300) n = -300;
+    /* straight-line code (selects, no branches): a warp that evaluates many of these can overlap them */
+    n = n > 254 ? 254 : n;
+    n = n < -300 ? -300 : n;
     int n1 = n / 2;
     int n2 = n - n1;
+    int low = (n2 + 127 > 0) ? 0 : 1; /* n2 in [-150,-127]: the second factor is built from two normal ones */
     float s1 = nvmoe_bits_f32((uint32_t)(n1 + 127) << 23);
-    float s2;
-    if (n2 + 127 > 0) {
-        s2 = nvmoe_bits_f32((uint32_t)(n2 + 127) << 23);
-    } else {
-        /* n2 in [-150,-127]: build from two normal factors */
-        s1 = NVMOE_FMUL(s1, nvmoe_bits_f32((uint32_t)(n2 + 64 + 127) << 23));
-        s2 = nvmoe_bits_f32((uint32_t)(-64 + 127) << 23);
-    }
+    float s1_low = NVMOE_FMUL(s1, nvmoe_bits_f32((uint32_t)(n2 + 64 + 127) << 23));
+    float s2 = nvmoe_bits_f32((uint32_t)(n2 + 127) << 23);
+    s1 = low ? s1_low : s1;
+    s2 = low ? nvmoe_bits_f32((uint32_t)(-64 + 127) << 23) : s2;
     return NVMOE_FMUL(NVMOE_FMUL(y, s1), s2);
 }
 
 /* exp(x): round-to-nearest range reduction by ln2 (two-part constant), degree-6 polynomial. */
 NVMOE_HD float nvmoe_expf(float x) {
-    if (x != x) return x;
-    if (x > 88.72284f) return nvmoe_bits_f32(0x7f800000u);
-    if (x < -103.98f) return 0.0f;
-    float fn = floorf(NVMOE_FMA(x, 1.44269504088896341f, 0.5f));
-    float r = NVMOE_FMA(fn, -0.693359375f, x);
+    /* Arguments outside the range (and NaN) run the same straight-line code on a clamped copy and are
+     * replaced at the end; inside the range the clamp changes nothing. */
+    float xc = fminf(fmaxf(x, -104.0f), 89.0f);
+    float fn = floorf(NVMOE_FMA(xc, 1.44269504088896341f, 0.5f));
+    float r = NVMOE_FMA(fn, -0.693359375f, xc);
     r = NVMOE_FMA(fn, 2.12194440e-4f, r);
     float p = 1.9875691500e-4f;
     p = NVMOE_FMA(p, r, 1.3981999507e-3f);
@@ -185,7 +183,10 @@ NVMOE_HD float nvmoe_expf(float x) {
     p = NVMOE_FMA(p, r, 5.0000001201e-1f);
     float r2 = NVMOE_FMUL(r, r);
     float y = NVMOE_FADD(NVMOE_FMA(p, r2, r), 1.0f);
-    return nvmoe_scalbn(y, (int)fn);
+    y = nvmoe_scalbn(y, (int)fn);
+    y = (x < -103.98f) ? 0.0f : y;
+    y = (x > 88.72284f) ? nvmoe_bits_f32(0x7f800000u) : y;
+    return (x != x) ? x : y;
 }
 
 /* log(x) for finite x > 0: mantissa in [sqrt(1/2), sqrt(2)), degree-8 polynomial. */

@@ -722,7 +722,8 @@ static int prepare_expert_set(nvmoe_plan* p, bool gate_up, const nvmoe_buffer* a
 static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* act_q, const float* act_scales,
                        const uint32_t* act_e8m0, const uint32_t* routes, uint32_t* intermediates, uint16_t* outputs,
                        const nvmoe_buffer* addresses, const nvmoe_buffer* slots, const uint32_t* control,
-                       bool allow_tensor_path, ExpertSet* prepared = nullptr, bool scheduled = false) {
+                       bool allow_tensor_path, ExpertSet* prepared = nullptr, bool scheduled = false,
+                       bool quantise_outputs = false) {
     const nvmoe_geometry& g = p->g;
     cudaStream_t st = p->device->stream;
     const int set = gate_up ? 0 : 1;
@@ -747,6 +748,11 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
     el.status = p->status.as<uint32_t>();
     el.scale_stamps = es->stamps.as<uint64_t>();
     el.cta_trace = p->cta_trace.as<uint64_t>();
+    if (quantise_outputs && gate_up && tensor) {
+        el.q_out = p->iq.as<uint8_t>();
+        el.q_scales = p->i_scales.as<float>();
+        el.q_e8m0 = p->i_e8m0.as<uint32_t>();
+    }
     el.tmaps = tensor && p->tma[set] ? es->tmaps.as<uint8_t>() : nullptr;
     el.tile_count = p->tile_list.as<uint32_t>() + set * tile_region_words(p);  // first word of the stage's region
     el.tile_list = el.tile_count + 64;
@@ -984,6 +990,8 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     if (!a->routes_in) NVMOE_TRY(nvmoe_route(p, T, logits, routes, a->bias, a->telemetry));
     mark(kStageSchedule);
     const bool tensor = use_tensor_path(p);
+    // with 32-wide scale blocks the tensor-path gate/up epilogue quantises its own output for the down stage
+    const bool fused_quantise = tensor && g.act_block == 32u;
     ExpertSet* sets[2] = {nullptr, nullptr};
     NVMOE_TRY(prepare_expert_set(p, true, a->gate_up_addresses, a->gate_up_slots, tensor, &sets[0]));
     NVMOE_TRY(prepare_expert_set(p, false, a->down_addresses, a->down_slots, tensor, &sets[1]));
@@ -1034,12 +1042,14 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     mark(kStageGateUp);
     NVMOE_TRY(run_experts(p, true, T, p->xq.as<uint8_t>(), p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(),
                           (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, nullptr, a->gate_up_addresses,
-                          a->gate_up_slots, (const uint32_t*)gate_control.ptr, true, sets[0], scheduled));
+                          a->gate_up_slots, (const uint32_t*)gate_control.ptr, true, sets[0], scheduled, fused_quantise));
     mark(kStageQuantI);
-    launch_quantize_frames((const uint32_t*)frames.ptr, T, p->K, g.intermediate_size, g.act_block, p->iq.as<uint8_t>(),
-                           p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), st);
-    p->launches++;
-    NVMOE_TRY(post_launch(p, "quantize intermediates"));
+    if (!fused_quantise) {
+        launch_quantize_frames((const uint32_t*)frames.ptr, T, p->K, g.intermediate_size, g.act_block, p->iq.as<uint8_t>(),
+                               p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), st);
+        p->launches++;
+        NVMOE_TRY(post_launch(p, "quantize intermediates"));
+    }
     mark(kStageDown);
     // routes that are skipped (owned by another device, expert not resident) leave their rows
     // untouched: start every row at zero so that the combine adds nothing for them
@@ -1073,17 +1083,30 @@ int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hi
     cudaError_t err = p->hidden_dev.ensure(cap);
     if (err == cudaSuccess) err = p->output_dev.ensure(cap);
     if (err != cudaSuccess) return fail(d, NVMOE_ERR_OUT_OF_MEMORY, "staging allocation failed: %s", cudaGetErrorString(err));
-    std::memcpy(p->pinned_in, hidden_host, bytes);
-    NVMOE_CUDA(d, cudaMemcpyAsync(p->hidden_dev.ptr, p->pinned_in, bytes, cudaMemcpyHostToDevice, d->stream));
+    // page-locked caller memory is read and written by the copy engine directly; anything else goes
+    // through the plan's own page-locked staging buffers
+    auto page_locked = [](const void* ptr) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        return attr.type == cudaMemoryTypeHost;
+    };
+    const bool direct_in = page_locked(hidden_host), direct_out = page_locked(output_host);
+    if (!direct_in) std::memcpy(p->pinned_in, hidden_host, bytes);
+    NVMOE_CUDA(d, cudaMemcpyAsync(p->hidden_dev.ptr, direct_in ? hidden_host : p->pinned_in, bytes, cudaMemcpyHostToDevice,
+                                  d->stream));
     nvmoe_buffer hidden{d, p->hidden_dev.ptr, cap};
     nvmoe_buffer output{d, p->output_dev.ptr, cap};
     nvmoe_layer_args local = *args;
     local.hidden = &hidden;
     local.output = &output;
     NVMOE_TRY(nvmoe_layer(p, &local));
-    NVMOE_CUDA(d, cudaMemcpyAsync(p->pinned_out, p->output_dev.ptr, bytes, cudaMemcpyDeviceToHost, d->stream));
+    NVMOE_CUDA(d, cudaMemcpyAsync(direct_out ? output_host : p->pinned_out, p->output_dev.ptr, bytes, cudaMemcpyDeviceToHost,
+                                  d->stream));
     NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
-    std::memcpy(output_host, p->pinned_out, bytes);
+    if (!direct_out) std::memcpy(output_host, p->pinned_out, bytes);
     return NVMOE_OK;
 }
 

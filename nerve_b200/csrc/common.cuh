@@ -14,6 +14,35 @@ constexpr uint32_t kUnboundSlot = 0xffffffffu;
 constexpr uint32_t kRecordWords = 8u;
 constexpr uint32_t kMaxTopK = 64u;       // routed_k + always_count
 constexpr uint32_t kMaxExperts = 4096u;  // ids travel in the low 16 bits of a route word
+// Programmatic dependent launch: a kernel launched with launch_chained may start (and run whatever
+// precedes its grid_dependency_sync) while the kernel before it in the stream is still running;
+// grid_dependency_sync returns once that kernel has completed and its writes are visible, and lets
+// the next kernel in the stream start in the same way. Every thread of a chained kernel calls it
+// before touching global memory and before any return, so completion still implies that all earlier
+// kernels have completed. Launched the ordinary way, the same kernels run unchanged.
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <class... Params, class... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+#endif
+
 constexpr uint32_t kSortChunk = 256u;    // routes per block in the multi-block counting sort
 
 // Weight pointers of one expert after the address/slot tables were validated
@@ -155,6 +184,11 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     uint16_t* outputs;           // down output [T][K][H]
     uint32_t* status;
     const uint8_t* tmaps;        // tensor path: 128-byte tensor maps [expert][matrix], null = move weights with cp.async
+    // tensor path, gate/up only, optional: the down stage's activation quantisation done in the epilogue
+    // (E4M3 bytes [route][I], f32 scales [route][I/32], E8M0 bytes [route][ceil(I/128)] words); needs act_block 32
+    uint8_t* q_out;
+    float* q_scales;
+    uint32_t* q_e8m0;
     uint64_t* cta_trace;         // tensor path diagnostics: [2][grid][4] words per CTA, or null
     uint64_t* scale_stamps;      // tensor path: {scale pointer, generation} the derived tiles were built from
     uint32_t* tile_list;         // tensor path scratch: routes / 16 + experts + 1 words

@@ -28,6 +28,7 @@
 // the packaged scale tensors that is rebuilt whenever a scale record's address or generation
 // changes.  Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include <cstring>
 
@@ -64,9 +65,14 @@ struct Config {
     static constexpr uint32_t kRowsPerPass = kProducerThreads / 8u;  // eight threads cover the 128 bytes of one row
     static constexpr uint32_t kThreads = kFirstProducerThread + kProducerThreads;
     static constexpr uint32_t kBTileBytes = N_TILE * 128u;
-    // every stage starts on a 1024-byte boundary: the 128-byte swizzle is a function of the address
-    static constexpr uint32_t kStageBytes =
+    // A stage holds kSub K blocks, each with its own operand tiles and scale blocks. Down moves one
+    // matrix, so a stage of one block would carry half the bytes of a gate/up stage for the same
+    // barrier traffic and issue overhead: it takes two blocks a stage.
+    static constexpr uint32_t kSub = GATE_UP ? 1u : 2u;
+    // every block starts on a 1024-byte boundary: the 128-byte swizzle is a function of the address
+    static constexpr uint32_t kSubBytes =
         (kMatrices * kATileBytes + kBTileBytes + (kMatrices + 1u) * kScaleBlockBytes + 1023u) / 1024u * 1024u;
+    static constexpr uint32_t kStageBytes = kSub * kSubBytes;
     static constexpr uint32_t kStagesRaw = kSmemBudget / kStageBytes;
     static constexpr uint32_t kStages = kStagesRaw > kMaxStages ? kMaxStages : kStagesRaw;
     static constexpr uint32_t kAccColumns = kMatrices * N_TILE;
@@ -105,11 +111,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
     const uint32_t k_dim = GATE_UP ? H : I;
     const uint32_t out_rows = GATE_UP ? I : H;
     const uint32_t k_blocks = (k_dim + kBlockK - 1u) / kBlockK;
+    const uint32_t k_stages = (k_blocks + C::kSub - 1u) / C::kSub;
     const uint32_t m_tiles = (out_rows + kBlockM - 1u) / kBlockM;
-    const uint32_t pair_count = *list.count;
     // cycle counters of CTA 0, one writer per role (diagnostics; words 16.. of the tile-count block)
     uint64_t* trace = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(list.count) + 16) + (GATE_UP ? 0 : 12);
-    const uint32_t tile_count = pair_count * m_tiles;
     if (blockIdx.x == 0u && threadIdx.x == 0u) trace[8] = global_timer_ns();  // kernel entry of CTA 0
 
     // ---- one-time setup ---------------------------------------------------------------------
@@ -140,6 +145,11 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_scales = tmem_base + C::kAccStages * C::kAccColumns;
+    // everything above touched only this CTA's shared and tensor memory; what follows reads what the
+    // kernels before this one wrote
+    grid_dependency_sync();
+    const uint32_t pair_count = *list.count;
+    const uint32_t tile_count = pair_count * m_tiles;
 
     if (warp == 5u) {
         // ===== TMA issue (one lane): whole 128 x 128 boxes of weight codes, padded and swizzled by the unit =====
@@ -152,19 +162,26 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 const uint8_t* maps = p.tmaps + (size_t)(pair >> 16) * C::kMatrices * 128u;
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++) tensormap_acquire(maps + mx * 128u);
-                for (uint32_t kb = 0; kb < k_blocks; kb++) {
+                for (uint32_t ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag)) {
                         alive = false;
                         break;
                     }
-                    if ((kb + 1u) * kBlockK <= k_dim) {
-                        const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
-                        mbar_arrive_expect_tx(&bars->full[slot], C::kMatrices * kTmaBoxBytes);
+                    // whole K blocks of this stage come by TMA; a trailing partial one is staged by the cp.async warps
+                    uint32_t whole = 0u;
 #pragma unroll
-                        for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                            tma_load_3d(stage + mx * kATileBytes, maps + mx * 128u, 0, (int)kb, row0, &bars->full[slot]);
+                    for (uint32_t sub = 0; sub < C::kSub; sub++) whole += ((ks * C::kSub + sub + 1u) * kBlockK <= k_dim) ? 1u : 0u;
+                    if (whole != 0u) {
+                        const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
+                        mbar_arrive_expect_tx(&bars->full[slot], whole * C::kMatrices * kTmaBoxBytes);
+                        for (uint32_t sub = 0; sub < whole; sub++) {
+#pragma unroll
+                            for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+                                tma_load_3d(stage + sub * C::kSubBytes + mx * kATileBytes, maps + mx * 128u, 0,
+                                            (int)(ks * C::kSub + sub), row0, &bars->full[slot]);
+                        }
                     } else {
-                        mbar_arrive(&bars->full[slot]);  // a partial K block is staged by the cp.async warps
+                        mbar_arrive(&bars->full[slot]);
                     }
                     if (++slot == C::kStages) {
                         slot = 0u;
@@ -228,14 +245,18 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             for (uint32_t mx = 0; mx < C::kMatrices; mx++)
                 wcol[mx] = cur.w[mx] + (size_t)(row0 + my_r) * row_bytes + my_c * 8u;
             const size_t row_step = (size_t)kRowsPerPass * row_bytes;
-            for (uint32_t kb = 0; kb < k_blocks; kb++, it++) {
+            for (uint32_t ks = 0; ks < k_stages; ks++, it++) {
                 const long long w0 = clock64();
                 if (!mbar_wait_warp(&bars->empty[slot], empty_parity, abort_flag)) {
                     alive = false;
                     break;
                 }
                 trace_wait += clock64() - w0;
-                unsigned char* stage = smem + slot * C::kStageBytes;
+#pragma unroll
+                for (uint32_t sub = 0; sub < C::kSub; sub++) {
+                const uint32_t kb = ks * C::kSub + sub;
+                if (kb >= k_blocks) break;  // the last stage of an odd count holds one block
+                unsigned char* stage = smem + slot * C::kStageBytes + sub * C::kSubBytes;
                 const uint32_t k_left = k_dim - kb * kBlockK;  // elements of K from this block on
                 const bool chunk_ok = my_c * 16u < k_left;
                 // weights: 8-byte pieces of 16 codes into the low half of 16-byte slots
@@ -278,6 +299,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + (pt & 31u) * 16u + (pt >> 5) * 4u), src,
                                ok ? 4u : 0u);
                 }
+                }
                 // the arrival fires when this thread's copies have landed; the thread moves on at once
                 cp_async_arrive_noinc(&bars->full[slot]);
                 if (++slot == C::kStages) {
@@ -300,6 +322,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             // K steps of a stage are unrolled with compile-time descriptors offsets and scale ids.
             constexpr uint32_t kIdesc = idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, kBlockM, N_TILE);
             constexpr uint32_t kStageUnits = C::kStageBytes >> 4;  // descriptor start addresses count 16 bytes
+            constexpr uint32_t kSubUnits = C::kSubBytes >> 4;
             const uint32_t base = smem_u32(smem);
             const uint64_t a_desc0 = desc_k_major_sw128(base);
             const uint64_t b_desc0 = desc_k_major_sw128(base + C::kMatrices * kATileBytes);
@@ -319,7 +342,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 trace_acc += clock64() - a0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccColumns;
-                for (uint32_t kb = 0; kb < k_blocks; kb++, it++) {
+                for (uint32_t ks = 0; ks < k_stages; ks++, it++) {
                     const long long f0 = clock64();
                     if (!mbar_wait(&bars->full[slot], full_parity, abort_flag)) {
                         alive = false;
@@ -327,7 +350,11 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     }
                     trace_full += clock64() - f0;
                     tc_fence_after();
-                    const uint64_t off = (uint64_t)(slot * kStageUnits);
+#pragma unroll
+                    for (uint32_t sub = 0; sub < C::kSub; sub++) {
+                    const uint32_t kb = ks * C::kSub + sub;
+                    if (kb >= k_blocks) break;
+                    const uint64_t off = (uint64_t)(slot * kStageUnits + sub * kSubUnits);
                     const uint64_t a_desc = a_desc0 + off, b_desc = b_desc0 + off, sf_desc = sf_desc0 + off;
 #pragma unroll
                     for (uint32_t mx = 0; mx <= C::kMatrices; mx++)
@@ -344,6 +371,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                                                     sfb_tmem, j == 0u ? (kb != 0u ? 1u : 0u) : 1u);
                             }
                         }
+                    }
                     }
                     tc_commit(&bars->empty[slot]);  // the stage may be refilled once these MMAs retire
                     if (++slot == C::kStages) {
@@ -404,8 +432,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 // while the accumulators arrive; the sixteen results are then handed round by shuffles
                 uint64_t my_row = 0u;
                 float my_weight = 0.0f;
+                uint32_t my_route = 0u;
                 if (lane < 16u && c0 + lane < valid) {
                     const uint32_t ri = __ldg(p.work.grouped_routes + first + c0 + lane);
+                    my_route = ri;
                     if (GATE_UP) {
                         my_row = reinterpret_cast<uint64_t>(reinterpret_cast<uint16_t*>(p.intermediates + (size_t)(ri / K) * frame_words) +
                                                             (size_t)(ri % K) * I);
@@ -415,17 +445,59 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     }
                 }
                 tmem_ld_wait();
+                const bool quantise = GATE_UP && p.q_out != nullptr;  // host: only with 32-row scale blocks
+                // Four tokens at a time go through each step together, with no branch between them, so that
+                // their instruction latencies overlap (the activation math is one long dependent chain per
+                // value); columns past `valid` hold zeros and are only not stored.
 #pragma unroll
-                for (uint32_t j = 0; j < 16u; j++) {
-                    uint16_t* out = reinterpret_cast<uint16_t*>(__shfl_sync(0xffffffffu, my_row, j));
-                    const float weight = __shfl_sync(0xffffffffu, my_weight, j);
-                    if (c0 + j >= valid || !row_ok) continue;
-                    if (GATE_UP) {
-                        const float a = nvmoe_swiglu(__uint_as_float(d0[j]), __uint_as_float(d1[j]), p.g.swiglu_limit,
-                                                     p.g.swiglu_alpha, p.g.swiglu_up_offset);
-                        out[row] = (uint16_t)nvmoe_f32_to_bf16(a);
-                    } else {
-                        out[row] = (uint16_t)nvmoe_f32_to_bf16(__fmul_rn(__uint_as_float(d0[j]), weight));
+                for (uint32_t g0 = 0; g0 < 16u; g0 += 4u) {
+                    if (c0 + g0 >= valid) break;  // uniform
+                    uint32_t bits[4];
+#pragma unroll
+                    for (uint32_t t = 0; t < 4u; t++) {
+                        const uint32_t j = g0 + t;
+                        if (GATE_UP) {
+                            bits[t] = nvmoe_f32_to_bf16(nvmoe_swiglu(__uint_as_float(d0[j]), __uint_as_float(d1[j]),
+                                                                     p.g.swiglu_limit, p.g.swiglu_alpha, p.g.swiglu_up_offset));
+                        } else {
+                            const float weight = __shfl_sync(0xffffffffu, my_weight, j);
+                            bits[t] = nvmoe_f32_to_bf16(__fmul_rn(__uint_as_float(d0[j]), weight));
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t t = 0; t < 4u; t++) {
+                        uint16_t* out = reinterpret_cast<uint16_t*>(__shfl_sync(0xffffffffu, my_row, g0 + t));
+                        if (c0 + g0 + t < valid && row_ok) out[row] = (uint16_t)bits[t];
+                    }
+                    if (quantise) {
+                        // the activation quantisation of the down stage, on the values just rounded to bf16: one
+                        // power-of-two scale per 32 rows, which is exactly this warp's share of the tile
+                        float m[4];
+#pragma unroll
+                        for (uint32_t t = 0; t < 4u; t++) m[t] = row_ok ? fabsf(nvmoe_bf16_to_f32(bits[t])) : 0.0f;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                            for (uint32_t t = 0; t < 4u; t++) m[t] = fmaxf(m[t], __shfl_xor_sync(0xffffffffu, m[t], o));
+                        }
+                        const uint32_t first_row = m_tile * kBlockM + warp * 32u;
+                        const bool writes_scale = lane == 0u && first_row < out_rows;
+#pragma unroll
+                        for (uint32_t t = 0; t < 4u; t++) {
+                            const uint32_t ri = __shfl_sync(0xffffffffu, my_route, g0 + t);
+                            const float scale = nvmoe_rounded_fp8_scale(m[t]);
+                            const float inv = __fdiv_rn(1.0f, scale);  // exact: a power of two
+                            const uint8_t q =
+                                (uint8_t)__nv_cvt_float_to_fp8(nvmoe_bf16_to_f32(bits[t]) * inv, __NV_SATFINITE, __NV_E4M3);
+                            if (c0 + g0 + t < valid) {
+                                if (row_ok) p.q_out[(size_t)ri * I + row] = q;
+                                if (writes_scale) {
+                                    p.q_scales[(size_t)ri * (I / 32u) + first_row / 32u] = scale;
+                                    reinterpret_cast<uint8_t*>(p.q_e8m0 + (size_t)ri * ((I + 127u) / 128u))[first_row / 32u] =
+                                        (uint8_t)(nvmoe_f32_bits(scale) >> 23);
+                                }
+                            }
+                        }
                     }
                 }
             }
@@ -509,7 +581,7 @@ void launch_n(const ExpertLaunch& p, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (g_sm_count[dev & 15] == 0) cudaDeviceGetAttribute(&g_sm_count[dev & 15], cudaDevAttrMultiProcessorCount, dev);
-    experts_tc_kernel<GATE_UP, N_TILE, USE_TMA><<<g_sm_count[dev & 15], C::kThreads, C::kSmemBytes, stream>>>(
+    launch_chained(experts_tc_kernel<GATE_UP, N_TILE, USE_TMA>, dim3(g_sm_count[dev & 15]), dim3(C::kThreads), C::kSmemBytes, stream,
         p, TileList{p.tile_list, p.tile_count});
 }
 

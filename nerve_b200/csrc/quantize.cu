@@ -64,6 +64,7 @@ __device__ void quantize_body(RowFn row_of, uint32_t rows, uint32_t cols, uint32
 __global__ void __launch_bounds__(256) quantize_kernel(const uint16_t* input, uint32_t rows, uint32_t cols,
                                                       uint32_t block, size_t row_stride, uint8_t* q,
                                                       float* scales_f32, uint32_t* scales_e8m0) {
+    grid_dependency_sync();
     quantize_body([&](uint32_t r) { return input + (size_t)r * row_stride; }, rows, cols, block, q, scales_f32,
                   scales_e8m0);
 }
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const uint16_t* input, ui
 __global__ void __launch_bounds__(256) quantize_frames_kernel(const uint32_t* intermediates, uint32_t tokens,
                                                              uint32_t K, uint32_t I, uint32_t block, uint8_t* q,
                                                              float* scales_f32, uint32_t* scales_e8m0) {
+    grid_dependency_sync();
     const uint32_t frame_words = K * (I / 2u) + K;
     quantize_body(
         [&](uint32_t r) {
@@ -104,16 +106,16 @@ uint32_t grid_for(uint64_t warps) {
 void launch_quantize(const uint16_t* input, uint32_t rows, uint32_t cols, uint32_t block, size_t input_row_stride,
                      uint8_t* q, float* scales_f32, uint32_t* scales_e8m0, cudaStream_t stream) {
     if (rows == 0u) return;
-    quantize_kernel<<<grid_for((uint64_t)rows * (cols / block)), 256, 0, stream>>>(
-        input, rows, cols, block, input_row_stride, q, scales_f32, scales_e8m0);
+    launch_chained(quantize_kernel, dim3(grid_for((uint64_t)rows * (cols / block))), dim3(256), 0, stream, input, rows, cols,
+                   block, input_row_stride, q, scales_f32, scales_e8m0);
 }
 
 void launch_quantize_frames(const uint32_t* intermediates, uint32_t tokens, uint32_t K, uint32_t intermediate_size,
                             uint32_t block, uint8_t* q, float* scales_f32, uint32_t* scales_e8m0,
                             cudaStream_t stream) {
     if (tokens == 0u) return;
-    quantize_frames_kernel<<<grid_for((uint64_t)tokens * K * (intermediate_size / block)), 256, 0, stream>>>(
-        intermediates, tokens, K, intermediate_size, block, q, scales_f32, scales_e8m0);
+    launch_chained(quantize_frames_kernel, dim3(grid_for((uint64_t)tokens * K * (intermediate_size / block))), dim3(256), 0,
+                   stream, intermediates, tokens, K, intermediate_size, block, q, scales_f32, scales_e8m0);
 }
 
 void launch_scales_to_e8m0(const float* scales, uint32_t rows, uint32_t cols, uint32_t block,

@@ -14,6 +14,7 @@ namespace {
 __global__ void __launch_bounds__(256) reduce_kernel(const uint32_t* __restrict__ expert_outputs,
                                                     uint32_t* __restrict__ output, uint32_t tokens, uint32_t K,
                                                     uint32_t hidden_words, float routed_scale) {
+    grid_dependency_sync();
     const uint64_t total = (uint64_t)tokens * hidden_words;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(i / hidden_words), word = (uint32_t)(i % hidden_words);
@@ -36,9 +37,9 @@ void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t to
     const uint64_t total = (uint64_t)tokens * (hidden / 2u);
     uint64_t blocks = (total + 255u) / 256u;
     if (blocks > 148u * 8u) blocks = 148u * 8u;
-    reduce_kernel<<<(uint32_t)blocks, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(expert_outputs),
-                                                        reinterpret_cast<uint32_t*>(output), tokens, K, hidden / 2u,
-                                                        routed_scale);
+    launch_chained(reduce_kernel, dim3((uint32_t)blocks), dim3(256), 0, stream,
+                   reinterpret_cast<const uint32_t*>(expert_outputs), reinterpret_cast<uint32_t*>(output), tokens, K,
+                   hidden / 2u, routed_scale);
 }
 
 }  // namespace nvmoe

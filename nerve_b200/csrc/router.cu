@@ -61,6 +61,7 @@ __device__ __forceinline__ float read_bias(const void* bias, uint32_t dtype, uin
 
 __global__ void __launch_bounds__(128) router_kernel(RouterLaunch p, uint32_t warps_per_block) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    grid_dependency_sync();
     const uint32_t E = p.g.routed_experts;
     const uint32_t k = p.g.routed_k;
     const uint32_t kind = p.g.router_kind;
@@ -283,6 +284,7 @@ __global__ void __launch_bounds__(64) router_linear_kernel(const uint16_t* __res
                                                            uint32_t hidden, uint32_t outputs) {
     __shared__ float fold[TT * ET][32];
     __shared__ float result[TT * ET];
+    grid_dependency_sync();
     const uint32_t v = threadIdx.x;
     const uint32_t t0 = blockIdx.y * TT, e0 = blockIdx.x * ET;
     const uint32_t words = hidden / 2u;
@@ -368,17 +370,17 @@ void launch_router(const RouterLaunch& p, cudaStream_t stream) {
     if (smem > 48u * 1024u)
         cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     uint32_t blocks = (p.tokens + warps - 1u) / warps;
-    router_kernel<<<blocks, warps * 32u, smem, stream>>>(p, warps);
+    launch_chained(router_kernel, dim3(blocks), dim3(warps * 32u), smem, stream, p, warps);
 }
 
 void launch_router_linear(const uint16_t* x, const uint16_t* w, const uint16_t* bias, uint32_t* logits,
                           uint32_t tokens, uint32_t hidden, uint32_t outputs, cudaStream_t stream) {
     if (tokens <= 256u) {
         dim3 grid((outputs + 3u) / 4u, (tokens + 1u) / 2u);
-        router_linear_kernel<2, 4><<<grid, 64, 0, stream>>>(x, w, bias, logits, tokens, hidden, outputs);
+        launch_chained(router_linear_kernel<2, 4>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
     } else {
         dim3 grid((outputs + 15u) / 16u, (tokens + 7u) / 8u);
-        router_linear_kernel<8, 16><<<grid, 64, 0, stream>>>(x, w, bias, logits, tokens, hidden, outputs);
+        launch_chained(router_linear_kernel<8, 16>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
     }
 }
 

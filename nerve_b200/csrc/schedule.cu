@@ -484,6 +484,7 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const uint32_t* exper
 // each of the two expert stages the expert-grouped route list and the tensor-path tile list.
 __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedule s) {
     extern __shared__ uint32_t hist[];
+    grid_dependency_sync();
     if (threadIdx.x < 14u) {
         const uint32_t j = threadIdx.x % 7u;
         s.control[threadIdx.x / 7u][j] = j == 0u ? s.tokens : j == 1u ? s.expert_start : j == 2u ? s.expert_count : 0u;
@@ -552,6 +553,7 @@ struct PackEmit {  // one warp-wide row copy per route would be faster; rows are
 __global__ void __launch_bounds__(1024) ep_pack_small_kernel(DestKey key, PackEmit emit, uint32_t count,
                                                             uint32_t* dest_counts) {
     extern __shared__ uint32_t hist[];
+    grid_dependency_sync();
     for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) emit.send_index[i] = kUnboundSlot;
     __syncthreads();
     sort_single_block(count, key.world, hist, key, emit, [&](const uint32_t* base) {
@@ -578,6 +580,7 @@ __global__ void __launch_bounds__(256) ep_pack_scatter_kernel(DestKey key, PackE
 __global__ void __launch_bounds__(256) ep_gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                                             const uint32_t* __restrict__ index, const uint32_t* total,
                                                             uint32_t max_rows, uint32_t divide, uint32_t row_vec) {
+    grid_dependency_sync();
     const uint32_t rows = total ? min_u32(*total, max_rows) : max_rows;
     const uint32_t warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31u;
     for (uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -600,6 +603,7 @@ __global__ void __launch_bounds__(256) ep_pad_kernel(const uint4* __restrict__ h
                                                     const uint32_t* __restrict__ send_source, uint32_t world, uint32_t cap,
                                                     uint32_t K, uint32_t row_vec, uint4* __restrict__ rows_out,
                                                     uint32_t* __restrict__ routes_out, uint32_t* __restrict__ send_index) {
+    grid_dependency_sync();
     const uint32_t warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t slots = world * cap;
     for (uint32_t slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; slot < slots; slot += warps) {
@@ -644,8 +648,8 @@ void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32
     // the padded form packs positions only; its route words and rows are placed by ep_pad_kernel
     PackEmit emit{routes, segment_rows ? contiguous_routes : send_routes, send_index, send_source};
     if (count <= kSmallSortLimit) {
-        ep_pack_small_kernel<<<1, count <= 256u ? 256u : 1024u, (world + 1u) * sizeof(uint32_t), stream>>>(key, emit, count,
-                                                                                                           dest_counts);
+        launch_chained(ep_pack_small_kernel, dim3(1), dim3(count <= 256u ? 256u : 1024u), (world + 1u) * sizeof(uint32_t),
+                       stream, key, emit, count, dest_counts);
     } else {
         const uint32_t blocks = (count + kSortChunk - 1u) / kSortChunk;
         ep_pack_hist_kernel<<<blocks, 256, world * sizeof(uint32_t), stream>>>(key, count, scratch.block_hist, send_index);
@@ -657,9 +661,9 @@ void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32
     if (segment_rows) {
         uint32_t pad_blocks = (world * segment_rows + 7u) / 8u;
         if (pad_blocks > 148u * 8u) pad_blocks = 148u * 8u;
-        ep_pad_kernel<<<pad_blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(hidden), routes, dest_counts, send_source,
-                                                      world, segment_rows, K, row_vec, reinterpret_cast<uint4*>(send_rows),
-                                                      send_routes, send_index);
+        launch_chained(ep_pad_kernel, dim3(pad_blocks), dim3(256), 0, stream, reinterpret_cast<const uint4*>(hidden), routes,
+                       dest_counts, send_source, world, segment_rows, K, row_vec, reinterpret_cast<uint4*>(send_rows),
+                       send_routes, send_index);
         return;
     }
     sum_counts_kernel<<<1, 32, 0, stream>>>(dest_counts, world, total);
@@ -675,9 +679,8 @@ void launch_ep_unpack(const uint16_t* returned_rows, const uint32_t* send_index,
     uint32_t blocks = (count + 7u) / 8u;
     if (blocks > 148u * 8u) blocks = 148u * 8u;
     // expert_outputs[t][r] = returned_rows[send_index[t*K + r]]; routes that were dropped give zeros
-    ep_gather_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(returned_rows),
-                                                      reinterpret_cast<uint4*>(expert_outputs), send_index, nullptr, count,
-                                                      1u, hidden_size / 8u);
+    launch_chained(ep_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, reinterpret_cast<const uint4*>(returned_rows),
+                   reinterpret_cast<uint4*>(expert_outputs), send_index, (const uint32_t*)nullptr, count, 1u, hidden_size / 8u);
 }
 
 void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const uint32_t* slots,
@@ -709,7 +712,8 @@ bool layer_schedule_is_small(uint32_t tokens, uint32_t K) { return (uint64_t)tok
 
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
     const uint32_t count = s.tokens * s.K;
-    layer_schedule_small_kernel<<<1, count <= 256u ? 256u : 1024u, (s.num_experts + 2u) * sizeof(uint32_t), stream>>>(s);
+    launch_chained(layer_schedule_small_kernel, dim3(1), dim3(count <= 256u ? 256u : 1024u),
+                   (s.num_experts + 2u) * sizeof(uint32_t), stream, s);
 }
 
 void launch_build_tiles(const uint32_t* expert_offsets, uint32_t num_experts, uint32_t n_tile, uint32_t* tiles,
