@@ -127,6 +127,9 @@ struct nvmoe_plan {
     std::vector<std::unique_ptr<ExpertSet>> sets[2];  // [gate/up, down], least recently used replaced
     uint64_t use_clock = 0;
     DeviceArray xq, x_scales, x_e8m0, iq, i_scales, i_e8m0, tile_list, ep_source;
+    // tensor path: expert-grouped quantised activations of the two stages (row = position in grouped[stage]),
+    // where each route landed, and the tensor maps of the two matrices for the four token tile sizes
+    DeviceArray grouped_q[2], grouped_e8m0[2], position[2], act_maps;
     DeviceArray cta_trace;       // per-CTA diagnostics of the tensor-path kernels, allocated on first request
     DeviceArray tmap_templates;  // tensor maps of the two weight matrix shapes; each expert's map is one with its address patched in
     bool tma[2] = {false, false};
@@ -459,11 +462,33 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
     want(p->i_e8m0, sizeof(uint32_t) * R * ((I + 127u) / 128u));
     want(p->tile_list, sizeof(uint32_t) * 2u * tile_region_words(p));
     if (tc_shape_supported(g)) {
+        want(p->grouped_q[0], R * H);
+        want(p->grouped_q[1], R * I);
+        want(p->grouped_e8m0[0], sizeof(uint32_t) * R * ((H + 127u) / 128u));
+        want(p->grouped_e8m0[1], sizeof(uint32_t) * R * ((I + 127u) / 128u));
+        want(p->position[0], sizeof(uint32_t) * R);
+        want(p->position[1], sizeof(uint32_t) * R);
+        want(p->act_maps, 8u * 128u);
+        if (err == cudaSuccess) {
+            unsigned char maps[8 * 128];
+            bool ok = true;
+            for (uint32_t set = 0; set < 2u && ok; set++)
+                for (uint32_t i = 0; i < 4u && ok; i++)
+                    ok = tc_encode_activation_map(maps + (set * 4u + i) * 128u, p->grouped_q[set].ptr, (uint32_t)R,
+                                                  (uint32_t)(set == 0u ? H : I), 16u << i);
+            if (ok) {
+                err = cudaMemcpyAsync(p->act_maps.ptr, maps, sizeof maps, cudaMemcpyHostToDevice, d->stream);
+                if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer
+            } else {
+                p->act_maps.release();  // no tensor maps on this system: the tensor path copies with cp.async
+            }
+        }
         want(p->tmap_templates, 256);
         if (err == cudaSuccess) {
             unsigned char maps[256];
             p->tma[0] = tc_encode_weight_map(maps, p->tmap_templates.ptr, g.intermediate_size, g.hidden_size);
             p->tma[1] = tc_encode_weight_map(maps + 128, p->tmap_templates.ptr, g.hidden_size, g.intermediate_size);
+            if (!p->act_maps.ptr) p->tma[0] = p->tma[1] = false;
             err = cudaMemcpyAsync(p->tmap_templates.ptr, maps, 256, cudaMemcpyHostToDevice, d->stream);
             if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer
         }
@@ -491,7 +516,8 @@ void nvmoe_plan_destroy(nvmoe_plan* p) {
         for (auto& es : stage_sets) es->release();
     DeviceArray* all[] = {&p->status, &p->grouped[0], &p->grouped[1], &p->offsets[0],
                           &p->offsets[1], &p->block_hist, &p->bucket_base, &p->xq, &p->x_scales, &p->x_e8m0, &p->iq,
-                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->tmap_templates, &p->cta_trace, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
+                          &p->i_scales, &p->i_e8m0, &p->tile_list, &p->ep_source, &p->tmap_templates, &p->cta_trace, &p->grouped_q[0], &p->grouped_q[1],
+                          &p->grouped_e8m0[0], &p->grouped_e8m0[1], &p->position[0], &p->position[1], &p->act_maps, &p->logits, &p->routes, &p->frames, &p->expert_outputs,
                           &p->controls, &p->hidden_dev, &p->output_dev};
     for (DeviceArray* a : all) a->release();
     if (p->pinned_in) cudaFreeHost(p->pinned_in);
@@ -719,48 +745,110 @@ static int prepare_expert_set(nvmoe_plan* p, bool gate_up, const nvmoe_buffer* a
     return post_launch(p, gate_up ? "gate/up expert tables" : "down expert tables");
 }
 
-static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* act_q, const float* act_scales,
-                       const uint32_t* act_e8m0, const uint32_t* routes, uint32_t* intermediates, uint16_t* outputs,
-                       const nvmoe_buffer* addresses, const nvmoe_buffer* slots, const uint32_t* control,
-                       bool allow_tensor_path, ExpertSet* prepared = nullptr, bool scheduled = false,
-                       bool quantise_outputs = false) {
+// Groups the routes of one expert stage by expert (and, for the tensor path, records where each route
+// landed and lists the (expert, token tile) pairs).
+static int schedule_stage(nvmoe_plan* p, bool gate_up, ExpertSet* es, uint32_t T, const uint32_t* routes,
+                          const uint32_t* intermediates, const uint32_t* control, bool tensor) {
+    const int set = gate_up ? 0 : 1;
+    cudaStream_t st = p->device->stream;
+    launch_group_slots(routes, intermediates, control, es->ptrs.as<ExpertPtrs>(), p->experts, T, p->K, p->g.intermediate_size,
+                       p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(),
+                       tensor ? p->position[set].as<uint32_t>() : nullptr, p->status.as<uint32_t>(), sort_scratch(p), st);
+    p->launches += (size_t)T * p->K <= 4096u ? 1u : 3u;
+    if (tensor) {
+        uint32_t* region = p->tile_list.as<uint32_t>() + set * tile_region_words(p);
+        launch_build_tiles(p->offsets[set].as<uint32_t>(), p->experts, tc_token_tile_for(T, p->K, p->experts), region + 64, region, st);
+        p->launches++;
+    }
+    return post_launch(p, gate_up ? "gate/up schedule" : "down schedule");
+}
+
+// Quantises the activations of one expert stage into the form its kernels read: expert-grouped rows
+// with E8M0 scales for the tensor path (after the stage has been scheduled), token- or route-ordered
+// rows with f32 scales for the CUDA-core path. `source` is the bf16 hidden matrix (gate/up) or the
+// intermediates frames (down).
+static int quantise_operands(nvmoe_plan* p, bool gate_up, uint32_t T, const void* source, bool tensor) {
+    const nvmoe_geometry& g = p->g;
+    const int set = gate_up ? 0 : 1;
+    cudaStream_t st = p->device->stream;
+    if (tensor) {
+        launch_quantize_grouped(source, !gate_up, p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->experts,
+                                T * p->K, p->K, gate_up ? g.hidden_size : g.intermediate_size, g.intermediate_size,
+                                g.act_block, p->grouped_q[set].as<uint8_t>(), p->grouped_e8m0[set].as<uint32_t>(), st);
+    } else if (gate_up) {
+        launch_quantize((const uint16_t*)source, T, g.hidden_size, g.act_block, g.hidden_size, p->xq.as<uint8_t>(),
+                        p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(), st);
+    } else {
+        launch_quantize_frames((const uint32_t*)source, T, p->K, g.intermediate_size, g.act_block, p->iq.as<uint8_t>(),
+                               p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), st);
+    }
+    p->launches++;
+    return post_launch(p, gate_up ? "quantize hidden" : "quantize intermediates");
+}
+
+struct ExpertCall {
+    bool gate_up = true;
+    uint32_t T = 0;
+    const void* source = nullptr;          // bf16 activations to quantise first (null: operands are ready)
+    const uint8_t* pre_q = nullptr;        // pre-quantised contract (CUDA-core path only)
+    const float* pre_scales = nullptr;
+    const uint32_t* routes = nullptr;
+    uint32_t* intermediates = nullptr;
+    uint16_t* outputs = nullptr;
+    const nvmoe_buffer* addresses = nullptr;
+    const nvmoe_buffer* slots = nullptr;
+    const uint32_t* control = nullptr;
+    bool allow_tensor_path = true;
+    ExpertSet* prepared = nullptr;
+    bool scheduled = false;         // grouping (and tile list) already built for this call
+    bool fuse_quantise = false;     // gate/up on the tensor path: the epilogue also writes the down stage's operands
+};
+
+// shared tail of the two gate/up entry points and of down
+static int run_experts(nvmoe_plan* p, const ExpertCall& c) {
     const nvmoe_geometry& g = p->g;
     cudaStream_t st = p->device->stream;
+    const bool gate_up = c.gate_up;
     const int set = gate_up ? 0 : 1;
-    const bool tensor = allow_tensor_path && use_tensor_path(p);
-    ExpertSet* es = prepared;
-    if (!es) NVMOE_TRY(prepare_expert_set(p, gate_up, addresses, slots, tensor, &es));
-    ExpertPtrs* ptrs = es->ptrs.as<ExpertPtrs>();
-    if (!scheduled) {
-        launch_group_slots(routes, intermediates, control, ptrs, p->experts, T, p->K, g.intermediate_size,
-                           p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->status.as<uint32_t>(),
-                           sort_scratch(p), st);
-        p->launches += (size_t)T * p->K <= 4096u ? 1u : 3u;
-    }
+    const uint32_t T = c.T;
+    const bool tensor = c.allow_tensor_path && use_tensor_path(p);
+    ExpertSet* es = c.prepared;
+    if (!es) NVMOE_TRY(prepare_expert_set(p, gate_up, c.addresses, c.slots, tensor, &es));
+    if (!c.scheduled) NVMOE_TRY(schedule_stage(p, gate_up, es, T, c.routes, c.intermediates, c.control, tensor));
+    if (c.source) NVMOE_TRY(quantise_operands(p, gate_up, T, c.source, tensor));
     ExpertLaunch el{};
-    el.work = GroupedWork{p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), ptrs, p->experts};
-    el.act_q = act_q;
-    el.act_scales = act_scales;
-    el.act_e8m0 = act_e8m0;
-    el.routes = routes;
-    el.intermediates = intermediates;
-    el.outputs = outputs;
+    el.work = GroupedWork{p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), es->ptrs.as<ExpertPtrs>(), p->experts};
+    if (tensor) {
+        el.act_q = p->grouped_q[set].as<uint8_t>();
+        el.act_e8m0 = p->grouped_e8m0[set].as<uint32_t>();
+    } else if (c.pre_q) {
+        el.act_q = c.pre_q;
+        el.act_scales = c.pre_scales;
+    } else {
+        el.act_q = (gate_up ? p->xq : p->iq).as<uint8_t>();
+        el.act_scales = (gate_up ? p->x_scales : p->i_scales).as<float>();
+        el.act_e8m0 = (gate_up ? p->x_e8m0 : p->i_e8m0).as<uint32_t>();
+    }
+    el.routes = c.routes;
+    el.intermediates = c.intermediates;
+    el.outputs = c.outputs;
     el.status = p->status.as<uint32_t>();
     el.scale_stamps = es->stamps.as<uint64_t>();
     el.cta_trace = p->cta_trace.as<uint64_t>();
-    if (quantise_outputs && gate_up && tensor) {
-        el.q_out = p->iq.as<uint8_t>();
-        el.q_scales = p->i_scales.as<float>();
-        el.q_e8m0 = p->i_e8m0.as<uint32_t>();
-    }
     el.tmaps = tensor && p->tma[set] ? es->tmaps.as<uint8_t>() : nullptr;
     el.tile_count = p->tile_list.as<uint32_t>() + set * tile_region_words(p);  // first word of the stage's region
     el.tile_list = el.tile_count + 64;
     el.tokens = T;
     el.g = g;
-    if (tensor && !scheduled) {
-        launch_build_tiles_tc(el, st);
-        p->launches++;
+    if (tensor) {
+        const uint32_t n = tc_token_tile(el);
+        const uint32_t size_index = n == 16u ? 0u : n == 32u ? 1u : n == 64u ? 2u : 3u;
+        el.act_tmap = el.tmaps ? p->act_maps.as<uint8_t>() + (set * 4u + size_index) * 128u : nullptr;
+        if (c.fuse_quantise && gate_up) {
+            el.q_out = p->grouped_q[1].as<uint8_t>();
+            el.q_e8m0 = p->grouped_e8m0[1].as<uint32_t>();
+            el.down_position = p->position[1].as<uint32_t>();
+        }
     }
     if (p->profile_stages) cudaEventRecord(p->kernel_ev[set][0], st);
     if (tensor) {
@@ -769,7 +857,6 @@ static int run_experts(nvmoe_plan* p, bool gate_up, uint32_t T, const uint8_t* a
         } else {
             launch_down_tc(el, st);
         }
-        p->launches++;
     } else {
         if (gate_up) {
             launch_gate_up_simt(el, st);
@@ -806,13 +893,16 @@ int nvmoe_gate_up(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const n
     NVMOE_TRY(check_buffer(p, control, 28u, "control"));
     NVMOE_TRY(check_expert_tables(p, addresses, slots, 4u));
     NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
-    launch_quantize((const uint16_t*)hidden->ptr, T, g.hidden_size, g.act_block, g.hidden_size, p->xq.as<uint8_t>(),
-                    p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(), p->device->stream);
-    p->launches++;
-    NVMOE_TRY(post_launch(p, "quantize hidden"));
-    return run_experts(p, true, T, p->xq.as<uint8_t>(), p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(),
-                       (const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr, nullptr, addresses, slots,
-                       (const uint32_t*)control->ptr, true);
+    ExpertCall c;
+    c.gate_up = true;
+    c.T = T;
+    c.source = hidden->ptr;
+    c.routes = (const uint32_t*)routes->ptr;
+    c.intermediates = (uint32_t*)intermediates->ptr;
+    c.addresses = addresses;
+    c.slots = slots;
+    c.control = (const uint32_t*)control->ptr;
+    return run_experts(p, c);
 }
 
 int nvmoe_gate_up_prequant(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* quantized_hidden,
@@ -829,9 +919,18 @@ int nvmoe_gate_up_prequant(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* quanti
     NVMOE_TRY(check_expert_tables(p, addresses, slots, 4u));
     NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
     // the f32 scales of this contract need not be powers of two: the CUDA-core kernels take them as they are
-    return run_experts(p, true, T, (const uint8_t*)quantized_hidden->ptr, (const float*)hidden_scales->ptr, nullptr,
-                       (const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr, nullptr, addresses, slots,
-                       (const uint32_t*)control->ptr, false);
+    ExpertCall c;
+    c.gate_up = true;
+    c.T = T;
+    c.pre_q = (const uint8_t*)quantized_hidden->ptr;
+    c.pre_scales = (const float*)hidden_scales->ptr;
+    c.routes = (const uint32_t*)routes->ptr;
+    c.intermediates = (uint32_t*)intermediates->ptr;
+    c.addresses = addresses;
+    c.slots = slots;
+    c.control = (const uint32_t*)control->ptr;
+    c.allow_tensor_path = false;
+    return run_experts(p, c);
 }
 
 int nvmoe_down(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* intermediates, const nvmoe_buffer* routes,
@@ -846,13 +945,17 @@ int nvmoe_down(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* intermediates, con
     NVMOE_TRY(check_buffer(p, control, 28u, "control"));
     NVMOE_TRY(check_expert_tables(p, addresses, slots, 2u));
     NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
-    launch_quantize_frames((const uint32_t*)intermediates->ptr, T, p->K, g.intermediate_size, g.act_block,
-                           p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), p->device->stream);
-    p->launches++;
-    NVMOE_TRY(post_launch(p, "quantize intermediates"));
-    return run_experts(p, false, T, p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(),
-                       (const uint32_t*)routes->ptr, (uint32_t*)intermediates->ptr, (uint16_t*)outputs->ptr, addresses,
-                       slots, (const uint32_t*)control->ptr, true);
+    ExpertCall c;
+    c.gate_up = false;
+    c.T = T;
+    c.source = intermediates->ptr;
+    c.routes = (const uint32_t*)routes->ptr;
+    c.intermediates = (uint32_t*)intermediates->ptr;
+    c.outputs = (uint16_t*)outputs->ptr;
+    c.addresses = addresses;
+    c.slots = slots;
+    c.control = (const uint32_t*)control->ptr;
+    return run_experts(p, c);
 }
 
 int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, nvmoe_buffer* output) {
@@ -995,8 +1098,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     ExpertSet* sets[2] = {nullptr, nullptr};
     NVMOE_TRY(prepare_expert_set(p, true, a->gate_up_addresses, a->gate_up_slots, tensor, &sets[0]));
     NVMOE_TRY(prepare_expert_set(p, false, a->down_addresses, a->down_slots, tensor, &sets[1]));
-    const bool scheduled = layer_schedule_is_small(T, p->K);
-    if (scheduled) {
+    if (layer_schedule_is_small(T, p->K)) {
         LayerSchedule ls{};
         ls.routes = (const uint32_t*)routes->ptr;
         ls.intermediates = (uint32_t*)frames.ptr;
@@ -1010,6 +1112,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
             ls.experts[i] = sets[i]->ptrs.as<ExpertPtrs>();
             ls.grouped[i] = p->grouped[i].as<uint32_t>();
             ls.offsets[i] = p->offsets[i].as<uint32_t>();
+            ls.position[i] = tensor ? p->position[i].as<uint32_t>() : nullptr;
             ls.tile_count[i] = tensor ? p->tile_list.as<uint32_t>() + i * tile_region_words(p) : nullptr;
             ls.tiles[i] = tensor ? ls.tile_count[i] + 64 : nullptr;
         }
@@ -1032,31 +1135,42 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
         p->launches += 2;
         NVMOE_TRY(nvmoe_route_compact(p, T, routes, &frames, a->gate_up_slots, &gate_control));
         NVMOE_TRY(nvmoe_route_count(p, T, routes, a->down_slots, &down_control));
+        // both stages are grouped before the first runs: gate/up's epilogue needs to know where the down
+        // stage will look for each route's activations
+        NVMOE_TRY(schedule_stage(p, true, sets[0], T, (const uint32_t*)routes->ptr, (const uint32_t*)frames.ptr,
+                                 (const uint32_t*)gate_control.ptr, tensor));
+        NVMOE_TRY(schedule_stage(p, false, sets[1], T, (const uint32_t*)routes->ptr, (const uint32_t*)frames.ptr,
+                                 (const uint32_t*)down_control.ptr, tensor));
     }
     mark(kStageQuantX);
-    // nvmoe_gate_up quantises then runs the experts; the stage marks split the two for the report
-    launch_quantize((const uint16_t*)a->hidden->ptr, T, g.hidden_size, g.act_block, g.hidden_size, p->xq.as<uint8_t>(),
-                    p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(), st);
-    p->launches++;
-    NVMOE_TRY(post_launch(p, "quantize hidden"));
+    NVMOE_TRY(quantise_operands(p, true, T, a->hidden->ptr, tensor));
     mark(kStageGateUp);
-    NVMOE_TRY(run_experts(p, true, T, p->xq.as<uint8_t>(), p->x_scales.as<float>(), p->x_e8m0.as<uint32_t>(),
-                          (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, nullptr, a->gate_up_addresses,
-                          a->gate_up_slots, (const uint32_t*)gate_control.ptr, true, sets[0], scheduled, fused_quantise));
+    ExpertCall call;
+    call.T = T;
+    call.routes = (const uint32_t*)routes->ptr;
+    call.intermediates = (uint32_t*)frames.ptr;
+    call.scheduled = true;
+    call.gate_up = true;
+    call.addresses = a->gate_up_addresses;
+    call.slots = a->gate_up_slots;
+    call.control = (const uint32_t*)gate_control.ptr;
+    call.prepared = sets[0];
+    call.fuse_quantise = fused_quantise;
+    NVMOE_TRY(run_experts(p, call));
     mark(kStageQuantI);
-    if (!fused_quantise) {
-        launch_quantize_frames((const uint32_t*)frames.ptr, T, p->K, g.intermediate_size, g.act_block, p->iq.as<uint8_t>(),
-                               p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(), st);
-        p->launches++;
-        NVMOE_TRY(post_launch(p, "quantize intermediates"));
-    }
+    if (!fused_quantise) NVMOE_TRY(quantise_operands(p, false, T, frames.ptr, tensor));
     mark(kStageDown);
     // routes that are skipped (owned by another device, expert not resident) leave their rows
     // untouched: start every row at zero so that the combine adds nothing for them
     cudaMemsetAsync(outs.ptr, 0, (size_t)T * p->K * g.hidden_size * 2u, st);
-    NVMOE_TRY(run_experts(p, false, T, p->iq.as<uint8_t>(), p->i_scales.as<float>(), p->i_e8m0.as<uint32_t>(),
-                          (const uint32_t*)routes->ptr, (uint32_t*)frames.ptr, (uint16_t*)outs.ptr, a->down_addresses,
-                          a->down_slots, (const uint32_t*)down_control.ptr, true, sets[1], scheduled));
+    call.gate_up = false;
+    call.outputs = (uint16_t*)outs.ptr;
+    call.addresses = a->down_addresses;
+    call.slots = a->down_slots;
+    call.control = (const uint32_t*)down_control.ptr;
+    call.prepared = sets[1];
+    call.fuse_quantise = false;
+    NVMOE_TRY(run_experts(p, call));
     mark(kStageReduce);
     if (!a->expert_outputs) NVMOE_TRY(nvmoe_reduce(p, T, &outs, a->output));
     mark(kStageCount);

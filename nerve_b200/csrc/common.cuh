@@ -130,6 +130,7 @@ struct LayerSchedule {
     const ExpertPtrs* experts[2];
     uint32_t* grouped[2];
     uint32_t* offsets[2];
+    uint32_t* position[2];  // optional inverse of grouped: position[stage][route] (0xffffffff if dropped)
     uint32_t* tiles[2];
     uint32_t* tile_count[2];
     uint32_t* status;
@@ -143,11 +144,12 @@ void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, c
                             uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
                             size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream);
 // groups the compact slots the expert shaders would visit by expert (stable), skipping what the
-// shaders skip; writes grouped_routes and expert_offsets
+// shaders skip; writes grouped_routes and expert_offsets and, if `position` is given, the inverse
+// position[route] = place in grouped_routes (0xffffffff for routes that were skipped)
 void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,
                         const ExpertPtrs* experts, uint32_t num_experts, uint32_t max_tokens, uint32_t K,
                         uint32_t intermediate_size, uint32_t* grouped_routes, uint32_t* expert_offsets,
-                        uint32_t* status, const SortScratch& scratch, cudaStream_t stream);
+                        uint32_t* position, uint32_t* status, const SortScratch& scratch, cudaStream_t stream);
 
 // expert-parallel dispatch (schedule.cu): routes grouped by the rank owning their expert, stable
 // in source order; send_index[i] = position of source route i (kUnboundSlot if dropped),
@@ -166,6 +168,15 @@ void launch_ep_unpack(const uint16_t* returned_rows, const uint32_t* send_index,
 void launch_quantize(const uint16_t* input, uint32_t rows, uint32_t cols, uint32_t block,
                      size_t input_row_stride, uint8_t* q, float* scales_f32, uint32_t* scales_e8m0,
                      cudaStream_t stream);
+// The tensor path's operand form: row `pos` of the output is the quantised source row of route
+// grouped_routes[pos] (the token's hidden row when frames is false: source row = route / K of
+// `input` with `cols` columns; the route's own row of the intermediates frames otherwise), for pos below
+// expert_offsets[num_experts]. Scales as E8M0 words only. Expert-grouped rows are what a tiled TMA
+// load can fetch as one box per (expert, token tile).
+void launch_quantize_grouped(const void* input, bool frames, const uint32_t* grouped_routes,
+                             const uint32_t* expert_offsets, uint32_t num_experts, uint32_t max_routes, uint32_t K,
+                             uint32_t cols, uint32_t intermediate_size, uint32_t block, uint8_t* q,
+                             uint32_t* scales_e8m0, cudaStream_t stream);
 // the same for the K rows of every intermediates frame (skips the schedule words)
 void launch_quantize_frames(const uint32_t* intermediates, uint32_t tokens, uint32_t K,
                             uint32_t intermediate_size, uint32_t block, uint8_t* q, float* scales_f32,
@@ -184,10 +195,14 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     uint16_t* outputs;           // down output [T][K][H]
     uint32_t* status;
     const uint8_t* tmaps;        // tensor path: 128-byte tensor maps [expert][matrix], null = move weights with cp.async
+    // tensor path: act_q / act_e8m0 hold expert-grouped rows (row = position in grouped_routes);
+    // act_tmap is the tensor map of act_q with a box of [token tile][128 bytes] (null: fetch rows with cp.async)
+    const uint8_t* act_tmap;
+    // tensor path, gate/up only: where the down stage's grouping puts each route (its operand row)
+    const uint32_t* down_position;
     // tensor path, gate/up only, optional: the down stage's activation quantisation done in the epilogue
-    // (E4M3 bytes [route][I], f32 scales [route][I/32], E8M0 bytes [route][ceil(I/128)] words); needs act_block 32
+    // (E4M3 bytes [down_position][I], E8M0 bytes [down_position][ceil(I/128)] words); needs act_block 32
     uint8_t* q_out;
-    float* q_scales;
     uint32_t* q_e8m0;
     uint64_t* cta_trace;         // tensor path diagnostics: [2][grid][4] words per CTA, or null
     uint64_t* scale_stamps;      // tensor path: {scale pointer, generation} the derived tiles were built from

@@ -59,8 +59,9 @@ template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
 struct Config {
     static constexpr uint32_t kMatrices = GATE_UP ? 2u : 1u;
     // cp.async producers: one warp sustains only about one copy instruction every 60-130 cycles, so the
-    // path that moves the weights with them takes eight warps; with TMA they only move tokens and scales
-    static constexpr uint32_t kProducerWarps = USE_TMA ? 4u : 8u;
+    // copies of a stage are spread over eight warps (with TMA for the weights: token rows on the first
+    // four, scales on the other four)
+    static constexpr uint32_t kProducerWarps = 8u;
     static constexpr uint32_t kProducerThreads = 32u * kProducerWarps;
     static constexpr uint32_t kRowsPerPass = kProducerThreads / 8u;  // eight threads cover the 128 bytes of one row
     static constexpr uint32_t kThreads = kFirstProducerThread + kProducerThreads;
@@ -158,8 +159,17 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             bool alive = true;
             for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
                 const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
-                const int row0 = (int)((tile % m_tiles) * kBlockM);
-                const uint8_t* maps = p.tmaps + (size_t)(pair >> 16) * C::kMatrices * 128u;
+                const uint32_t m_tile = tile % m_tiles;
+                const int row0 = (int)(m_tile * kBlockM);
+                const uint32_t expert = pair >> 16;
+                const uint8_t* maps = p.tmaps + (size_t)expert * C::kMatrices * 128u;
+                // first operand row of this token tile in the expert-grouped activation matrix
+                const int token0 = (int)(__ldg(p.work.expert_offsets + expert) + (pair & 0xffffu) * N_TILE);
+                const ExpertPtrs* ptrs = p.work.experts + expert;
+                const uint8_t* scale_blocks[C::kMatrices];
+#pragma unroll
+                for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+                    scale_blocks[mx] = ptrs->ts[mx] + (size_t)m_tile * k_blocks * kScaleBlockBytes;
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++) tensormap_acquire(maps + mx * 128u);
                 for (uint32_t ks = 0; ks < k_stages; ks++) {
@@ -168,20 +178,29 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                         break;
                     }
                     // whole K blocks of this stage come by TMA; a trailing partial one is staged by the cp.async warps
-                    uint32_t whole = 0u;
+                    uint32_t whole = 0u, present = 0u;
 #pragma unroll
-                    for (uint32_t sub = 0; sub < C::kSub; sub++) whole += ((ks * C::kSub + sub + 1u) * kBlockK <= k_dim) ? 1u : 0u;
-                    if (whole != 0u) {
-                        const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
-                        mbar_arrive_expect_tx(&bars->full[slot], whole * C::kMatrices * kTmaBoxBytes);
-                        for (uint32_t sub = 0; sub < whole; sub++) {
+                    for (uint32_t sub = 0; sub < C::kSub; sub++) {
+                        whole += ((ks * C::kSub + sub + 1u) * kBlockK <= k_dim) ? 1u : 0u;
+                        present += (ks * C::kSub + sub < k_blocks) ? 1u : 0u;
+                    }
+                    // token rows (zeros past the edge of K) and weight scale blocks of every K block present
+                    const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
+                    mbar_arrive_expect_tx(&bars->full[slot], whole * C::kMatrices * kTmaBoxBytes +
+                                                                 present * (C::kBTileBytes + C::kMatrices * kScaleBlockBytes));
+                    for (uint32_t sub = 0; sub < present; sub++) {
+                        const uint32_t kb = ks * C::kSub + sub;
+                        const uint32_t block = stage + sub * C::kSubBytes;
+                        if (sub < whole) {
 #pragma unroll
                             for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                                tma_load_3d(stage + sub * C::kSubBytes + mx * kATileBytes, maps + mx * 128u, 0,
-                                            (int)(ks * C::kSub + sub), row0, &bars->full[slot]);
+                                tma_load_3d(block + mx * kATileBytes, maps + mx * 128u, 0, (int)kb, row0, &bars->full[slot]);
                         }
-                    } else {
-                        mbar_arrive(&bars->full[slot]);
+                        tma_load_2d(block + C::kMatrices * kATileBytes, p.act_tmap, (int)(kb * kBlockK), token0, &bars->full[slot]);
+#pragma unroll
+                        for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+                            bulk_copy_g2s(block + C::kMatrices * kATileBytes + C::kBTileBytes + mx * kScaleBlockBytes,
+                                          scale_blocks[mx] + (size_t)kb * kScaleBlockBytes, kScaleBlockBytes, &bars->full[slot]);
                     }
                     if (++slot == C::kStages) {
                         slot = 0u;
@@ -218,15 +237,11 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 m.w[mx] = ptrs->w[mx];
                 m.ts[mx] = ptrs->ts[mx];
             }
-            // gate/up reads the token's hidden row, down the route's own row
+            // the operand matrices are expert-grouped: token n of the tile is row first + n
 #pragma unroll
-            for (uint32_t i = 0; i < kTokenPasses; i++) {
-                const uint32_t n = my_r + kRowsPerPass * i;
-                const uint32_t ri = n < m.valid ? __ldg(p.work.grouped_routes + first + n) : 0u;
-                m.code_rows[i] = GATE_UP ? ri / K : ri;
-            }
-            const uint32_t ri = pt < m.valid ? __ldg(p.work.grouped_routes + first + pt) : 0u;
-            m.scale_row = GATE_UP ? ri / K : ri;
+            for (uint32_t i = 0; i < kTokenPasses; i++) m.code_rows[i] = first + my_r + kRowsPerPass * i;
+            // (the thread that copies token n's scales is kProducerThreads - 65 - n: see the copy below)
+            m.scale_row = first + (kProducerThreads - 65u - pt);
         };
         uint32_t it = 0u, slot = 0u, empty_parity = 1u;  // a fresh barrier passes a wait on parity 1
         long long trace_wait = 0;
@@ -274,10 +289,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     }
                 }
                 }
-                // activations: 16-byte pieces of 16 E4M3 codes, rows gathered through the route list
+                // activations: 16-byte pieces of 16 E4M3 codes (with TMA the whole tile is one box)
                 const uint32_t b_dst = smem_u32(stage + C::kMatrices * kATileBytes) + my_dst;
 #pragma unroll
-                for (uint32_t i = 0; i < kTokenPasses; i++) {
+                for (uint32_t i = 0; i < (USE_TMA ? 0u : kTokenPasses); i++) {
                     const uint32_t n = my_r + kRowsPerPass * i;
                     if (n < N_TILE) {
                         const bool ok = chunk_ok && (n < cur.valid);
@@ -288,15 +303,19 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 // scales: the derived copy already has the 32x16-byte layout tcgen05.cp reads, one 512-byte
                 // block per (row tile, K block); token scales are gathered four bytes (one K block) a row
                 unsigned char* sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
-                if (pt < 32u * C::kMatrices) {
-                    const uint32_t mx = pt >> 5, l = pt & 31u;
+                // (threads from the far end of the producer group, so that with few tokens a tile these are not
+                // the threads that carry the token rows)
+                const uint32_t st = kProducerThreads - 1u - pt;
+                if (!USE_TMA && st < 32u * C::kMatrices) {
+                    const uint32_t mx = st >> 5, l = st & 31u;
                     const uint8_t* src = cur.ts[mx] + ((size_t)cur.m_tile * k_blocks + kb) * kScaleBlockBytes + l * 16u;
                     cp_async_16(smem_u32(sf + mx * kScaleBlockBytes + l * 16u), src, 16u);
                 }
-                if (pt < N_TILE) {
-                    const bool ok = pt < cur.valid;
+                if (st >= 64u && st < 64u + N_TILE) {
+                    const uint32_t n = st - 64u;
+                    const bool ok = n < cur.valid;
                     const uint32_t* src = ok ? p.act_e8m0 + (size_t)cur.scale_row * k_blocks + kb : p.act_e8m0;
-                    cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + (pt & 31u) * 16u + (pt >> 5) * 4u), src,
+                    cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + (n & 31u) * 16u + (n >> 5) * 4u), src,
                                ok ? 4u : 0u);
                 }
                 }
@@ -432,10 +451,11 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 // while the accumulators arrive; the sixteen results are then handed round by shuffles
                 uint64_t my_row = 0u;
                 float my_weight = 0.0f;
-                uint32_t my_route = 0u;
+                uint32_t my_route = kUnboundSlot;
                 if (lane < 16u && c0 + lane < valid) {
                     const uint32_t ri = __ldg(p.work.grouped_routes + first + c0 + lane);
-                    my_route = ri;
+                    // the row of the down stage's operand matrix that this route's activations go to
+                    my_route = (GATE_UP && p.q_out != nullptr) ? __ldg(p.down_position + ri) : kUnboundSlot;
                     if (GATE_UP) {
                         my_row = reinterpret_cast<uint64_t>(reinterpret_cast<uint16_t*>(p.intermediates + (size_t)(ri / K) * frame_words) +
                                                             (size_t)(ri % K) * I);
@@ -484,18 +504,16 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                         const bool writes_scale = lane == 0u && first_row < out_rows;
 #pragma unroll
                         for (uint32_t t = 0; t < 4u; t++) {
-                            const uint32_t ri = __shfl_sync(0xffffffffu, my_route, g0 + t);
+                            const uint32_t dp = __shfl_sync(0xffffffffu, my_route, g0 + t);
                             const float scale = nvmoe_rounded_fp8_scale(m[t]);
                             const float inv = __fdiv_rn(1.0f, scale);  // exact: a power of two
                             const uint8_t q =
                                 (uint8_t)__nv_cvt_float_to_fp8(nvmoe_bf16_to_f32(bits[t]) * inv, __NV_SATFINITE, __NV_E4M3);
-                            if (c0 + g0 + t < valid) {
-                                if (row_ok) p.q_out[(size_t)ri * I + row] = q;
-                                if (writes_scale) {
-                                    p.q_scales[(size_t)ri * (I / 32u) + first_row / 32u] = scale;
-                                    reinterpret_cast<uint8_t*>(p.q_e8m0 + (size_t)ri * ((I + 127u) / 128u))[first_row / 32u] =
+                            if (dp != kUnboundSlot) {  // (lanes past `valid` and routes the down stage skips)
+                                if (row_ok) p.q_out[(size_t)dp * I + row] = q;
+                                if (writes_scale)
+                                    reinterpret_cast<uint8_t*>(p.q_e8m0 + (size_t)dp * ((I + 127u) / 128u))[first_row / 32u] =
                                         (uint8_t)(nvmoe_f32_bits(scale) >> 23);
-                                }
                             }
                         }
                     }
@@ -647,23 +665,31 @@ void launch_derive_scales_tc(const ExpertLaunch& p, bool gate_up, cudaStream_t s
     commit_stamps_kernel<<<(count + 127u) / 128u, 128, 0, stream>>>(p.work.experts, p.scale_stamps, matrices, count);
 }
 
-bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows, uint32_t cols) {
-    // The packaged [rows][cols/2] bytes seen as a 3-D tensor of 4-bit elements
-    // {128 elements, cols/128 K blocks, rows}: a box {128, 1, 128} is one operand tile. The padded 4-bit
-    // type wants 32-byte strides (cols % 64 == 0); a trailing partial K block is not part of the map.
-    if (cols < kBlockK || cols % 64u != 0u) return false;
-    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// the driver's encoder, looked up through the runtime (no link-time dependency on libcuda)
+static EncodeFn tensor_map_encoder() {
     static EncodeFn encode = nullptr;
     if (!encode) {
         cudaDriverEntryPointQueryResult q;
         void* fn = nullptr;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
             q != cudaDriverEntryPointSuccess || !fn)
-            return false;
+            return nullptr;
         encode = reinterpret_cast<EncodeFn>(fn);
     }
+    return encode;
+}
+
+bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows, uint32_t cols) {
+    // The packaged [rows][cols/2] bytes seen as a 3-D tensor of 4-bit elements
+    // {128 elements, cols/128 K blocks, rows}: a box {128, 1, 128} is one operand tile. The padded 4-bit
+    // type wants 32-byte strides (cols % 64 == 0); a trailing partial K block is not part of the map.
+    if (cols < kBlockK || cols % 64u != 0u) return false;
+    EncodeFn encode = tensor_map_encoder();
+    if (!encode) return false;
     const cuuint64_t dims[3] = {kBlockK, cols / kBlockK, rows};
     const cuuint64_t strides[2] = {kBlockK / 2u, cols / 2u};
     const cuuint32_t box[3] = {kBlockK, 1u, kBlockM};
@@ -672,6 +698,22 @@ bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows,
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, any_device_address, dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::memcpy(map128, &map, 128);
+    return true;
+}
+
+bool tc_encode_activation_map(void* map128, void* base, uint32_t rows, uint32_t cols, uint32_t n_tile) {
+    if (cols % 16u != 0u || rows == 0u) return false;
+    EncodeFn encode = tensor_map_encoder();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols};
+    const cuuint32_t box[2] = {kBlockK, n_tile};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUtensorMap map;
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     std::memcpy(map128, &map, 128);
     return true;

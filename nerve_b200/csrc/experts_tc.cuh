@@ -13,6 +13,9 @@ void tc_configure_kernels();
 // Encodes the template tensor map of a [rows][cols] weight matrix (any 32-byte aligned device address
 // will do: it is replaced per expert). False when the shape cannot use TMA.
 bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows, uint32_t cols);
+// Encodes the tensor map of an expert-grouped activation matrix [rows][cols] of E4M3 bytes with a box of
+// n_tile rows x 128 bytes (the operand tile of one K block). False when tensor maps are unavailable.
+bool tc_encode_activation_map(void* map128, void* base, uint32_t rows, uint32_t cols, uint32_t n_tile);
 // per-expert tensor maps = template + the expert's weight address (p.tmaps must be set)
 void launch_build_tensormaps_tc(const ExpertLaunch& p, bool gate_up, const uint8_t* templ, cudaStream_t stream);
 // token tile size for this call, and the (expert, token tile) list the kernels walk

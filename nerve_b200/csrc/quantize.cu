@@ -81,6 +81,23 @@ __global__ void __launch_bounds__(256) quantize_frames_kernel(const uint32_t* in
         tokens * K, I, block, q, scales_f32, scales_e8m0);
 }
 
+__global__ void __launch_bounds__(256) quantize_grouped_kernel(const void* input, bool frames, const uint32_t* grouped,
+                                                              const uint32_t* expert_offsets, uint32_t num_experts,
+                                                              uint32_t max_routes, uint32_t K, uint32_t cols, uint32_t I,
+                                                              uint32_t block, uint8_t* q, uint32_t* scales_e8m0) {
+    grid_dependency_sync();
+    const uint32_t total = min(expert_offsets[num_experts], max_routes);
+    const uint32_t frame_words = K * (I / 2u) + K;
+    quantize_body(
+        [&](uint32_t pos) {
+            const uint32_t ri = grouped[pos];
+            return frames ? reinterpret_cast<const uint16_t*>(static_cast<const uint32_t*>(input) + (size_t)(ri / K) * frame_words) +
+                                (size_t)(ri % K) * I
+                          : static_cast<const uint16_t*>(input) + (size_t)(ri / K) * cols;
+        },
+        total, cols, block, q, nullptr, scales_e8m0);
+}
+
 __global__ void __launch_bounds__(256) scales_to_e8m0_kernel(const float* scales, uint32_t rows, uint32_t cols,
                                                             uint32_t block, uint32_t* scales_e8m0, uint32_t* status) {
     const uint32_t blocks_per_row = cols / block;
@@ -116,6 +133,16 @@ void launch_quantize_frames(const uint32_t* intermediates, uint32_t tokens, uint
     if (tokens == 0u) return;
     launch_chained(quantize_frames_kernel, dim3(grid_for((uint64_t)tokens * K * (intermediate_size / block))), dim3(256), 0,
                    stream, intermediates, tokens, K, intermediate_size, block, q, scales_f32, scales_e8m0);
+}
+
+void launch_quantize_grouped(const void* input, bool frames, const uint32_t* grouped_routes,
+                             const uint32_t* expert_offsets, uint32_t num_experts, uint32_t max_routes, uint32_t K,
+                             uint32_t cols, uint32_t intermediate_size, uint32_t block, uint8_t* q,
+                             uint32_t* scales_e8m0, cudaStream_t stream) {
+    if (max_routes == 0u) return;
+    launch_chained(quantize_grouped_kernel, dim3(grid_for((uint64_t)max_routes * (cols / block))), dim3(256), 0, stream, input,
+                   frames, grouped_routes, expert_offsets, num_experts, max_routes, K, cols, intermediate_size, block, q,
+                   scales_e8m0);
 }
 
 void launch_scales_to_e8m0(const float* scales, uint32_t rows, uint32_t cols, uint32_t block,

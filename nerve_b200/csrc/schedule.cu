@@ -156,7 +156,12 @@ struct SlotKey {
 struct GroupEmit {
     const SlotKey key;
     uint32_t* grouped;
-    __device__ void operator()(uint32_t rank, uint32_t c) const { grouped[rank] = key.route_index(c); }
+    uint32_t* position;  // optional inverse: position[route] = its place in `grouped`
+    __device__ void operator()(uint32_t rank, uint32_t c) const {
+        const uint32_t ri = key.route_index(c);
+        grouped[rank] = ri;
+        if (position) position[ri] = rank;
+    }
 };
 
 // ---- kernels ---------------------------------------------------------------------------------
@@ -414,11 +419,15 @@ __device__ __forceinline__ uint32_t slot_count(const uint32_t* control, uint32_t
 }
 
 __device__ void group_small_body(SlotKey key, const uint32_t* control, uint32_t max_tokens, uint32_t* grouped,
-                                 uint32_t* expert_offsets, uint32_t* hist) {
+                                 uint32_t* expert_offsets, uint32_t* position, uint32_t* hist) {
     const uint32_t T = min_u32(control[0], max_tokens);
     key.capacity = T * key.K;
     const uint32_t count = slot_count(control, max_tokens, key.K);
-    GroupEmit emit{key, grouped};
+    if (position) {  // routes the grouping drops keep "nowhere"
+        for (uint32_t i = threadIdx.x; i < key.capacity; i += blockDim.x) position[i] = kUnboundSlot;
+        __syncthreads();
+    }
+    GroupEmit emit{key, grouped, position};
     const uint32_t buckets = key.num_experts;
     sort_single_block(count, buckets, hist, key, emit, [&](const uint32_t* base) {
         for (uint32_t b = threadIdx.x; b <= buckets; b += blockDim.x) expert_offsets[b] = base[b];
@@ -427,9 +436,9 @@ __device__ void group_small_body(SlotKey key, const uint32_t* control, uint32_t 
 
 __global__ void __launch_bounds__(1024) group_small_kernel(SlotKey key, const uint32_t* control,
                                                           uint32_t max_tokens, uint32_t* grouped,
-                                                          uint32_t* expert_offsets) {
+                                                          uint32_t* expert_offsets, uint32_t* position) {
     extern __shared__ uint32_t hist[];
-    group_small_body(key, control, max_tokens, grouped, expert_offsets, hist);
+    group_small_body(key, control, max_tokens, grouped, expert_offsets, position, hist);
 }
 
 // (expert, token tile) pairs in expert order for the tensor-core expert kernels: entry =
@@ -498,7 +507,7 @@ __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedul
     const uint32_t data_words = s.K * (s.I / 2u);
     for (uint32_t stage = 0; stage < 2u; stage++) {
         SlotKey key{s.routes, s.intermediates, s.experts[stage], s.status, s.num_experts, s.K, data_words + s.K, data_words, 0u};
-        group_small_body(key, s.control[stage], s.tokens, s.grouped[stage], s.offsets[stage], hist);
+        group_small_body(key, s.control[stage], s.tokens, s.grouped[stage], s.offsets[stage], s.position[stage], hist);
         __syncthreads();
         if (s.tiles[stage]) build_tiles_body(s.offsets[stage], s.num_experts, s.n_tile, s.tiles[stage], s.tile_count[stage]);
         __syncthreads();
@@ -506,18 +515,21 @@ __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedul
 }
 
 __global__ void __launch_bounds__(256) group_hist_kernel(SlotKey key, const uint32_t* control,
-                                                        uint32_t max_tokens, uint32_t* block_hist) {
+                                                        uint32_t max_tokens, uint32_t* block_hist, uint32_t* position) {
     key.capacity = min_u32(control[0], max_tokens) * key.K;
     key.status = nullptr;  // raised once, by the scatter pass
+    if (position)  // routes the grouping drops keep "nowhere"; the scatter pass (a later launch) fills the rest
+        for (uint32_t i = blockIdx.x * kSortChunk + threadIdx.x; i < min_u32(key.capacity, (blockIdx.x + 1u) * kSortChunk); i += blockDim.x)
+            position[i] = kUnboundSlot;
     phase_hist(slot_count(control, max_tokens, key.K), key.num_experts, block_hist, key);
 }
 
 __global__ void __launch_bounds__(256) group_scatter_kernel(SlotKey key, const uint32_t* control,
                                                            uint32_t max_tokens, uint32_t* grouped,
                                                            uint32_t* expert_offsets, const uint32_t* block_hist,
-                                                           const uint32_t* bucket_base) {
+                                                           const uint32_t* bucket_base, uint32_t* position) {
     key.capacity = min_u32(control[0], max_tokens) * key.K;
-    GroupEmit emit{key, grouped};
+    GroupEmit emit{key, grouped, position};
     phase_scatter(slot_count(control, max_tokens, key.K), key.num_experts, block_hist, bucket_base, key, emit);
     if (blockIdx.x == 0u)
         for (uint32_t b = threadIdx.x; b <= key.num_experts; b += blockDim.x) expert_offsets[b] = bucket_base[b];
@@ -741,23 +753,23 @@ void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, c
 void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,
                         const ExpertPtrs* experts, uint32_t num_experts, uint32_t max_tokens, uint32_t K,
                         uint32_t intermediate_size, uint32_t* grouped_routes, uint32_t* expert_offsets,
-                        uint32_t* status, const SortScratch& scratch, cudaStream_t stream) {
+                        uint32_t* position, uint32_t* status, const SortScratch& scratch, cudaStream_t stream) {
     const uint32_t data_words = K * (intermediate_size / 2u);
     SlotKey key{routes, intermediates, experts, status, num_experts, K, data_words + K, data_words, 0u};
     const uint32_t count = max_tokens * K;
     if (count <= kSmallSortLimit) {
         uint32_t threads = count <= 256u ? 256u : 1024u;
         group_small_kernel<<<1, threads, (num_experts + 1u) * sizeof(uint32_t), stream>>>(
-            key, control, max_tokens, grouped_routes, expert_offsets);
+            key, control, max_tokens, grouped_routes, expert_offsets, position);
         return;
     }
     const uint32_t blocks = (count + kSortChunk - 1u) / kSortChunk;
     group_hist_kernel<<<blocks, 256, num_experts * sizeof(uint32_t), stream>>>(key, control, max_tokens,
-                                                                               scratch.block_hist);
+                                                                               scratch.block_hist, position);
     phase_scan_kernel<<<1, 1024, num_experts * sizeof(uint32_t), stream>>>(scratch.block_hist, scratch.bucket_base,
                                                                             blocks, num_experts);
     group_scatter_kernel<<<blocks, 256, num_experts * sizeof(uint32_t), stream>>>(
-        key, control, max_tokens, grouped_routes, expert_offsets, scratch.block_hist, scratch.bucket_base);
+        key, control, max_tokens, grouped_routes, expert_offsets, scratch.block_hist, scratch.bucket_base, position);
 }
 
 }  // namespace nvmoe

@@ -118,6 +118,20 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tenso
         ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
         : "memory");
 }
+// 2-D tiled load (byte tensors: the barrier is credited with the bytes of the whole box, rows and
+// columns past the tensor's edge included - they arrive as zeros)
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+// linear copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) credited to the barrier
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 // a tensor map that a kernel wrote (tensormap_publish) must be acquired by the thread that uses it
 __device__ __forceinline__ void tensormap_acquire(const void* tensor_map) {
     asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tensor_map) : "memory");
