@@ -137,11 +137,13 @@ NVMOE_HD uint32_t nvmoe_f32_to_e4m3(float v) {
 
 /* Activation scale of the reference: the smallest power of two >= max(block_max, 1e-4) / 448. */
 NVMOE_HD float nvmoe_rounded_fp8_scale(float block_max) {
-    float ratio = NVMOE_FDIV(fmaxf(block_max, 1e-4f), 448.0f);
-    uint32_t bits = nvmoe_f32_bits(ratio);
-    int exponent = (int)((bits >> 23) & 0xffu) - 127;
-    if ((bits & 0x7fffffu) != 0u) exponent++;
-    return nvmoe_bits_f32((uint32_t)(exponent + 127) << 23);
+    /* 2^ceil(log2(m / 448)) for m = max(block_max, 1e-4) without the division: 448 = 1.75 * 2^8, so with
+     * m = f * 2^e (1 <= f < 2) the quotient is (f / 1.75) * 2^(e-8), which lies in (2^(e-9), 2^(e-8)] when
+     * f <= 1.75 and in (2^(e-8), 2^(e-7)) when f > 1.75; the division rounds to nearest and cannot cross
+     * either power of two. m >= 1e-4 is a normal number. */
+    uint32_t bits = nvmoe_f32_bits(fmaxf(block_max, 1e-4f));
+    uint32_t exponent = ((bits >> 23) & 0xffu) - 8u + ((bits & 0x7fffffu) > 0x600000u ? 1u : 0u);
+    return nvmoe_bits_f32(exponent << 23);
 }
 
 /* The same scale as the E8M0 byte (exponent + 127) that a block-scaled MMA consumes. */

@@ -475,7 +475,7 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
             for (uint32_t set = 0; set < 2u && ok; set++)
                 for (uint32_t i = 0; i < 4u && ok; i++)
                     ok = tc_encode_activation_map(maps + (set * 4u + i) * 128u, p->grouped_q[set].ptr, (uint32_t)R,
-                                                  (uint32_t)(set == 0u ? H : I), 16u << i);
+                                                  (uint32_t)(set == 0u ? H : I), i < 3u ? 16u << i : set == 0u ? 96u : 128u);
             if (ok) {
                 err = cudaMemcpyAsync(p->act_maps.ptr, maps, sizeof maps, cudaMemcpyHostToDevice, d->stream);
                 if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer
@@ -757,7 +757,8 @@ static int schedule_stage(nvmoe_plan* p, bool gate_up, ExpertSet* es, uint32_t T
     p->launches += (size_t)T * p->K <= 4096u ? 1u : 3u;
     if (tensor) {
         uint32_t* region = p->tile_list.as<uint32_t>() + set * tile_region_words(p);
-        launch_build_tiles(p->offsets[set].as<uint32_t>(), p->experts, tc_token_tile_for(T, p->K, p->experts), region + 64, region, st);
+        launch_build_tiles(p->offsets[set].as<uint32_t>(), p->experts, tc_token_tile_for(T, p->K, p->experts, gate_up), region + 64,
+                           region, st);
         p->launches++;
     }
     return post_launch(p, gate_up ? "gate/up schedule" : "down schedule");
@@ -841,8 +842,7 @@ static int run_experts(nvmoe_plan* p, const ExpertCall& c) {
     el.tokens = T;
     el.g = g;
     if (tensor) {
-        const uint32_t n = tc_token_tile(el);
-        const uint32_t size_index = n == 16u ? 0u : n == 32u ? 1u : n == 64u ? 2u : 3u;
+        const uint32_t size_index = tc_token_tile_index(tc_token_tile_for(T, p->K, p->experts, gate_up));
         el.act_tmap = el.tmaps ? p->act_maps.as<uint8_t>() + (set * 4u + size_index) * 128u : nullptr;
         if (c.fuse_quantise && gate_up) {
             el.q_out = p->grouped_q[1].as<uint8_t>();
@@ -1125,7 +1125,8 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
         ls.tiles_per_route[0] = (g.intermediate_size + g.gate_tile_rows - 1u) / g.gate_tile_rows;
         ls.tiles_per_route[1] = (g.hidden_size + g.down_tile_rows - 1u) / g.down_tile_rows;
         ls.num_experts = p->experts;
-        ls.n_tile = tc_token_tile_for(T, p->K, p->experts);
+        ls.n_tile[0] = tc_token_tile_for(T, p->K, p->experts, true);
+        ls.n_tile[1] = tc_token_tile_for(T, p->K, p->experts, false);
         launch_layer_schedule_small(ls, st);
         p->launches++;
         NVMOE_TRY(post_launch(p, "layer schedule"));

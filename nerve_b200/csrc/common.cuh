@@ -134,7 +134,7 @@ struct LayerSchedule {
     uint32_t* tiles[2];
     uint32_t* tile_count[2];
     uint32_t* status;
-    uint32_t tokens, expert_start, expert_count, K, I, tiles_per_route[2], num_experts, n_tile;
+    uint32_t tokens, expert_start, expert_count, K, I, tiles_per_route[2], num_experts, n_tile[2];
 };
 bool layer_schedule_is_small(uint32_t tokens, uint32_t K);
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream);

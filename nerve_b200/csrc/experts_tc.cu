@@ -28,6 +28,7 @@
 // the packaged scale tensors that is rebuilt whenever a scale record's address or generation
 // changes.  Stages are handed over with mbarriers; every wait is bounded (tcgen05.cuh).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
 #include <cstring>
@@ -42,8 +43,7 @@ using namespace tc;
 
 constexpr uint32_t kBlockM = 128u;   // weight rows per tile
 constexpr uint32_t kBlockK = 128u;   // K elements per pipeline stage = 4 MMAs of K = 32
-constexpr uint32_t kEpilogueThreads = 128u;
-constexpr uint32_t kFirstProducerThread = 192u;    // warps 0-3 epilogue, 4 MMA, 5 TMA, 6.. cp.async
+constexpr uint32_t kFirstProducerThread = 192u;    // warps 0-3 epilogue, 4 MMA, 5 TMA, 6.. cp.async, then more epilogue warps
 constexpr uint32_t kTmaBoxBytes = kBlockM * 64u;   // global bytes of one 128 x 128 box of 4-bit codes
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
@@ -61,10 +61,19 @@ struct Config {
     // cp.async producers: one warp sustains only about one copy instruction every 60-130 cycles, so the
     // copies of a stage are spread over eight warps (with TMA for the weights: token rows on the first
     // four, scales on the other four)
-    static constexpr uint32_t kProducerWarps = 8u;
+    // With TMA two cp.async warps are left with the token scales and a trailing partial K block, and the
+    // warps they free become epilogue warps: the epilogue (activation, rounding, re-quantisation: a
+    // couple of hundred instructions per value) is what large token tiles wait for, and a warp only
+    // issues one instruction at a time. Epilogue warps come in groups of four, one per quadrant of
+    // tensor-memory lanes (a warp reads the quadrant warp_id % 4); the groups share out a tile's columns.
+    static constexpr uint32_t kProducerWarps = USE_TMA ? 2u : 8u;
     static constexpr uint32_t kProducerThreads = 32u * kProducerWarps;
     static constexpr uint32_t kRowsPerPass = kProducerThreads / 8u;  // eight threads cover the 128 bytes of one row
-    static constexpr uint32_t kThreads = kFirstProducerThread + kProducerThreads;
+    static constexpr uint32_t kEpilogueGroups = USE_TMA ? 3u : 1u;
+    static constexpr uint32_t kEpilogueThreads = 128u * kEpilogueGroups;
+    static constexpr uint32_t kFirstExtraEpilogueWarp = 6u + kProducerWarps;  // a multiple of four
+    static constexpr uint32_t kThreads = kFirstProducerThread + kProducerThreads + 128u * (kEpilogueGroups - 1u);
+    static_assert(kFirstExtraEpilogueWarp % 4u == 0u || kEpilogueGroups == 1u, "extra epilogue warps keep warp % 4 = quadrant");
     static constexpr uint32_t kBTileBytes = N_TILE * 128u;
     // A stage holds kSub K blocks, each with its own operand tiles and scale blocks. Down moves one
     // matrix, so a stage of one block would carry half the bytes of a gate/up stage for the same
@@ -83,8 +92,26 @@ struct Config {
     static constexpr uint32_t kTmemColumns = kColumnsUsed <= 32u ? 32u : kColumnsUsed <= 64u ? 64u : kColumnsUsed <= 128u ? 128u : kColumnsUsed <= 256u ? 256u : 512u;
     static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024u /* alignment slack */ + 256u /* barriers */;
     static_assert(N_TILE % 16u == 0u && N_TILE >= 16u && N_TILE <= 128u, "token tile");
+    static_assert(kBTileBytes % 1024u == 0u, "the scale blocks behind the token tile keep their alignment");
     static_assert(kStages >= 3u, "pipeline too shallow");
 };
+
+// SwiGLU of the tensor path: the same expression and roundings as nvmoe_swiglu (accumulators rounded
+// to bf16, clamp, g / (1 + exp(-alpha g)) * (u + offset), result rounded to bf16) with the hardware's
+// approximate exponential and reciprocal (a few units in the last place of f32, far below the bf16
+// rounding that follows) instead of the pinned software forms: a wide token tile spends more issue
+// slots on its epilogue than on its MMAs, and the pinned forms cost several times as many.
+// Returns the bf16 bits. The CUDA-core path keeps the pinned forms.
+__device__ __forceinline__ uint32_t swiglu_bf16_bits(float gate_acc, float up_acc, float limit, float alpha, float up_offset) {
+    float g = __bfloat162float(__float2bfloat16_rn(gate_acc));
+    float u = __bfloat162float(__float2bfloat16_rn(up_acc));
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    const float act = __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + up_offset);
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(act));
+}
 
 struct Barriers {
     uint64_t full[kMaxStages];
@@ -126,7 +153,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
         }
         for (uint32_t a = 0; a < 2u; a++) {
             mbar_init(&bars->acc_full[a], 1u);
-            mbar_init(&bars->acc_empty[a], kEpilogueThreads);
+            mbar_init(&bars->acc_empty[a], C::kEpilogueThreads);
         }
         mbar_init(&bars->drain, 1u);
         bars->abort = 0u;
@@ -209,7 +236,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 }
             }
         }
-    } else if (warp >= 6u) {
+    } else if (warp >= 6u && warp < 6u + C::kProducerWarps) {
         // ===== operand producers: cp.async into the swizzled tiles, completion arrives on `full` =====
         const uint32_t pt = threadIdx.x - kFirstProducerThread;  // 0..kProducerThreads-1
         const uint32_t my_r = pt >> 3, my_c = pt & 7u;  // this thread's row (plus kRowsPerPass i) and 16-element chunk
@@ -222,7 +249,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             const uint8_t* ts[C::kMatrices];
             uint32_t code_rows[kTokenPasses];  // activation row of token my_r + kRowsPerPass i
             uint32_t scale_row;                // activation row of token pt
-            uint32_t valid, m_tile;
+            uint32_t valid, m_tile, first;
         };
         auto load_meta = [&](uint32_t tile, Meta& m) {
             const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
@@ -231,6 +258,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             const uint32_t e_begin = __ldg(p.work.expert_offsets + expert), e_end = __ldg(p.work.expert_offsets + expert + 1u);
             const uint32_t first = e_begin + n_tile * N_TILE;
             m.valid = min(N_TILE, e_end - first);
+            m.first = first;
             const ExpertPtrs* ptrs = p.work.experts + expert;
 #pragma unroll
             for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
@@ -311,7 +339,14 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     const uint8_t* src = cur.ts[mx] + ((size_t)cur.m_tile * k_blocks + kb) * kScaleBlockBytes + l * 16u;
                     cp_async_16(smem_u32(sf + mx * kScaleBlockBytes + l * 16u), src, 16u);
                 }
-                if (st >= 64u && st < 64u + N_TILE) {
+                if (USE_TMA) {
+                    for (uint32_t n = pt; n < N_TILE; n += kProducerThreads) {
+                        const bool ok = n < cur.valid;
+                        const uint32_t* src = ok ? p.act_e8m0 + (size_t)(cur.first + n) * k_blocks + kb : p.act_e8m0;
+                        cp_async_4(smem_u32(sf + C::kMatrices * kScaleBlockBytes + (n & 31u) * 16u + (n >> 5) * 4u), src,
+                                   ok ? 4u : 0u);
+                    }
+                } else if (st >= 64u && st < 64u + N_TILE) {
                     const uint32_t n = st - 64u;
                     const bool ok = n < cur.valid;
                     const uint32_t* src = ok ? p.act_e8m0 + (size_t)cur.scale_row * k_blocks + kb : p.act_e8m0;
@@ -423,6 +458,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
         __syncwarp();
     } else {
         // ===== epilogue: TMEM -> registers -> global =============================================
+        const uint32_t quad = warp & 3u;  // the quadrant of tensor-memory lanes this warp may read
+        const uint32_t epilogue_group = warp < 4u ? 0u : (warp - C::kFirstExtraEpilogueWarp) / 4u + 1u;
         const uint32_t frame_words = K * (I / 2u) + K;
         uint32_t acc_it = 0u;
         long long trace_epi_wait = 0;
@@ -439,10 +476,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             if (!mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag)) break;
             trace_epi_wait += clock64() - e0;
             tc_fence_after();
-            const uint32_t row = m_tile * kBlockM + warp * 32u + lane;
+            const uint32_t row = m_tile * kBlockM + quad * 32u + lane;
             const bool row_ok = row < out_rows;
-            const uint32_t lane_addr = tmem_base + ((warp * 32u) << 16) + acc * C::kAccColumns;
-            for (uint32_t c0 = 0; c0 < N_TILE; c0 += 16u) {
+            const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16) + acc * C::kAccColumns;
+            for (uint32_t c0 = 16u * epilogue_group; c0 < N_TILE; c0 += 16u * C::kEpilogueGroups) {
                 if (c0 >= valid) break;  // uniform: no token of this tile lives in the remaining columns
                 uint32_t d0[16], d1[16];
                 tmem_ld16(lane_addr + c0, d0);
@@ -477,11 +514,11 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     for (uint32_t t = 0; t < 4u; t++) {
                         const uint32_t j = g0 + t;
                         if (GATE_UP) {
-                            bits[t] = nvmoe_f32_to_bf16(nvmoe_swiglu(__uint_as_float(d0[j]), __uint_as_float(d1[j]),
-                                                                     p.g.swiglu_limit, p.g.swiglu_alpha, p.g.swiglu_up_offset));
+                            bits[t] = swiglu_bf16_bits(__uint_as_float(d0[j]), __uint_as_float(d1[j]), p.g.swiglu_limit,
+                                                       p.g.swiglu_alpha, p.g.swiglu_up_offset);
                         } else {
                             const float weight = __shfl_sync(0xffffffffu, my_weight, j);
-                            bits[t] = nvmoe_f32_to_bf16(__fmul_rn(__uint_as_float(d0[j]), weight));
+                            bits[t] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__uint_as_float(d0[j]), weight)));
                         }
                     }
 #pragma unroll
@@ -500,13 +537,14 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
 #pragma unroll
                             for (uint32_t t = 0; t < 4u; t++) m[t] = fmaxf(m[t], __shfl_xor_sync(0xffffffffu, m[t], o));
                         }
-                        const uint32_t first_row = m_tile * kBlockM + warp * 32u;
+                        const uint32_t first_row = m_tile * kBlockM + quad * 32u;
                         const bool writes_scale = lane == 0u && first_row < out_rows;
 #pragma unroll
                         for (uint32_t t = 0; t < 4u; t++) {
                             const uint32_t dp = __shfl_sync(0xffffffffu, my_route, g0 + t);
                             const float scale = nvmoe_rounded_fp8_scale(m[t]);
-                            const float inv = __fdiv_rn(1.0f, scale);  // exact: a power of two
+                            // 1 / scale, exact: the scale is a power of two with a biased exponent in [107, 247]
+                            const float inv = __uint_as_float(0x7f000000u - __float_as_uint(scale));
                             const uint8_t q =
                                 (uint8_t)__nv_cvt_float_to_fp8(nvmoe_bf16_to_f32(bits[t]) * inv, __NV_SATFINITE, __NV_E4M3);
                             if (dp != kUnboundSlot) {  // (lanes past `valid` and routes the down stage skips)
@@ -605,20 +643,21 @@ void launch_n(const ExpertLaunch& p, cudaStream_t stream) {
 
 template <bool GATE_UP>
 void launch(const ExpertLaunch& p, cudaStream_t stream) {
-    const uint32_t n = tc_token_tile(p);
+    constexpr uint32_t kWide = GATE_UP ? 96u : 128u;
+    const uint32_t n = tc_token_tile_for(p.tokens, p.g.routed_k + p.g.always_count, p.work.num_experts, GATE_UP);
     if (p.tmaps != nullptr) {
         switch (n) {
             case 16u: launch_n<GATE_UP, 16u, true>(p, stream); break;
             case 32u: launch_n<GATE_UP, 32u, true>(p, stream); break;
             case 64u: launch_n<GATE_UP, 64u, true>(p, stream); break;
-            default: launch_n<GATE_UP, 128u, true>(p, stream); break;
+            default: launch_n<GATE_UP, kWide, true>(p, stream); break;
         }
     } else {
         switch (n) {
             case 16u: launch_n<GATE_UP, 16u, false>(p, stream); break;
             case 32u: launch_n<GATE_UP, 32u, false>(p, stream); break;
             case 64u: launch_n<GATE_UP, 64u, false>(p, stream); break;
-            default: launch_n<GATE_UP, 128u, false>(p, stream); break;
+            default: launch_n<GATE_UP, kWide, false>(p, stream); break;
         }
     }
 }
@@ -639,16 +678,16 @@ bool tc_shape_supported(const nvmoe_geometry& g) {
 
 bool tc_enabled_by_default() { return true; }
 
-uint32_t tc_token_tile_for(uint32_t tokens, uint32_t routes_per_token, uint32_t num_experts) {
+uint32_t tc_token_tile_for(uint32_t tokens, uint32_t routes_per_token, uint32_t num_experts, bool gate_up) {
     // tokens per expert if routing were uniform; skew only adds token tiles
     const uint32_t routes = tokens * routes_per_token;
     const uint32_t per_expert = (routes + num_experts - 1u) / num_experts;
-    return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : 128u;
+    // gate/up holds two accumulators per token column: 96 columns is the widest tile that still leaves
+    // tensor memory for a second pair, so that the epilogue of one tile overlaps the MMAs of the next
+    return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : gate_up ? 96u : 128u;
 }
 
-uint32_t tc_token_tile(const ExpertLaunch& p) {
-    return tc_token_tile_for(p.tokens, p.g.routed_k + p.g.always_count, p.work.num_experts);
-}
+uint32_t tc_token_tile_index(uint32_t n_tile) { return n_tile == 16u ? 0u : n_tile == 32u ? 1u : n_tile == 64u ? 2u : 3u; }
 
 size_t tc_derived_scale_bytes(uint32_t rows, uint32_t cols) {
     return (size_t)((rows + kBlockM - 1u) / kBlockM) * ((cols + kBlockK - 1u) / kBlockK) * kScaleBlockBytes;
@@ -725,15 +764,13 @@ void launch_build_tensormaps_tc(const ExpertLaunch& p, bool gate_up, const uint8
                                                                               const_cast<uint8_t*>(p.tmaps), matrices);
 }
 
-void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream) {
-    launch_build_tiles(p.work.expert_offsets, p.work.num_experts, tc_token_tile(p), p.tile_list, p.tile_count, stream);
-}
+
 
 void tc_configure_kernels() {
     configure_one<true, 16u>();
     configure_one<true, 32u>();
     configure_one<true, 64u>();
-    configure_one<true, 128u>();
+    configure_one<true, 96u>();
     configure_one<false, 16u>();
     configure_one<false, 32u>();
     configure_one<false, 64u>();

@@ -18,10 +18,10 @@ bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows,
 bool tc_encode_activation_map(void* map128, void* base, uint32_t rows, uint32_t cols, uint32_t n_tile);
 // per-expert tensor maps = template + the expert's weight address (p.tmaps must be set)
 void launch_build_tensormaps_tc(const ExpertLaunch& p, bool gate_up, const uint8_t* templ, cudaStream_t stream);
-// token tile size for this call, and the (expert, token tile) list the kernels walk
-uint32_t tc_token_tile(const ExpertLaunch& p);
-uint32_t tc_token_tile_for(uint32_t tokens, uint32_t routes_per_token, uint32_t num_experts);
-void launch_build_tiles_tc(const ExpertLaunch& p, cudaStream_t stream);
+// token tile size of a stage for this many tokens (the (expert, token tile) list must be built with it)
+uint32_t tc_token_tile_for(uint32_t tokens, uint32_t routes_per_token, uint32_t num_experts, bool gate_up);
+// which of a stage's four tile sizes (and activation tensor maps) that is
+uint32_t tc_token_tile_index(uint32_t n_tile);
 // bytes of the derived (tiled) scale copy of one expert matrix with `rows` x `cols` elements
 size_t tc_derived_scale_bytes(uint32_t rows, uint32_t cols);
 // re-tiles the scales of every expert whose scale record changed since the last call

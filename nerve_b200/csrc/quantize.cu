@@ -22,7 +22,8 @@ __device__ __forceinline__ uint32_t to_e4m3x4(float a, float b, float c, float d
     return lo | (hi << 16);
 }
 
-// One warp per (row, block of `block` columns); a lane owns 4 columns at a time.
+// A lane owns 4 columns at a time, so a block of `block` columns keeps block/4 lanes busy: a warp takes
+// one block of 128 or more columns, or 32*4/block smaller ones side by side (four blocks of 32).
 // row_of(r) gives the bf16 row pointer, so the same body serves plain matrices and MoE frames.
 template <class RowFn>
 __device__ void quantize_body(RowFn row_of, uint32_t rows, uint32_t cols, uint32_t block, uint8_t* q,
@@ -32,31 +33,42 @@ __device__ void quantize_body(RowFn row_of, uint32_t rows, uint32_t cols, uint32
     const uint32_t blocks_per_row = cols / block;
     const uint32_t words128 = (cols + 127u) / 128u;
     const uint64_t total = (uint64_t)rows * blocks_per_row;
-    for (uint64_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < total; item += warps_per_grid) {
-        const uint32_t r = (uint32_t)(item / blocks_per_row), b = (uint32_t)(item % blocks_per_row);
+    // lanes per block: a power of two that divides 32 (blocks of 32, 64 or 128+ columns), else the whole warp
+    const uint32_t quarter = block / 4u;
+    const uint32_t lanes = (quarter == 8u || quarter == 16u) ? quarter : 32u;
+    const uint32_t side_by_side = 32u / lanes;
+    const uint32_t group = lane / lanes, gl = lane % lanes;
+    for (uint64_t first = (uint64_t)((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * side_by_side; first < total;
+         first += (uint64_t)warps_per_grid * side_by_side) {
+        const uint64_t item = first + group;
+        const bool active = item < total;
+        const uint32_t r = active ? (uint32_t)(item / blocks_per_row) : 0u, b = active ? (uint32_t)(item % blocks_per_row) : 0u;
         // rows of a frame are only 4-byte aligned when the route count is odd: 4-byte loads
         const uint32_t* in = reinterpret_cast<const uint32_t*>(row_of(r) + (size_t)b * block);
         float m = 0.0f;
-        for (uint32_t c4 = lane; c4 < block / 4u; c4 += 32u) {
-            uint2 v = make_uint2(in[2u * c4], in[2u * c4 + 1u]);
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(nvmoe_bf16_to_f32(v.x)), fabsf(nvmoe_bf16_to_f32(v.x >> 16))),
-                               fmaxf(fabsf(nvmoe_bf16_to_f32(v.y)), fabsf(nvmoe_bf16_to_f32(v.y >> 16)))));
+        if (active) {
+            for (uint32_t c4 = gl; c4 < quarter; c4 += lanes) {
+                uint2 v = make_uint2(in[2u * c4], in[2u * c4 + 1u]);
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(nvmoe_bf16_to_f32(v.x)), fabsf(nvmoe_bf16_to_f32(v.x >> 16))),
+                                   fmaxf(fabsf(nvmoe_bf16_to_f32(v.y)), fabsf(nvmoe_bf16_to_f32(v.y >> 16)))));
+            }
         }
-        m = warp_max(m);
+        for (uint32_t o = lanes >> 1; o > 0u; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (!active) continue;
         const float scale = nvmoe_rounded_fp8_scale(m);
         const float inv = __fdiv_rn(1.0f, scale);  // exact: the scale is a power of two
         uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)r * cols + (size_t)b * block);
-        for (uint32_t c4 = lane; c4 < block / 4u; c4 += 32u) {
+        for (uint32_t c4 = gl; c4 < quarter; c4 += lanes) {
             uint2 v = make_uint2(in[2u * c4], in[2u * c4 + 1u]);
             out[c4] = to_e4m3x4(nvmoe_bf16_to_f32(v.x) * inv, nvmoe_bf16_to_f32(v.x >> 16) * inv,
                                 nvmoe_bf16_to_f32(v.y) * inv, nvmoe_bf16_to_f32(v.y >> 16) * inv);
         }
-        if (scales_f32 && lane == 0u) scales_f32[(size_t)r * blocks_per_row + b] = scale;
+        if (scales_f32 && gl == 0u) scales_f32[(size_t)r * blocks_per_row + b] = scale;
         if (scales_e8m0) {
             // one byte per 32 columns; this block covers block/32 of them
             uint8_t* bytes = reinterpret_cast<uint8_t*>(scales_e8m0 + (size_t)r * words128);
             const uint32_t e8 = nvmoe_f32_bits(scale) >> 23;
-            for (uint32_t j = lane; j < block / 32u; j += 32u) bytes[b * (block / 32u) + j] = (uint8_t)e8;
+            for (uint32_t j = gl; j < block / 32u; j += lanes) bytes[b * (block / 32u) + j] = (uint8_t)e8;
         }
     }
 }
@@ -113,6 +125,7 @@ __global__ void __launch_bounds__(256) scales_to_e8m0_kernel(const float* scales
     }
 }
 
+// blocks for `warps` warp-sized work items (callers pass one item per scale block; a warp may take several)
 uint32_t grid_for(uint64_t warps) {
     uint64_t blocks = (warps + 7u) / 8u;
     return (uint32_t)(blocks < 1u ? 1u : (blocks > 148u * 16u ? 148u * 16u : blocks));

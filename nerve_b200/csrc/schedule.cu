@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedul
         SlotKey key{s.routes, s.intermediates, s.experts[stage], s.status, s.num_experts, s.K, data_words + s.K, data_words, 0u};
         group_small_body(key, s.control[stage], s.tokens, s.grouped[stage], s.offsets[stage], s.position[stage], hist);
         __syncthreads();
-        if (s.tiles[stage]) build_tiles_body(s.offsets[stage], s.num_experts, s.n_tile, s.tiles[stage], s.tile_count[stage]);
+        if (s.tiles[stage]) build_tiles_body(s.offsets[stage], s.num_experts, s.n_tile[stage], s.tiles[stage], s.tile_count[stage]);
         __syncthreads();
     }
 }
