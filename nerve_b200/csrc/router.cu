@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(64) router_linear_kernel(const uint16_t* __res
 
     // The sum order of a lane is fixed (its words in ascending order), the load order is not: the
     // loads of kDepth steps are issued together so that their latencies overlap.
-    constexpr int kDepth = TT * ET <= 16 ? 4 : 1;
+    constexpr int kDepth = TT * ET <= 16 ? 4 : 2;
     for (uint32_t cw0 = v; cw0 < words; cw0 += 64u * kDepth) {
         uint32_t xr[kDepth][TT], wr[kDepth][ET];
 #pragma unroll
@@ -379,8 +379,8 @@ void launch_router_linear(const uint16_t* x, const uint16_t* w, const uint16_t* 
         dim3 grid((outputs + 3u) / 4u, (tokens + 1u) / 2u);
         launch_chained(router_linear_kernel<2, 4>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
     } else {
-        dim3 grid((outputs + 15u) / 16u, (tokens + 7u) / 8u);
-        launch_chained(router_linear_kernel<8, 16>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
+        dim3 grid((outputs + 15u) / 16u, (tokens + 3u) / 4u);
+        launch_chained(router_linear_kernel<4, 16>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
     }
 }
 
