@@ -47,7 +47,7 @@ constexpr uint32_t kFirstProducerThread = 192u;    // warps 0-3 epilogue, 4 MMA,
 constexpr uint32_t kTmaBoxBytes = kBlockM * 64u;   // global bytes of one 128 x 128 box of 4-bit codes
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
-constexpr uint32_t kSmemBudget = 215u * 1024u;
+constexpr uint32_t kSmemBudget = 225u * 1024u;  // of the 227 KB a CTA may have; the rest is alignment slack and barriers
 constexpr uint32_t kMaxStages = 8u;
 
 struct TileList {
