@@ -461,13 +461,13 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
     want(p->i_scales, sizeof(float) * R * (I / g.act_block));
     want(p->i_e8m0, sizeof(uint32_t) * R * ((I + 127u) / 128u));
     want(p->tile_list, sizeof(uint32_t) * 2u * tile_region_words(p));
+    want(p->position[0], sizeof(uint32_t) * R);
+    want(p->position[1], sizeof(uint32_t) * R);
     if (tc_shape_supported(g)) {
         want(p->grouped_q[0], R * H);
         want(p->grouped_q[1], R * I);
         want(p->grouped_e8m0[0], sizeof(uint32_t) * R * ((H + 127u) / 128u));
         want(p->grouped_e8m0[1], sizeof(uint32_t) * R * ((I + 127u) / 128u));
-        want(p->position[0], sizeof(uint32_t) * R);
-        want(p->position[1], sizeof(uint32_t) * R);
         want(p->act_maps, 8u * 128u);
         if (err == cudaSuccess) {
             unsigned char maps[8 * 128];
@@ -752,8 +752,8 @@ static int schedule_stage(nvmoe_plan* p, bool gate_up, ExpertSet* es, uint32_t T
     const int set = gate_up ? 0 : 1;
     cudaStream_t st = p->device->stream;
     launch_group_slots(routes, intermediates, control, es->ptrs.as<ExpertPtrs>(), p->experts, T, p->K, p->g.intermediate_size,
-                       p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(),
-                       tensor ? p->position[set].as<uint32_t>() : nullptr, p->status.as<uint32_t>(), sort_scratch(p), st);
+                       p->grouped[set].as<uint32_t>(), p->offsets[set].as<uint32_t>(), p->position[set].as<uint32_t>(),
+                       p->status.as<uint32_t>(), sort_scratch(p), st);
     p->launches += (size_t)T * p->K <= 4096u ? 1u : 3u;
     if (tensor) {
         uint32_t* region = p->tile_list.as<uint32_t>() + set * tile_region_words(p);
@@ -966,7 +966,7 @@ int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, 
     NVMOE_TRY(check_buffer(p, output, (size_t)T * g.hidden_size * 2u, "output"));
     NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
     launch_reduce((const uint16_t*)expert_outputs->ptr, (uint16_t*)output->ptr, T, p->K, g.hidden_size, g.reduce_scale,
-                  p->device->stream);
+                  nullptr, p->device->stream);
     p->launches++;
     return post_launch(p, "reduce");
 }
@@ -1112,7 +1112,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
             ls.experts[i] = sets[i]->ptrs.as<ExpertPtrs>();
             ls.grouped[i] = p->grouped[i].as<uint32_t>();
             ls.offsets[i] = p->offsets[i].as<uint32_t>();
-            ls.position[i] = tensor ? p->position[i].as<uint32_t>() : nullptr;
+            ls.position[i] = p->position[i].as<uint32_t>();
             ls.tile_count[i] = tensor ? p->tile_list.as<uint32_t>() + i * tile_region_words(p) : nullptr;
             ls.tiles[i] = tensor ? ls.tile_count[i] + 64 : nullptr;
         }
@@ -1161,9 +1161,10 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     mark(kStageQuantI);
     if (!fused_quantise) NVMOE_TRY(quantise_operands(p, false, T, frames.ptr, tensor));
     mark(kStageDown);
-    // routes that are skipped (owned by another device, expert not resident) leave their rows
-    // untouched: start every row at zero so that the combine adds nothing for them
-    cudaMemsetAsync(outs.ptr, 0, (size_t)T * p->K * g.hidden_size * 2u, st);
+    // routes that are skipped (owned by another device, expert not resident) leave their rows untouched:
+    // the combine below reads the down stage's position table and counts them as zeros; rows handed to
+    // the caller instead start at zero
+    if (a->expert_outputs) cudaMemsetAsync(outs.ptr, 0, (size_t)T * p->K * g.hidden_size * 2u, st);
     call.gate_up = false;
     call.outputs = (uint16_t*)outs.ptr;
     call.addresses = a->down_addresses;
@@ -1173,7 +1174,12 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     call.fuse_quantise = false;
     NVMOE_TRY(run_experts(p, call));
     mark(kStageReduce);
-    if (!a->expert_outputs) NVMOE_TRY(nvmoe_reduce(p, T, &outs, a->output));
+    if (!a->expert_outputs) {
+        launch_reduce((const uint16_t*)outs.ptr, (uint16_t*)a->output->ptr, T, p->K, g.hidden_size, g.reduce_scale,
+                      p->position[1].as<uint32_t>(), st);
+        p->launches++;
+        NVMOE_TRY(post_launch(p, "reduce"));
+    }
     mark(kStageCount);
     p->events_valid = true;
     p->report.batch_width = T;

@@ -215,8 +215,9 @@ void configure_simt_kernels();
 void launch_gate_up_simt(const ExpertLaunch& p, cudaStream_t stream);
 void launch_down_simt(const ExpertLaunch& p, cudaStream_t stream);
 
-// reduce.cu: moe_reduce_batch1_bf16
+// reduce.cu: moe_reduce_batch1_bf16. `computed` (optional, [tokens * K]) marks with 0xffffffff the routes
+// whose rows were never written: they count as zeros, so the rows need no clearing beforehand.
 void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t tokens, uint32_t K,
-                   uint32_t hidden, float routed_scale, cudaStream_t stream);
+                   uint32_t hidden, float routed_scale, const uint32_t* computed, cudaStream_t stream);
 
 }  // namespace nvmoe

@@ -13,7 +13,8 @@ namespace {
 
 __global__ void __launch_bounds__(256) reduce_kernel(const uint32_t* __restrict__ expert_outputs,
                                                     uint32_t* __restrict__ output, uint32_t tokens, uint32_t K,
-                                                    uint32_t hidden_words, float routed_scale) {
+                                                    uint32_t hidden_words, float routed_scale,
+                                                    const uint32_t* __restrict__ computed) {
     grid_dependency_sync();
     const uint64_t total = (uint64_t)tokens * hidden_words;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -21,7 +22,8 @@ __global__ void __launch_bounds__(256) reduce_kernel(const uint32_t* __restrict_
         const uint32_t* in = expert_outputs + (size_t)t * K * hidden_words + word;
         float lo = 0.0f, hi = 0.0f;
         for (uint32_t r = 0; r < K; r++) {
-            const uint32_t c = in[(size_t)r * hidden_words];
+            // a route the down stage skipped (computed[route] says "nowhere") counts as a row of zeros
+            const uint32_t c = (computed && computed[(size_t)t * K + r] == kUnboundSlot) ? 0u : in[(size_t)r * hidden_words];
             lo = nvmoe_round_bf16(__fadd_rn(lo, nvmoe_bf16_to_f32(c)));
             hi = nvmoe_round_bf16(__fadd_rn(hi, nvmoe_bf16_to_f32(c >> 16)));
         }
@@ -32,14 +34,14 @@ __global__ void __launch_bounds__(256) reduce_kernel(const uint32_t* __restrict_
 }  // namespace
 
 void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t tokens, uint32_t K, uint32_t hidden,
-                   float routed_scale, cudaStream_t stream) {
+                   float routed_scale, const uint32_t* computed, cudaStream_t stream) {
     if (tokens == 0u) return;
     const uint64_t total = (uint64_t)tokens * (hidden / 2u);
     uint64_t blocks = (total + 255u) / 256u;
     if (blocks > 148u * 8u) blocks = 148u * 8u;
     launch_chained(reduce_kernel, dim3((uint32_t)blocks), dim3(256), 0, stream,
                    reinterpret_cast<const uint32_t*>(expert_outputs), reinterpret_cast<uint32_t*>(output), tokens, K,
-                   hidden / 2u, routed_scale);
+                   hidden / 2u, routed_scale, computed);
 }
 
 }  // namespace nvmoe
