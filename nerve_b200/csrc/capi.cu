@@ -475,7 +475,7 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
             for (uint32_t set = 0; set < 2u && ok; set++)
                 for (uint32_t i = 0; i < 4u && ok; i++)
                     ok = tc_encode_activation_map(maps + (set * 4u + i) * 128u, p->grouped_q[set].ptr, (uint32_t)R,
-                                                  (uint32_t)(set == 0u ? H : I), i < 3u ? 16u << i : set == 0u ? 96u : 128u);
+                                                  (uint32_t)(set == 0u ? H : I), i < 3u ? 16u << i : 96u);
             if (ok) {
                 err = cudaMemcpyAsync(p->act_maps.ptr, maps, sizeof maps, cudaMemcpyHostToDevice, d->stream);
                 if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer

@@ -55,9 +55,20 @@ struct TileList {
     const uint32_t* count;   // number of entries
 };
 
-template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
+// ROW_PAIR (down only): a tile covers two 128-row tiles of the one weight matrix, handled as the two
+// "matrices" of a stage exactly as gate and up are: two accumulators alternate (one MMA cannot follow
+// another into the same accumulator at full rate) and the token tile is fetched once for 256 rows. Used
+// for the wide token tiles of large batches; small batches keep 128-row tiles, which spread better
+// over the SMs.
+template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA, bool ROW_PAIR>
 struct Config {
-    static constexpr uint32_t kMatrices = GATE_UP ? 2u : 1u;
+    static_assert(!(GATE_UP && ROW_PAIR), "gate/up already holds two matrices a stage");
+    static constexpr uint32_t kMatrices = (GATE_UP || ROW_PAIR) ? 2u : 1u;
+    static constexpr uint32_t kSources = GATE_UP ? 2u : 1u;        // weight tensors (and tensor maps) per expert
+    static constexpr uint32_t kTileRows = kMatrices / kSources * kBlockM;  // weight rows a tile covers
+    // matrix mx of a stage = weight tensor source_of(mx), rows shifted by row_shift(mx)
+    static constexpr uint32_t source_of(uint32_t mx) { return GATE_UP ? mx : 0u; }
+    static constexpr uint32_t row_shift(uint32_t mx) { return ROW_PAIR ? mx * kBlockM : 0u; }
     // cp.async producers: one warp sustains only about one copy instruction every 60-130 cycles, so the
     // copies of a stage are spread over eight warps (with TMA for the weights: token rows on the first
     // four, scales on the other four)
@@ -78,7 +89,7 @@ struct Config {
     // A stage holds kSub K blocks, each with its own operand tiles and scale blocks. Down moves one
     // matrix, so a stage of one block would carry half the bytes of a gate/up stage for the same
     // barrier traffic and issue overhead: it takes two blocks a stage.
-    static constexpr uint32_t kSub = GATE_UP ? 1u : 2u;
+    static constexpr uint32_t kSub = kMatrices == 2u ? 1u : 2u;
     // every block starts on a 1024-byte boundary: the 128-byte swizzle is a function of the address
     static constexpr uint32_t kSubBytes =
         (kMatrices * kATileBytes + kBTileBytes + (kMatrices + 1u) * kScaleBlockBytes + 1023u) / 1024u * 1024u;
@@ -123,9 +134,10 @@ struct Barriers {
     uint32_t abort;
 };
 
-template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
-__global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 1) experts_tc_kernel(ExpertLaunch p, TileList list) {
-    using C = Config<GATE_UP, N_TILE, USE_TMA>;
+template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA, bool ROW_PAIR>
+__global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::kThreads), 1)
+    experts_tc_kernel(ExpertLaunch p, TileList list) {
+    using C = Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>;
     constexpr uint32_t kThreads = C::kThreads, kProducerThreads = C::kProducerThreads, kRowsPerPass = C::kRowsPerPass;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -140,7 +152,14 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
     const uint32_t out_rows = GATE_UP ? I : H;
     const uint32_t k_blocks = (k_dim + kBlockK - 1u) / kBlockK;
     const uint32_t k_stages = (k_blocks + C::kSub - 1u) / C::kSub;
-    const uint32_t m_tiles = (out_rows + kBlockM - 1u) / kBlockM;
+    const uint32_t m_tiles = (out_rows + C::kTileRows - 1u) / C::kTileRows;   // tiles along the weight rows
+    const uint32_t row_tiles = (out_rows + kBlockM - 1u) / kBlockM;           // 128-row tiles (scale blocks are kept per these)
+    // the derived scale blocks of matrix mx of tile m_tile (a second half past the last rows borrows the first's:
+    // its weights arrive as zeros)
+    auto scale_tile = [&](uint32_t m_tile, uint32_t mx) {
+        const uint32_t t = ROW_PAIR ? 2u * m_tile + mx : m_tile;
+        return t < row_tiles ? t : t - 1u;
+    };
     // cycle counters of CTA 0, one writer per role (diagnostics; words 16.. of the tile-count block)
     uint64_t* trace = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(list.count) + 16) + (GATE_UP ? 0 : 12);
     if (blockIdx.x == 0u && threadIdx.x == 0u) trace[8] = global_timer_ns();  // kernel entry of CTA 0
@@ -187,18 +206,18 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
                 const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
                 const uint32_t m_tile = tile % m_tiles;
-                const int row0 = (int)(m_tile * kBlockM);
+                const int row0 = (int)(m_tile * C::kTileRows);
                 const uint32_t expert = pair >> 16;
-                const uint8_t* maps = p.tmaps + (size_t)expert * C::kMatrices * 128u;
+                const uint8_t* maps = p.tmaps + (size_t)expert * C::kSources * 128u;
                 // first operand row of this token tile in the expert-grouped activation matrix
                 const int token0 = (int)(__ldg(p.work.expert_offsets + expert) + (pair & 0xffffu) * N_TILE);
                 const ExpertPtrs* ptrs = p.work.experts + expert;
                 const uint8_t* scale_blocks[C::kMatrices];
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                    scale_blocks[mx] = ptrs->ts[mx] + (size_t)m_tile * k_blocks * kScaleBlockBytes;
+                    scale_blocks[mx] = ptrs->ts[C::source_of(mx)] + (size_t)scale_tile(m_tile, mx) * k_blocks * kScaleBlockBytes;
 #pragma unroll
-                for (uint32_t mx = 0; mx < C::kMatrices; mx++) tensormap_acquire(maps + mx * 128u);
+                for (uint32_t mx = 0; mx < C::kSources; mx++) tensormap_acquire(maps + mx * 128u);
                 for (uint32_t ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag)) {
                         alive = false;
@@ -221,7 +240,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                         if (sub < whole) {
 #pragma unroll
                             for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                                tma_load_3d(block + mx * kATileBytes, maps + mx * 128u, 0, (int)kb, row0, &bars->full[slot]);
+                                tma_load_3d(block + mx * kATileBytes, maps + C::source_of(mx) * 128u, 0, (int)kb,
+                                            row0 + (int)C::row_shift(mx), &bars->full[slot]);  // rows past the matrix: zeros
                         }
                         tma_load_2d(block + C::kMatrices * kATileBytes, p.act_tmap, (int)(kb * kBlockK), token0, &bars->full[slot]);
 #pragma unroll
@@ -262,8 +282,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             const ExpertPtrs* ptrs = p.work.experts + expert;
 #pragma unroll
             for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
-                m.w[mx] = ptrs->w[mx];
-                m.ts[mx] = ptrs->ts[mx];
+                m.w[mx] = ptrs->w[C::source_of(mx)];
+                m.ts[mx] = ptrs->ts[C::source_of(mx)];
             }
             // the operand matrices are expert-grouped: token n of the tile is row first + n
 #pragma unroll
@@ -280,13 +300,15 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
         if (blockIdx.x < tile_count) load_meta(blockIdx.x, cur);
         for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
             if (tile + gridDim.x < tile_count) load_meta(tile + gridDim.x, nxt);
-            const uint32_t row0 = cur.m_tile * kBlockM;
-            const uint32_t rows_here = min(kBlockM, out_rows - row0);
-            // this thread's first weight row of the tile; its other rows are 16 rows apart
+            // this thread's first weight row of each matrix of the tile; its other rows are kRowsPerPass apart
             const uint8_t* wcol[C::kMatrices];
+            uint32_t rows_here[C::kMatrices];
 #pragma unroll
-            for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+            for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
+                const uint32_t row0 = cur.m_tile * C::kTileRows + C::row_shift(mx);
+                rows_here[mx] = row0 < out_rows ? min(kBlockM, out_rows - row0) : 0u;
                 wcol[mx] = cur.w[mx] + (size_t)(row0 + my_r) * row_bytes + my_c * 8u;
+            }
             const size_t row_step = (size_t)kRowsPerPass * row_bytes;
             for (uint32_t ks = 0; ks < k_stages; ks++, it++) {
                 const long long w0 = clock64();
@@ -312,7 +334,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
 #pragma unroll
                     for (uint32_t i = 0; i < kBlockM / kRowsPerPass; i++) {
                         // rows my_r + kRowsPerPass i share (row & 7), so the swizzled offset only moves by whole rows
-                        const bool ok = chunk_ok && (my_r + kRowsPerPass * i < rows_here);
+                        const bool ok = chunk_ok && (my_r + kRowsPerPass * i < rows_here[mx]);
                         cp_async_8(a_dst + i * (kRowsPerPass * 128u), ok ? src + i * row_step : cur.w[mx], ok ? 8u : 0u);
                     }
                 }
@@ -336,7 +358,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                 const uint32_t st = kProducerThreads - 1u - pt;
                 if (!USE_TMA && st < 32u * C::kMatrices) {
                     const uint32_t mx = st >> 5, l = st & 31u;
-                    const uint8_t* src = cur.ts[mx] + ((size_t)cur.m_tile * k_blocks + kb) * kScaleBlockBytes + l * 16u;
+                    const uint8_t* src = cur.ts[mx] + ((size_t)scale_tile(cur.m_tile, mx) * k_blocks + kb) * kScaleBlockBytes + l * 16u;
                     cp_async_16(smem_u32(sf + mx * kScaleBlockBytes + l * 16u), src, 16u);
                 }
                 if (USE_TMA) {
@@ -476,14 +498,14 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
             if (!mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag)) break;
             trace_epi_wait += clock64() - e0;
             tc_fence_after();
-            const uint32_t row = m_tile * kBlockM + quad * 32u + lane;
+            const uint32_t row = m_tile * C::kTileRows + quad * 32u + lane;  // (with row pairs: of the first half)
             const bool row_ok = row < out_rows;
             const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16) + acc * C::kAccColumns;
             for (uint32_t c0 = 16u * epilogue_group; c0 < N_TILE; c0 += 16u * C::kEpilogueGroups) {
                 if (c0 >= valid) break;  // uniform: no token of this tile lives in the remaining columns
                 uint32_t d0[16], d1[16];
                 tmem_ld16(lane_addr + c0, d0);
-                if (GATE_UP) tmem_ld16(lane_addr + N_TILE + c0, d1);
+                if (C::kMatrices == 2u) tmem_ld16(lane_addr + N_TILE + c0, d1);  // up, or the second 128 rows
                 // lane j < 16 works out where token c0 + j of the tile goes (and its route weight)
                 // while the accumulators arrive; the sixteen results are then handed round by shuffles
                 uint64_t my_row = 0u;
@@ -525,6 +547,12 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
                     for (uint32_t t = 0; t < 4u; t++) {
                         uint16_t* out = reinterpret_cast<uint16_t*>(__shfl_sync(0xffffffffu, my_row, g0 + t));
                         if (c0 + g0 + t < valid && row_ok) out[row] = (uint16_t)bits[t];
+                        if (ROW_PAIR) {  // the second accumulator holds the next 128 output rows of the same tokens
+                            const float weight = __shfl_sync(0xffffffffu, my_weight, g0 + t);
+                            const uint32_t second = (uint32_t)__bfloat16_as_ushort(
+                                __float2bfloat16_rn(__fmul_rn(__uint_as_float(d1[g0 + t]), weight)));
+                            if (c0 + g0 + t < valid && row + kBlockM < out_rows) out[row + kBlockM] = (uint16_t)second;
+                        }
                     }
                     if (quantise) {
                         // the activation quantisation of the down stage, on the values just rounded to bf16: one
@@ -537,7 +565,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA>::kThreads), 
 #pragma unroll
                             for (uint32_t t = 0; t < 4u; t++) m[t] = fmaxf(m[t], __shfl_xor_sync(0xffffffffu, m[t], o));
                         }
-                        const uint32_t first_row = m_tile * kBlockM + quad * 32u;
+                        const uint32_t first_row = m_tile * C::kTileRows + quad * 32u;
                         const bool writes_scale = lane == 0u && first_row < out_rows;
 #pragma unroll
                         for (uint32_t t = 0; t < 4u; t++) {
@@ -631,19 +659,24 @@ __global__ void __launch_bounds__(32) build_tensormaps_kernel(const ExpertPtrs* 
 
 int g_sm_count[16] = {0};
 
+// wide token tiles of the down stage take two row tiles at a time
+template <bool GATE_UP, uint32_t N_TILE>
+constexpr bool row_pair() { return !GATE_UP && N_TILE >= 64u; }
+
 template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA>
 void launch_n(const ExpertLaunch& p, cudaStream_t stream) {
-    using C = Config<GATE_UP, N_TILE, USE_TMA>;
+    using C = Config<GATE_UP, N_TILE, USE_TMA, row_pair<GATE_UP, N_TILE>()>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (g_sm_count[dev & 15] == 0) cudaDeviceGetAttribute(&g_sm_count[dev & 15], cudaDevAttrMultiProcessorCount, dev);
-    launch_chained(experts_tc_kernel<GATE_UP, N_TILE, USE_TMA>, dim3(g_sm_count[dev & 15]), dim3(C::kThreads), C::kSmemBytes, stream,
+    launch_chained(experts_tc_kernel<GATE_UP, N_TILE, USE_TMA, row_pair<GATE_UP, N_TILE>()>, dim3(g_sm_count[dev & 15]),
+                   dim3(C::kThreads), C::kSmemBytes, stream,
         p, TileList{p.tile_list, p.tile_count});
 }
 
 template <bool GATE_UP>
 void launch(const ExpertLaunch& p, cudaStream_t stream) {
-    constexpr uint32_t kWide = GATE_UP ? 96u : 128u;
+    constexpr uint32_t kWide = 96u;
     const uint32_t n = tc_token_tile_for(p.tokens, p.g.routed_k + p.g.always_count, p.work.num_experts, GATE_UP);
     if (p.tmaps != nullptr) {
         switch (n) {
@@ -664,10 +697,11 @@ void launch(const ExpertLaunch& p, cudaStream_t stream) {
 
 template <bool GATE_UP, uint32_t N_TILE>
 void configure_one() {
-    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)Config<GATE_UP, N_TILE, true>::kSmemBytes);
-    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)Config<GATE_UP, N_TILE, false>::kSmemBytes);
+    constexpr bool kPair = row_pair<GATE_UP, N_TILE>();
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, true, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Config<GATE_UP, N_TILE, true, kPair>::kSmemBytes);
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, false, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Config<GATE_UP, N_TILE, false, kPair>::kSmemBytes);
 }
 
 }  // namespace
@@ -682,9 +716,11 @@ uint32_t tc_token_tile_for(uint32_t tokens, uint32_t routes_per_token, uint32_t 
     // tokens per expert if routing were uniform; skew only adds token tiles
     const uint32_t routes = tokens * routes_per_token;
     const uint32_t per_expert = (routes + num_experts - 1u) / num_experts;
-    // gate/up holds two accumulators per token column: 96 columns is the widest tile that still leaves
-    // tensor memory for a second pair, so that the epilogue of one tile overlaps the MMAs of the next
-    return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : gate_up ? 96u : 128u;
+    // wide tiles hold two accumulators per token column (gate and up, or two row tiles of down): 96 columns
+    // is the widest tile that still leaves tensor memory for a second pair, so that the epilogue of one
+    // tile overlaps the MMAs of the next
+    (void)gate_up;
+    return per_expert <= 12u ? 16u : per_expert <= 24u ? 32u : per_expert <= 48u ? 64u : 96u;
 }
 
 uint32_t tc_token_tile_index(uint32_t n_tile) { return n_tile == 16u ? 0u : n_tile == 32u ? 1u : n_tile == 64u ? 2u : 3u; }
@@ -774,7 +810,7 @@ void tc_configure_kernels() {
     configure_one<false, 16u>();
     configure_one<false, 32u>();
     configure_one<false, 64u>();
-    configure_one<false, 128u>();
+    configure_one<false, 96u>();
 }
 
 void launch_gate_up_tc(const ExpertLaunch& p, cudaStream_t stream) { launch<true>(p, stream); }

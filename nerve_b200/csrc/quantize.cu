@@ -110,37 +110,39 @@ __global__ void __launch_bounds__(256) quantize_grouped_kernel(const void* input
         total, cols, block, q, nullptr, scales_e8m0);
 }
 
-// The common case of the tensor path's gate/up operands (32-column blocks, hidden rows 16-byte aligned):
-// four lanes per block, eight values a lane, one 16-byte load and one 8-byte store each; a warp takes
-// eight blocks side by side. Same values and scales as quantize_body.
-__global__ void __launch_bounds__(256) quantize_grouped_rows32_kernel(const uint16_t* __restrict__ input,
-                                                                     const uint32_t* __restrict__ grouped,
-                                                                     const uint32_t* __restrict__ expert_offsets,
-                                                                     uint32_t num_experts, uint32_t max_routes, uint32_t K,
-                                                                     uint32_t cols, uint8_t* __restrict__ q,
-                                                                     uint32_t* __restrict__ scales_e8m0) {
+// The common cases of the tensor path's gate/up operands (32- or 128-column blocks, hidden rows 16-byte
+// aligned): LANES = block / 8 lanes per block, eight values a lane, one 16-byte load and one 8-byte store
+// each; a warp takes 32 / LANES blocks side by side. Same values and scales as quantize_body.
+template <uint32_t LANES>
+__global__ void __launch_bounds__(256) quantize_grouped_rows_kernel(const uint16_t* __restrict__ input,
+                                                                   const uint32_t* __restrict__ grouped,
+                                                                   const uint32_t* __restrict__ expert_offsets,
+                                                                   uint32_t num_experts, uint32_t max_routes, uint32_t K,
+                                                                   uint32_t cols, uint8_t* __restrict__ q,
+                                                                   uint32_t* __restrict__ scales_e8m0) {
     grid_dependency_sync();
+    constexpr uint32_t kBlock = LANES * 8u, kSide = 32u / LANES;
     const uint32_t total_rows = min(expert_offsets[num_experts], max_routes);
-    const uint32_t blocks_per_row = cols / 32u, words128 = (cols + 127u) / 128u;
+    const uint32_t blocks_per_row = cols / kBlock, words128 = (cols + 127u) / 128u;
     const uint64_t total = (uint64_t)total_rows * blocks_per_row;
-    const uint32_t lane = threadIdx.x & 31u, sub = lane >> 2, part = lane & 3u;
+    const uint32_t lane = threadIdx.x & 31u, sub = lane / LANES, part = lane % LANES;
     const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
-    for (uint64_t first = (((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 8u; first < total; first += warps * 8u) {
+    for (uint64_t first = (((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * kSide; first < total; first += warps * kSide) {
         const uint64_t item = first + sub;
         const bool active = item < total;
         const uint32_t pos = active ? (uint32_t)(item / blocks_per_row) : 0u, b = active ? (uint32_t)(item % blocks_per_row) : 0u;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (active) {
             const uint32_t token = __ldg(grouped + pos) / K;
-            v = __ldg(reinterpret_cast<const uint4*>(input + (size_t)token * cols + (size_t)b * 32u) + part);
+            v = __ldg(reinterpret_cast<const uint4*>(input + (size_t)token * cols + (size_t)b * kBlock) + part);
         }
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         float m = 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; i++)
             m = fmaxf(m, fmaxf(fabsf(nvmoe_bf16_to_f32(w[i])), fabsf(nvmoe_bf16_to_f32(w[i] >> 16))));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+#pragma unroll
+        for (uint32_t o = 1u; o < LANES; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         if (!active) continue;
         const float scale = nvmoe_rounded_fp8_scale(m);
         const float inv = __uint_as_float(0x7f000000u - __float_as_uint(scale));  // 1 / scale, exact (a power of two)
@@ -149,8 +151,11 @@ __global__ void __launch_bounds__(256) quantize_grouped_rows32_kernel(const uint
                           nvmoe_bf16_to_f32(w[1] >> 16) * inv);
         out.y = to_e4m3x4(nvmoe_bf16_to_f32(w[2]) * inv, nvmoe_bf16_to_f32(w[2] >> 16) * inv, nvmoe_bf16_to_f32(w[3]) * inv,
                           nvmoe_bf16_to_f32(w[3] >> 16) * inv);
-        reinterpret_cast<uint2*>(q + (size_t)pos * cols + (size_t)b * 32u)[part] = out;
-        if (part == 0u) reinterpret_cast<uint8_t*>(scales_e8m0 + (size_t)pos * words128)[b] = (uint8_t)(nvmoe_f32_bits(scale) >> 23);
+        reinterpret_cast<uint2*>(q + (size_t)pos * cols + (size_t)b * kBlock)[part] = out;
+        // one scale byte per 32 columns: a block of 128 fills four
+        if (part < kBlock / 32u)
+            reinterpret_cast<uint8_t*>(scales_e8m0 + (size_t)pos * words128)[b * (kBlock / 32u) + part] =
+                (uint8_t)(nvmoe_f32_bits(scale) >> 23);
     }
 }
 
@@ -199,13 +204,14 @@ void launch_quantize_grouped(const void* input, bool frames, const uint32_t* gro
                              uint32_t cols, uint32_t intermediate_size, uint32_t block, uint8_t* q,
                              uint32_t* scales_e8m0, cudaStream_t stream) {
     if (max_routes == 0u) return;
-    if (!frames && block == 32u && cols % 8u == 0u && (reinterpret_cast<uintptr_t>(input) & 15u) == 0u) {
-        const uint64_t warps = ((uint64_t)max_routes * (cols / 32u) + 7u) / 8u;
+    if (!frames && (block == 32u || block == 128u) && cols % 8u == 0u && (reinterpret_cast<uintptr_t>(input) & 15u) == 0u) {
+        const uint32_t side = block == 32u ? 8u : 2u;  // blocks a warp takes at once
+        const uint64_t warps = ((uint64_t)max_routes * (cols / block) + side - 1u) / side;
         uint64_t blocks = (warps + 7u) / 8u;
         if (blocks > 148u * 64u) blocks = 148u * 64u;
-        launch_chained(quantize_grouped_rows32_kernel, dim3((uint32_t)blocks), dim3(256), 0, stream,
-                       static_cast<const uint16_t*>(input), grouped_routes, expert_offsets, num_experts, max_routes, K, cols, q,
-                       scales_e8m0);
+        const auto kernel = block == 32u ? quantize_grouped_rows_kernel<4u> : quantize_grouped_rows_kernel<16u>;
+        launch_chained(kernel, dim3((uint32_t)blocks), dim3(256), 0, stream, static_cast<const uint16_t*>(input), grouped_routes,
+                       expert_offsets, num_experts, max_routes, K, cols, q, scales_e8m0);
         return;
     }
     launch_chained(quantize_grouped_kernel, dim3(grid_for((uint64_t)max_routes * (cols / block))), dim3(256), 0, stream, input,

@@ -228,6 +228,8 @@ LAYER_CASES = [
     pytest.param("gpt-oss-20b", (256, 384, 16), 33, id="gptoss-small-T33"),
     pytest.param("gpt-oss-20b", (2880, 2880, 32), 8, id="gptoss-20b-T8"),            # configs[1] shape
     pytest.param("gpt-oss-20b-prefill", (352, 160, 32), 600, id="gptoss-zipf-small-T600"),
+    # wide token tiles on the TMA path: ragged row tiles (320 = 2.5 x 128), a K tail in down, row pairs with a lone half
+    pytest.param("gpt-oss-20b-prefill", (384, 320, 8), 300, id="gptoss-zipf-tma-T300"),
     pytest.param("deepseek-v3", (512, 256, 32), 50, id="deepseek-small-T50"),
     pytest.param("deepseek-v3", (7168, 2048, 16), 4, id="deepseek-wide-T4"),
 ]
