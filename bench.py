@@ -196,11 +196,21 @@ def cpu_baseline(cfg, tokens, seed, sample_tokens, budget_s=12.0):
     """Times the CPU restatement of the reference shaders on a bounded sample of the workload: `sample_tokens`
     tokens first (a probe of the host's speed), then as many tokens of the workload as about `budget_s`
     seconds take, passed over repeatedly if the whole workload takes less."""
+    from oracle import moe_oracle as mo
+
     probe = _cpu_layer_pass(cfg, tokens, seed, min(tokens, sample_tokens), passes=1)
     rate = probe["value"]
     sample = int(max(1, min(tokens, rate * budget_s)))
     passes = int(max(1, min(50, budget_s * rate / sample)))
-    return _cpu_layer_pass(cfg, tokens, seed, sample, passes)
+    result = _cpu_layer_pass(cfg, tokens, seed, sample, passes)
+    # one host core, on a sample a few per cent of that size
+    threads = mo.lib().oracle_set_threads(1)
+    try:
+        few = int(max(1, min(tokens, rate * budget_s / (8.0 * max(1, threads)))))
+        result["single_core_value"] = _cpu_layer_pass(cfg, tokens, seed, few, passes=1)["value"]
+    finally:
+        mo.lib().oracle_set_threads(threads)
+    return result
 
 
 def _cpu_layer_pass(cfg, tokens, seed, sample, passes):
@@ -383,7 +393,9 @@ def main() -> None:
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": None, "kernel": "gate_up", "mma_kind": "mxf8f6f4 (E4M3 activations x E2M1 weights)",
                     "peak_kind": f"2 x {peak_kind} cuBLAS bf16 burst rate; against the mxf4 rate (4 x bf16) the fraction halves",
-                    "kernel_ms": gate_ms,
+                    "kernel_ms": gate_ms, "frac_of_mxf4_rate": achieved / (peaks["bf16_tflops"] * 4.0),
+                    "down_kernel": {"achieved": flops_gate / 2.0 / (down_ms * 1e-3) / 1e12, "kernel_ms": down_ms,
+                                    "frac": flops_gate / 2.0 / (down_ms * 1e-3) / 1e12 / peak},
                     "layer": {"achieved": layer_flops(cfg, tokens) / (ms * 1e-3) / 1e12,
                               "frac": layer_flops(cfg, tokens) / (ms * 1e-3) / 1e12 / peak}}
 

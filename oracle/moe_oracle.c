@@ -45,6 +45,18 @@ int oracle_max_threads(void) {
 #endif
 }
 
+/* threads the next calls use (a benchmark's single-core figure); returns the previous setting */
+int oracle_set_threads(int threads) {
+#ifdef _OPENMP
+    int before = omp_get_max_threads();
+    if (threads > 0) omp_set_num_threads(threads);
+    return before;
+#else
+    (void)threads;
+    return 1;
+#endif
+}
+
 static inline float unpack_bf16(const uint32_t* words, uint32_t index) {
     uint32_t packed = words[index >> 1];
     return nvmoe_bf16_to_f32((index & 1u) == 0u ? packed : packed >> 16);

@@ -123,6 +123,7 @@ float oracle_tanhf(float v);
 void oracle_dequant_mxfp4(const uint8_t* packed, const uint8_t* scales, uint32_t rows,
                           uint32_t columns, float* out);
 int oracle_max_threads(void);
+int oracle_set_threads(int threads);
 
 #ifdef __cplusplus
 }

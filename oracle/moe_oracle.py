@@ -88,6 +88,7 @@ def lib() -> ctypes.CDLL:
             ("oracle_logf", f32, [f32]),
             ("oracle_tanhf", f32, [f32]),
             ("oracle_max_threads", ctypes.c_int, []),
+            ("oracle_set_threads", ctypes.c_int, [ctypes.c_int]),
         ]:
             fn = getattr(_lib, name)
             fn.restype = res
