@@ -178,10 +178,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
         bars->abort = 0u;
         fence_mbar_init();
     }
-    // the padding halves of the 4-bit slots are never written by the copies: clear them once
-    for (uint32_t i = threadIdx.x; i < C::kStages * C::kStageBytes / 16u; i += kThreads)
-        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
-    fence_proxy_async();
+    // (The padding halves of the 4-bit slots, the scale rows past the token tile and whatever else the
+    // copies never write stay as they were found: the MMA does not read them. Checked by filling the
+    // stages with 0xff first; rows and columns that are read but hold no data are written as zeros by the
+    // copies themselves.)
     __syncthreads();
     if (warp == 4u) {
         tmem_alloc(&bars->tmem_base, C::kTmemColumns);
@@ -501,8 +501,21 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             const uint32_t row = m_tile * C::kTileRows + quad * 32u + lane;  // (with row pairs: of the first half)
             const bool row_ok = row < out_rows;
             const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16) + acc * C::kAccColumns;
-            for (uint32_t c0 = 16u * epilogue_group; c0 < N_TILE; c0 += 16u * C::kEpilogueGroups) {
+            // The epilogue groups share out a wide tile by 16-column chunks. A narrow tile (one or two chunks)
+            // is shared out by sets of four tokens instead, every group reading the chunk: a tile of eight
+            // tokens is then two groups' work side by side, not one group's in turn.
+            constexpr bool kShareByFours = N_TILE <= 32u && C::kEpilogueGroups > 1u;
+            for (uint32_t c0 = kShareByFours ? 0u : 16u * epilogue_group; c0 < N_TILE;
+                 c0 += kShareByFours ? 16u : 16u * C::kEpilogueGroups) {
                 if (c0 >= valid) break;  // uniform: no token of this tile lives in the remaining columns
+                if (kShareByFours) {
+                    // does any of this chunk's sets of four fall to this group? (uniform)
+                    bool mine = false;
+#pragma unroll
+                    for (uint32_t g0 = 0; g0 < 16u; g0 += 4u)
+                        mine = mine || (c0 + g0 < valid && ((c0 + g0) / 4u) % C::kEpilogueGroups == epilogue_group);
+                    if (!mine) continue;
+                }
                 uint32_t d0[16], d1[16];
                 tmem_ld16(lane_addr + c0, d0);
                 if (C::kMatrices == 2u) tmem_ld16(lane_addr + N_TILE + c0, d1);  // up, or the second 128 rows
@@ -531,6 +544,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
 #pragma unroll
                 for (uint32_t g0 = 0; g0 < 16u; g0 += 4u) {
                     if (c0 + g0 >= valid) break;  // uniform
+                    if (kShareByFours && ((c0 + g0) / 4u) % C::kEpilogueGroups != epilogue_group) continue;  // another group's
                     uint32_t bits[4];
 #pragma unroll
                     for (uint32_t t = 0; t < 4u; t++) {

@@ -27,6 +27,16 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(capi.Geometry) == 22 * 4
     assert ctypes.sizeof(capi.LayerArgs) == 3 * 4 + 4 + 14 * 8
     assert ctypes.sizeof(capi.WorkReport) == 4 + 8 * 4 + 3 * 4 + 4 * 4 + 8
+    assert ctypes.sizeof(capi.EpLayerArgs) == 4 + 4 + 11 * 8
+
+
+def test_expert_parallel_entry_points_reject_bad_arguments_without_a_gpu():
+    lib = capi.load()
+    assert lib.nvmoe_ep_unique_id(None) != 0
+    handle = ctypes.c_void_p()
+    assert lib.nvmoe_ep_create(None, b"\0" * 128, 0, 1, ctypes.byref(handle)) != 0
+    assert lib.nvmoe_ep_layer(None, None, None, None) != 0
+    lib.nvmoe_ep_destroy(None)  # a null handle is ignored
 
 
 def test_geometry_default_matches_reference_constants():
