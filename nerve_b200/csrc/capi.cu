@@ -1098,7 +1098,7 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     ExpertSet* sets[2] = {nullptr, nullptr};
     NVMOE_TRY(prepare_expert_set(p, true, a->gate_up_addresses, a->gate_up_slots, tensor, &sets[0]));
     NVMOE_TRY(prepare_expert_set(p, false, a->down_addresses, a->down_slots, tensor, &sets[1]));
-    if (layer_schedule_is_small(T, p->K)) {
+    if (layer_schedule_is_small(T, p->K, p->experts)) {
         LayerSchedule ls{};
         ls.routes = (const uint32_t*)routes->ptr;
         ls.intermediates = (uint32_t*)frames.ptr;

@@ -136,7 +136,7 @@ struct LayerSchedule {
     uint32_t* status;
     uint32_t tokens, expert_start, expert_count, K, I, tiles_per_route[2], num_experts, n_tile[2];
 };
-bool layer_schedule_is_small(uint32_t tokens, uint32_t K);
+bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts);
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream);
 // validates the address/slot tables of every expert once per call
 void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(64) router_linear_kernel(const uint16_t* __res
 
     // The sum order of a lane is fixed (its words in ascending order), the load order is not: the
     // loads of kDepth steps are issued together so that their latencies overlap.
-    constexpr int kDepth = TT * ET <= 16 ? 4 : 2;
+    constexpr int kDepth = TT * ET <= 16 ? 8 : 2;
     for (uint32_t cw0 = v; cw0 < words; cw0 += 64u * kDepth) {
         uint32_t xr[kDepth][TT], wr[kDepth][ET];
 #pragma unroll

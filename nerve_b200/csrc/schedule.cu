@@ -119,8 +119,10 @@ struct OwnedKey {  // partitioned compact: keep owned routes, in source order (o
 struct ScheduleEmit {  // writes the compact list into the schedule words of the frames
     uint32_t* intermediates;
     uint32_t K, frame_words, data_words;
+    uint32_t* copy = nullptr;  // optional second, flat copy of the list
     __device__ void operator()(uint32_t rank, uint32_t i) const {
         intermediates[(size_t)(rank / K) * frame_words + data_words + rank % K] = i;
+        if (copy) copy[rank] = i;
     }
 };
 
@@ -131,6 +133,7 @@ struct SlotKey {
     const ExpertPtrs* experts;
     uint32_t* status;
     uint32_t num_experts, K, frame_words, data_words, capacity;
+    const uint8_t* resident = nullptr;  // optional per-expert copy of "experts[e].w[0] != nullptr" (a faster place)
     __device__ uint32_t route_index(uint32_t c) const {
         return intermediates[(size_t)(c / K) * frame_words + data_words + c % K];
     }
@@ -145,7 +148,7 @@ struct SlotKey {
             raise_status(status, NVMOE_STATUS_ROUTE_OUT_OF_RANGE);
             return kUnboundSlot;
         }
-        if (experts[e].w[0] == nullptr) {
+        if (resident ? resident[e] == 0u : experts[e].w[0] == nullptr) {
             raise_status(status, NVMOE_STATUS_EXPERT_NOT_RESIDENT);
             return kUnboundSlot;
         }
@@ -173,11 +176,11 @@ __device__ __forceinline__ uint32_t min_u32(uint32_t a, uint32_t b) { return a <
 __device__ void compact_small_body(const uint32_t* routes, uint32_t* intermediates, const uint32_t* slots,
                                    uint32_t slot_words, uint32_t params, uint32_t* control, uint32_t max_tokens,
                                    uint32_t K, uint32_t I, uint32_t tiles_per_route, uint32_t num_experts,
-                                   uint32_t* hist) {
+                                   uint32_t* hist, uint32_t* list_copy = nullptr) {
     const uint32_t T = min_u32(control[0], max_tokens);
     const uint32_t count = T * K;
     const uint32_t data_words = K * (I / 2u);
-    ScheduleEmit emit{intermediates, K, data_words + K, data_words};
+    ScheduleEmit emit{intermediates, K, data_words + K, data_words, list_copy};
     if (control[2] != 0u) {
         OwnedKey key{routes, slots, slot_words, params, control[1], control[1] + control[2]};
         sort_single_block(count, 1u, hist, key, emit, [&](const uint32_t* base) {
@@ -491,22 +494,40 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const uint32_t* exper
 // The whole schedule of one layer call in one block (T*K small): the control words the host of the
 // reference writes, the compact list in front of gate/up, the owned count in front of down, and for
 // each of the two expert stages the expert-grouped route list and the tensor-path tile list.
+// Shared memory of the fused schedule: sort histogram, then copies of what the five passes would otherwise
+// fetch from global memory through chains of dependent loads: the route words, the compact list, and
+// per stage whether each expert is resident.
+__host__ __device__ inline size_t layer_schedule_smem_bytes(uint32_t count, uint32_t num_experts) {
+    return ((size_t)num_experts + 2u + 2u * count) * sizeof(uint32_t) + 2u * (size_t)num_experts;
+}
+
 __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedule s) {
     extern __shared__ uint32_t hist[];
+    const uint32_t count = s.tokens * s.K;
+    uint32_t* route_words = hist + s.num_experts + 2u;
+    uint32_t* compact_list = route_words + count;
+    uint8_t* resident = reinterpret_cast<uint8_t*>(compact_list + count);
     grid_dependency_sync();
     if (threadIdx.x < 14u) {
         const uint32_t j = threadIdx.x % 7u;
         s.control[threadIdx.x / 7u][j] = j == 0u ? s.tokens : j == 1u ? s.expert_start : j == 2u ? s.expert_count : 0u;
     }
+    for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
+        route_words[i] = s.routes[i];
+        compact_list[i] = kUnboundSlot;  // positions past the owned count stay out of range
+    }
+    for (uint32_t e = threadIdx.x; e < 2u * s.num_experts; e += blockDim.x)
+        resident[e] = s.experts[e / s.num_experts][e % s.num_experts].w[0] != nullptr ? 1u : 0u;
     __syncthreads();
-    compact_small_body(s.routes, s.intermediates, s.slots[0], s.slot_words[0], 4u, s.control[0], s.tokens, s.K, s.I,
-                       s.tiles_per_route[0], s.num_experts, hist);
+    compact_small_body(route_words, s.intermediates, s.slots[0], s.slot_words[0], 4u, s.control[0], s.tokens, s.K, s.I,
+                       s.tiles_per_route[0], s.num_experts, hist, compact_list);
     __syncthreads();
-    route_count_body(s.routes, s.slots[1], s.slot_words[1], 2u, s.control[1], s.tokens, s.K, s.tiles_per_route[1]);
+    route_count_body(route_words, s.slots[1], s.slot_words[1], 2u, s.control[1], s.tokens, s.K, s.tiles_per_route[1]);
     __syncthreads();
-    const uint32_t data_words = s.K * (s.I / 2u);
     for (uint32_t stage = 0; stage < 2u; stage++) {
-        SlotKey key{s.routes, s.intermediates, s.experts[stage], s.status, s.num_experts, s.K, data_words + s.K, data_words, 0u};
+        // the flat copy of the compact list stands in for the schedule words of the frames: frame = K words, no data
+        SlotKey key{route_words, compact_list, s.experts[stage], s.status, s.num_experts, s.K, s.K, 0u, 0u,
+                    resident + stage * s.num_experts};
         group_small_body(key, s.control[stage], s.tokens, s.grouped[stage], s.offsets[stage], s.position[stage], hist);
         __syncthreads();
         if (s.tiles[stage]) build_tiles_body(s.offsets[stage], s.num_experts, s.n_tile[stage], s.tiles[stage], s.tile_count[stage]);
@@ -720,12 +741,14 @@ void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const
         intermediate_size, tiles_per_route, num_experts, scratch.block_hist, scratch.bucket_base);
 }
 
-bool layer_schedule_is_small(uint32_t tokens, uint32_t K) { return (uint64_t)tokens * K <= kSmallSortLimit; }
+bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts) {
+    return (uint64_t)tokens * K <= kSmallSortLimit && layer_schedule_smem_bytes(tokens * K, num_experts) <= 48u * 1024u;
+}
 
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
     const uint32_t count = s.tokens * s.K;
     launch_chained(layer_schedule_small_kernel, dim3(1), dim3(count <= 256u ? 256u : 1024u),
-                   (s.num_experts + 2u) * sizeof(uint32_t), stream, s);
+                   layer_schedule_smem_bytes(count, s.num_experts), stream, s);
 }
 
 void launch_build_tiles(const uint32_t* expert_offsets, uint32_t num_experts, uint32_t n_tile, uint32_t* tiles,

@@ -13,8 +13,17 @@ resource owned exactly once") drives an all-to-all exchange over NCCL/NVLink ins
 Every per-route row is computed by the same kernels, on the same operands, as on one GPU, and the
 combine sums them in the same order, so the result is bit-identical to the single-GPU layer.
 
-The exchange protocol (:func:`exchange`) is backend-neutral: the GPU path plugs in the CUDA
-operators, the CPU tests plug in stand-ins and run it over gloo.
+Three forms of the same protocol:
+
+* ``native``: the library owns the NCCL communicator and issues the two exchanges itself as grouped
+  send/receive on its compute stream, fixed-size segments per peer, one C call per step
+  (``nvmoe_ep_create`` / ``nvmoe_ep_layer``); torch.distributed is only used once, to hand the
+  communicator id round.
+* ``padded`` (:func:`exchange_padded`): the same fixed segments over ``all_to_all_single`` with equal splits.
+* ``ragged`` (:func:`exchange`): rows packed back to back, split sizes read on the host.
+
+The two torch forms are backend-neutral: the GPU path plugs in the CUDA operators, the CPU tests plug
+in stand-ins and run them over gloo.
 """
 from __future__ import annotations
 

@@ -336,14 +336,15 @@ def test_expert_ranges_partition_the_layer(device, path):
     plan.destroy()
 
 
+@pytest.mark.parametrize("tokens", [24, 700])  # 700: more than 4096 slots, the multi-block schedule
 @pytest.mark.parametrize("path", PATHS)
-def test_preselected_routes_form_reproduces_the_layer(device, path):
+def test_preselected_routes_form_reproduces_the_layer(device, path, tokens):
     """The owner's side of an expert-parallel exchange: the routes of a finished router arrive as rows
     of a top-1 plan (one hidden row and one route word per slot, unused slots marked 0xffffffff), the
     per-route rows come back instead of the combined output, and combining them reproduces the
     ordinary layer call bit for bit."""
     cfg = synthetic.small_variant(synthetic.CONFIGS["gpt-oss-120b"], 256, 384, 16)
-    tokens, K, H = 24, cfg.total_k, cfg.hidden
+    K, H = cfg.total_k, cfg.hidden
     case = synthetic.make_case(cfg, tokens, seed=8)
     plan = make_plan(device, cfg, tokens, path)
     bank = ExpertBank.upload(device, case.w1, case.s1, case.w3, case.s3, case.w2, case.s2)
