@@ -1226,6 +1226,17 @@ int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hi
     NVMOE_TRY(nvmoe_layer(p, &local));
     NVMOE_CUDA(d, cudaMemcpyAsync(direct_out ? output_host : p->pinned_out, p->output_dev.ptr, bytes, cudaMemcpyDeviceToHost,
                                   d->stream));
+    // the caller waits for this result: poll for it (a decode step is over in well under a millisecond; a
+    // blocking wait would add the wake-up of a sleeping thread to every step), then fall back to a blocking wait
+    NVMOE_CUDA(d, cudaEventRecord(d->sync_event, d->stream));
+    {
+        const auto give_up = std::chrono::steady_clock::now() + std::chrono::milliseconds(20);
+        cudaError_t q;
+        while ((q = cudaEventQuery(d->sync_event)) == cudaErrorNotReady && std::chrono::steady_clock::now() < give_up) {
+        }
+        if (q != cudaSuccess && q != cudaErrorNotReady)
+            return fail(d, NVMOE_ERR_CUDA, "device failed while waiting: %s", cudaGetErrorString(q));
+    }
     NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
     if (!direct_out) std::memcpy(output_host, p->pinned_out, bytes);
     return NVMOE_OK;
