@@ -70,3 +70,22 @@ def test_synthetic_cases_are_seeded_and_shaped():
     assert synthetic.CONFIGS["gpt-oss-20b"].expert_weight_bytes == 13_219_200
     assert synthetic.CONFIGS["deepseek-v3"].expert_weight_bytes == 23_396_352
     assert synthetic.CONFIGS["tiny"].expert_weight_bytes == 208_896
+
+
+def test_public_headers_compile_as_plain_c(tmp_path):
+    """The boundary is a C ABI: both headers must be valid C99 on their own."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc") or "/usr/bin/gcc"
+    source = tmp_path / "abi.c"
+    source.write_text(
+        '#include "nerve_cuda_moe.h"\n#include "nvmoe_math.h"\n'
+        "int main(void) { nvmoe_geometry g; nvmoe_layer_args a; nvmoe_ep_layer_args e; nvmoe_work_report r;\n"
+        "  (void)g; (void)a; (void)e; (void)r; return nvmoe_expf(0.0f) == 1.0f ? 0 : 1; }\n")
+    include = Path(__file__).resolve().parent.parent / "include"
+    binary = tmp_path / "abi"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-ffp-contract=off", f"-I{include}",
+                    str(source), "-o", str(binary), "-lm"], check=True)
+    subprocess.run([str(binary)], check=True)
+
