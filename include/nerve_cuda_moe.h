@@ -354,8 +354,10 @@ int nvmoe_ep_unpack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* 
 
 /*
  * The expert-parallel layer with the collectives inside the call: one process per GPU, each opening
- * its device, creating its plans and joining the same communicator. NCCL is bound at run time (the
- * libnccl.so.2 already in the process, else the system's).
+ * its device, creating its plans and joining the same communicator. NCCL is bound at run time: the
+ * libnccl.so.2 already in the process, else the file NVMOE_NCCL_LIBRARY names, else the system's. A
+ * process shares one libnccl.so.2: a framework that ships its own must be loaded before the first call
+ * here (or its copy named in NVMOE_NCCL_LIBRARY).
  *
  *   rank 0:      nvmoe_ep_unique_id(id)        then hands the 128 bytes to every rank (any transport)
  *   every rank:  nvmoe_ep_create(device, id, rank, world, &ep)     collective: all ranks must call it

@@ -177,12 +177,22 @@ class ExpertBank:
                           address_table(device, dres), device.resident_buffer_from(dslots))
 
 
+def _load_framework_nccl() -> None:
+    """The library binds whichever libnccl.so.2 the process already holds, else the system's. PyTorch ships
+    its own and cannot start on an older one loaded before it: if PyTorch is installed, let it load first."""
+    try:
+        import torch  # noqa: F401
+    except ImportError:
+        pass
+
+
 class ExpertParallelGroup:
     """This rank's membership of an expert-parallel communicator held by the library (NCCL)."""
 
     @staticmethod
     def unique_id() -> bytes:
         """Rank 0 makes the id; every rank needs the same 128 bytes to join."""
+        _load_framework_nccl()
         buf = ctypes.create_string_buffer(128)
         rc = capi.load().nvmoe_ep_unique_id(buf)
         if rc != 0:
@@ -191,6 +201,7 @@ class ExpertParallelGroup:
 
     def __init__(self, device: CudaComputeDevice, unique_id: bytes, rank: int, world_size: int):
         assert len(unique_id) == 128
+        _load_framework_nccl()
         self.device, self.rank, self.world_size = device, rank, world_size
         handle = ctypes.c_void_p()
         device._check(device._lib.nvmoe_ep_create(device._h, unique_id, rank, world_size, ctypes.byref(handle)))

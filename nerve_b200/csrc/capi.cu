@@ -5,6 +5,7 @@
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <memory>
@@ -1327,7 +1328,12 @@ struct NcclApi {
 const NcclApi& nccl_api() {
     static const NcclApi api = [] {
         NcclApi a;
+        // the copy already in the process (a framework's), else the one NVMOE_NCCL_LIBRARY names, else the system's.
+        // A process that will load a framework with its own NCCL later must do that first (or name that
+        // copy here): the loader shares one libnccl.so.2 per process, whichever comes first.
         a.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+        if (const char* path = getenv("NVMOE_NCCL_LIBRARY"))
+            if (!a.lib && path[0]) a.lib = dlopen(path, RTLD_NOW | RTLD_LOCAL);
         if (!a.lib) a.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
         if (!a.lib) {
             a.problem = std::string("libnccl.so.2 could not be loaded: ") + dlerror();
