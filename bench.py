@@ -375,7 +375,7 @@ def main() -> None:
     ab = algorithmic_bytes(cfg, tokens, distinct)
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised under
     # profiles/ (taken on this workload); other workloads have no capture and report null
-    ncu_traffic = {("gpt-oss-20b-decode", 64): {"gate_up": 289483264, "down": 146558208}}.get((args.workload, tokens))
+    ncu_traffic = {("gpt-oss-20b-decode", 64): {"gate_up": 289069568, "down": 146978816}}.get((args.workload, tokens))
     if bound == "hbm":
         achieved = ab["gate_up"] / (gate_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
