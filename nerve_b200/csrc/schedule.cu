@@ -233,14 +233,23 @@ __device__ void phase_hist(uint32_t count, uint32_t buckets, uint32_t* block_his
 __global__ void __launch_bounds__(1024) phase_scan_kernel(uint32_t* block_hist, uint32_t* bucket_base,
                                                          uint32_t blocks, uint32_t buckets) {
     extern __shared__ uint32_t totals[];
-    for (uint32_t b = threadIdx.x; b < buckets; b += blockDim.x) {
+    // a warp per bucket: thirty-two blocks' counts are scanned at a time with shuffles
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (uint32_t b = warp; b < buckets; b += warps) {
         uint32_t run = 0u;
-        for (uint32_t blk = 0; blk < blocks; blk++) {
-            uint32_t v = block_hist[(size_t)blk * buckets + b];
-            block_hist[(size_t)blk * buckets + b] = run;
-            run += v;
+        for (uint32_t blk0 = 0; blk0 < blocks; blk0 += 32u) {
+            const uint32_t blk = blk0 + lane;
+            const uint32_t v = blk < blocks ? block_hist[(size_t)blk * buckets + b] : 0u;
+            uint32_t incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)lane >= o) incl += n;
+            }
+            if (blk < blocks) block_hist[(size_t)blk * buckets + b] = run + incl - v;
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        totals[b] = run;
+        if (lane == 0u) totals[b] = run;
     }
     __syncthreads();
     if (threadIdx.x < 32u) {
