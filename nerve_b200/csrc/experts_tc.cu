@@ -138,7 +138,7 @@ template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA, bool ROW_PAIR>
 __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::kThreads), 1)
     experts_tc_kernel(ExpertLaunch p, TileList list) {
     using C = Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>;
-    constexpr uint32_t kThreads = C::kThreads, kProducerThreads = C::kProducerThreads, kRowsPerPass = C::kRowsPerPass;
+    constexpr uint32_t kProducerThreads = C::kProducerThreads, kRowsPerPass = C::kRowsPerPass;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023u));
@@ -341,14 +341,16 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 }
                 // activations: 16-byte pieces of 16 E4M3 codes (with TMA the whole tile is one box)
                 const uint32_t b_dst = smem_u32(stage + C::kMatrices * kATileBytes) + my_dst;
+                if (!USE_TMA) {
 #pragma unroll
-                for (uint32_t i = 0; i < (USE_TMA ? 0u : kTokenPasses); i++) {
+                for (uint32_t i = 0; i < kTokenPasses; i++) {
                     const uint32_t n = my_r + kRowsPerPass * i;
                     if (n < N_TILE) {
                         const bool ok = chunk_ok && (n < cur.valid);
                         const uint8_t* src = ok ? p.act_q + (size_t)cur.code_rows[i] * k_dim + kb * kBlockK + my_c * 16u : p.act_q;
                         cp_async_16(b_dst + i * (kRowsPerPass * 128u), src, ok ? 16u : 0u);
                     }
+                }
                 }
                 // scales: the derived copy already has the 32x16-byte layout tcgen05.cp reads, one 512-byte
                 // block per (row tile, K block); token scales are gathered four bytes (one K block) a row
