@@ -544,6 +544,134 @@ __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedul
     }
 }
 
+// The same schedule for the unpartitioned call (expert_count == 0), where the compact list and both
+// groupings are one stable sort of the routes by expert id seen through different filters: the rank r of a
+// route among the routes of its expert is found once, and every list position is a per-list bucket base
+// plus r.  Rank: a warp ranks its 32 routes with match_any and leaves its per-bucket counts in a table
+// [warp][bucket]; a column-wise running sum turns the counts into the ranks where each warp's routes start.
+// One pass over global memory, four block barriers.
+constexpr uint32_t kRankChunks = 4u;  // routes per thread at most (count <= 4 * blockDim)
+
+__host__ __device__ inline uint32_t layer_schedule_rank_threads(uint32_t count) { return count <= 256u ? 256u : 1024u; }
+
+__host__ __device__ inline size_t layer_schedule_rank_smem_bytes(uint32_t count, uint32_t num_experts) {
+    const size_t buckets = (size_t)num_experts + 1u;
+    const size_t warps = ((size_t)count + 31u) / 32u;
+    // table (u16, rounded to words), hist, base_all, gbase[2], tile_base[2] (buckets + 1 each), kept[2] (bytes)
+    return ((warps * buckets + 1u) / 2u + 6u * (buckets + 1u)) * sizeof(uint32_t) + 2u * buckets;
+}
+
+__global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule s) {
+    extern __shared__ uint32_t smem_words[];
+    const uint32_t count = s.tokens * s.K;
+    const uint32_t E = s.num_experts, B = E + 1u;  // bucket E collects out-of-range expert ids
+    const uint32_t V = (count + 31u) / 32u;
+    const uint32_t table_words = (V * B + 1u) / 2u;
+    uint16_t* table = reinterpret_cast<uint16_t*>(smem_words);
+    uint32_t* hist = smem_words + table_words;
+    uint32_t* base_all = hist + (B + 1u);
+    uint32_t* gbase[2] = {base_all + (B + 1u), base_all + 2u * (B + 1u)};
+    uint32_t* tile_base[2] = {base_all + 3u * (B + 1u), base_all + 4u * (B + 1u)};
+    uint8_t* kept = reinterpret_cast<uint8_t*>(base_all + 5u * (B + 1u));  // [2][B]: the stage keeps routes of this bucket
+    const uint32_t lane = threadIdx.x & 31u;
+
+    for (uint32_t w = threadIdx.x; w < table_words; w += blockDim.x) smem_words[w] = 0u;
+    grid_dependency_sync();
+    if (threadIdx.x < 14u) {
+        const uint32_t stage = threadIdx.x / 7u, j = threadIdx.x % 7u;
+        const uint32_t value = j == 0u ? s.tokens : j == 1u ? s.expert_start : j == 2u ? 0u : j == 3u ? count
+                             : j == 4u ? s.K * s.tiles_per_route[stage] : j == 5u ? s.tokens : 1u;
+        s.control[stage][j] = value;
+    }
+    // residency of every expert for both stages (bucket E is never kept)
+    for (uint32_t i = threadIdx.x; i < 2u * B; i += blockDim.x) {
+        const uint32_t stage = i / B, b = i % B;
+        kept[i] = (b < E && s.experts[stage][b].w[0] != nullptr) ? 1u : 0u;
+    }
+    uint32_t bucket[kRankChunks], before[kRankChunks];
+    __syncthreads();
+#pragma unroll
+    for (uint32_t c = 0; c < kRankChunks; c++) {
+        const uint32_t i = c * blockDim.x + threadIdx.x;
+        bucket[c] = kUnboundSlot;
+        before[c] = 0u;
+        if (c * blockDim.x < count) {  // uniform over the block: whole warps take part in the match
+            if (i < count) bucket[c] = min_u32(s.routes[i] & 0xffffu, E);
+            const uint32_t peers = __match_any_sync(0xffffffffu, bucket[c]);
+            before[c] = __popc(peers & ((1u << lane) - 1u));
+            if (i < count && lane == (uint32_t)__ffs(peers) - 1u) table[(size_t)(i >> 5) * B + bucket[c]] = (uint16_t)__popc(peers);
+        }
+    }
+    __syncthreads();
+    for (uint32_t b = threadIdx.x; b < B; b += blockDim.x) {
+        uint32_t running = 0u;
+        for (uint32_t v = 0; v < V; v++) {
+            const uint32_t here = table[(size_t)v * B + b];
+            table[(size_t)v * B + b] = (uint16_t)running;
+            running += here;
+        }
+        hist[b] = running;
+    }
+    __syncthreads();
+    // five exclusive scans over the buckets, a warp each: the compact list, and per stage the grouped list
+    // and the tile list
+    const uint32_t warp = threadIdx.x >> 5;
+    if (warp < 5u) {
+        const uint32_t stage = warp == 0u ? 0u : (warp - 1u) & 1u;
+        const bool tiles = warp >= 3u;
+        uint32_t* out = warp == 0u ? base_all : tiles ? tile_base[stage] : gbase[stage];
+        uint32_t carry = 0u;
+        for (uint32_t b0 = 0; b0 < B; b0 += 32u) {
+            const uint32_t b = b0 + lane;
+            uint32_t v = b < B ? hist[b] : 0u;
+            if (warp != 0u && b < B) {
+                v = kept[stage * B + b] ? v : 0u;
+                if (tiles) v = (v + s.n_tile[stage] - 1u) / s.n_tile[stage];
+            }
+            uint32_t incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)lane >= o) incl += n;
+            }
+            if (b < B) out[b] = carry + incl - v;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0u) out[B] = carry;
+    }
+    __syncthreads();
+    const uint32_t data_words = s.K * (s.I / 2u), frame_words = data_words + s.K;
+#pragma unroll
+    for (uint32_t c = 0; c < kRankChunks; c++) {
+        const uint32_t i = c * blockDim.x + threadIdx.x;
+        if (i >= count) continue;
+        const uint32_t b = bucket[c];
+        const uint32_t rank = table[(size_t)(i >> 5) * B + b] + before[c];
+        const uint32_t at = base_all[b] + rank;
+        s.intermediates[(size_t)(at / s.K) * frame_words + data_words + at % s.K] = i;
+        for (uint32_t stage = 0; stage < 2u; stage++) {
+            uint32_t place = kUnboundSlot;
+            if (kept[stage * B + b]) {
+                place = gbase[stage][b] + rank;
+                s.grouped[stage][place] = i;
+            } else {
+                raise_status(s.status, b == E ? NVMOE_STATUS_ROUTE_OUT_OF_RANGE : NVMOE_STATUS_EXPERT_NOT_RESIDENT);
+            }
+            if (s.position[stage]) s.position[stage][i] = place;
+        }
+    }
+    for (uint32_t i = threadIdx.x; i < 2u * B; i += blockDim.x) {
+        const uint32_t stage = i / B, b = i % B;
+        // bucket E is never kept, so gbase[stage][E] is already the total the offsets end with
+        s.offsets[stage][b] = gbase[stage][b];
+        if (s.tiles[stage] && b < E) {
+            const uint32_t first = tile_base[stage][b], n = tile_base[stage][b + 1u] - first;
+            for (uint32_t j = 0; j < n; j++) s.tiles[stage][first + j] = (b << 16) | j;
+        }
+        if (s.tiles[stage] && b == E) *s.tile_count[stage] = tile_base[stage][E];
+    }
+}
+
 __global__ void __launch_bounds__(256) group_hist_kernel(SlotKey key, const uint32_t* control,
                                                         uint32_t max_tokens, uint32_t* block_hist, uint32_t* position) {
     key.capacity = min_u32(control[0], max_tokens) * key.K;
@@ -756,6 +884,13 @@ bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts) 
 
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
     const uint32_t count = s.tokens * s.K;
+    const uint32_t rank_threads = layer_schedule_rank_threads(count);
+    if (s.expert_count == 0u && count <= kRankChunks * rank_threads &&
+        layer_schedule_rank_smem_bytes(count, s.num_experts) <= 48u * 1024u) {
+        launch_chained(layer_schedule_rank_kernel, dim3(1), dim3(rank_threads),
+                       layer_schedule_rank_smem_bytes(count, s.num_experts), stream, s);
+        return;
+    }
     launch_chained(layer_schedule_small_kernel, dim3(1), dim3(count <= 256u ? 256u : 1024u),
                    layer_schedule_smem_bytes(count, s.num_experts), stream, s);
 }
