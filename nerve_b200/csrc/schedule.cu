@@ -544,88 +544,127 @@ __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedul
     }
 }
 
-// The same schedule for the unpartitioned call (expert_count == 0), where the compact list and both
-// groupings are one stable sort of the routes by expert id seen through different filters: the rank r of a
-// route among the routes of its expert is found once, and every list position is a per-list bucket base
-// plus r.  Rank: a warp ranks its 32 routes with match_any and leaves its per-bucket counts in a table
+// The same schedule from one pass over the routes.  The compact list and both expert groupings are one
+// stable sort of the routes by expert id seen through different filters: the rank r of a route among the
+// listed routes of its expert is found once, and every list position is a per-list bucket base plus r.
+// Rank: a warp ranks its 32 routes with match_any and leaves its per-bucket counts in a table
 // [warp][bucket]; a column-wise running sum turns the counts into the ranks where each warp's routes start.
-// One pass over global memory, four block barriers.
+// The partitioned call (expert_count != 0) lists only owned routes, in source order (one more table column
+// counts them per warp), and its down stage visits the first owned-by-the-down-table-count of them.
+// One round trip to global memory, five block barriers.
 constexpr uint32_t kRankChunks = 4u;  // routes per thread at most (count <= 4 * blockDim)
 
 __host__ __device__ inline uint32_t layer_schedule_rank_threads(uint32_t count) { return count <= 256u ? 256u : 1024u; }
 
 __host__ __device__ inline size_t layer_schedule_rank_smem_bytes(uint32_t count, uint32_t num_experts) {
-    const size_t buckets = (size_t)num_experts + 1u;
+    const size_t columns = (size_t)num_experts + 2u;  // experts, out-of-range ids, owned routes
     const size_t warps = ((size_t)count + 31u) / 32u;
-    // table (u16, rounded to words), hist, base_all, gbase[2], tile_base[2] (buckets + 1 each), kept[2] (bytes)
-    return ((warps * buckets + 1u) / 2u + 6u * (buckets + 1u)) * sizeof(uint32_t) + 2u * buckets;
+    // table (u16, rounded to words); hist, hist_down, base_all, gbase[2], tile_base[2] (columns + 1 words each);
+    // two totals; kept[2] (a byte per column)
+    return ((warps * columns + 1u) / 2u + 7u * (columns + 1u) + 2u) * sizeof(uint32_t) + 2u * columns;
 }
 
 __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule s) {
     extern __shared__ uint32_t smem_words[];
     const uint32_t count = s.tokens * s.K;
-    const uint32_t E = s.num_experts, B = E + 1u;  // bucket E collects out-of-range expert ids
+    const uint32_t E = s.num_experts;
+    const uint32_t B = E + 1u;   // bucket E collects out-of-range expert ids
+    const uint32_t C = E + 2u;   // column B counts the owned routes of a warp (partitioned calls)
     const uint32_t V = (count + 31u) / 32u;
-    const uint32_t table_words = (V * B + 1u) / 2u;
+    const uint32_t table_words = (V * C + 1u) / 2u;
     uint16_t* table = reinterpret_cast<uint16_t*>(smem_words);
-    uint32_t* hist = smem_words + table_words;
-    uint32_t* base_all = hist + (B + 1u);
-    uint32_t* gbase[2] = {base_all + (B + 1u), base_all + 2u * (B + 1u)};
-    uint32_t* tile_base[2] = {base_all + 3u * (B + 1u), base_all + 4u * (B + 1u)};
-    uint8_t* kept = reinterpret_cast<uint8_t*>(base_all + 5u * (B + 1u));  // [2][B]: the stage keeps routes of this bucket
+    uint32_t* hist = smem_words + table_words;  // listed routes per bucket
+    uint32_t* hist_down = hist + (C + 1u);      // of which the down stage visits
+    uint32_t* base_all = hist + 2u * (C + 1u);
+    uint32_t* gbase[2] = {hist + 3u * (C + 1u), hist + 4u * (C + 1u)};
+    uint32_t* tile_base[2] = {hist + 5u * (C + 1u), hist + 6u * (C + 1u)};
+    uint32_t* totals = hist + 7u * (C + 1u);  // owned routes under the gate/up and the down slot table
+    uint8_t* kept = reinterpret_cast<uint8_t*>(totals + 2u);  // [2][C]: the stage keeps routes of this bucket
     const uint32_t lane = threadIdx.x & 31u;
+    const bool partitioned = s.expert_count != 0u;
+    const uint32_t owned_end = s.expert_start + s.expert_count;
 
     for (uint32_t w = threadIdx.x; w < table_words; w += blockDim.x) smem_words[w] = 0u;
+    if (threadIdx.x < 2u) totals[threadIdx.x] = 0u;
     grid_dependency_sync();
-    if (threadIdx.x < 14u) {
-        const uint32_t stage = threadIdx.x / 7u, j = threadIdx.x % 7u;
-        const uint32_t value = j == 0u ? s.tokens : j == 1u ? s.expert_start : j == 2u ? 0u : j == 3u ? count
-                             : j == 4u ? s.K * s.tiles_per_route[stage] : j == 5u ? s.tokens : 1u;
-        s.control[stage][j] = value;
-    }
     // residency of every expert for both stages (bucket E is never kept)
-    for (uint32_t i = threadIdx.x; i < 2u * B; i += blockDim.x) {
-        const uint32_t stage = i / B, b = i % B;
+    for (uint32_t i = threadIdx.x; i < 2u * C; i += blockDim.x) {
+        const uint32_t stage = i / C, b = i % C;
         kept[i] = (b < E && s.experts[stage][b].w[0] != nullptr) ? 1u : 0u;
     }
-    uint32_t bucket[kRankChunks], before[kRankChunks];
+    uint32_t bucket[kRankChunks], before[kRankChunks], owned_before[kRankChunks];
     __syncthreads();
 #pragma unroll
     for (uint32_t c = 0; c < kRankChunks; c++) {
         const uint32_t i = c * blockDim.x + threadIdx.x;
-        bucket[c] = kUnboundSlot;
+        bucket[c] = kUnboundSlot;  // not listed
         before[c] = 0u;
-        if (c * blockDim.x < count) {  // uniform over the block: whole warps take part in the match
-            if (i < count) bucket[c] = min_u32(s.routes[i] & 0xffffu, E);
+        owned_before[c] = 0u;
+        if (c * blockDim.x < count) {  // uniform over the block: whole warps take part in the votes
+            bool listed = i < count, owned_down = false;
+            uint32_t e = 0u;
+            if (listed) e = s.routes[i] & 0xffffu;
+            if (partitioned) {
+                const bool in_range = listed && e >= s.expert_start && e < owned_end;
+                listed = in_range && resource_is_local(s.slots[0], s.slot_words[0], 4u, e);
+                owned_down = in_range && resource_is_local(s.slots[1], s.slot_words[1], 2u, e);
+                const uint32_t owners = __ballot_sync(0xffffffffu, listed);
+                const uint32_t owners_down = __ballot_sync(0xffffffffu, owned_down);
+                owned_before[c] = __popc(owners & ((1u << lane) - 1u));
+                if (lane == 0u) {
+                    if (owners) {  // a warp past the end of the routes has no row in the table
+                        table[(size_t)(i >> 5) * C + B] = (uint16_t)__popc(owners);
+                        atomicAdd(totals + 0, (uint32_t)__popc(owners));
+                    }
+                    if (owners_down) atomicAdd(totals + 1, (uint32_t)__popc(owners_down));
+                }
+            }
+            if (listed) bucket[c] = min_u32(e, E);
             const uint32_t peers = __match_any_sync(0xffffffffu, bucket[c]);
             before[c] = __popc(peers & ((1u << lane) - 1u));
-            if (i < count && lane == (uint32_t)__ffs(peers) - 1u) table[(size_t)(i >> 5) * B + bucket[c]] = (uint16_t)__popc(peers);
+            if (listed && lane == (uint32_t)__ffs(peers) - 1u) table[(size_t)(i >> 5) * C + bucket[c]] = (uint16_t)__popc(peers);
         }
     }
     __syncthreads();
-    for (uint32_t b = threadIdx.x; b < B; b += blockDim.x) {
+    // the down stage of a partitioned call visits the first totals[1] entries of the compact list
+    const uint32_t listed_total = partitioned ? totals[0] : count;
+    const uint32_t down_total = partitioned ? totals[1] : count;
+    const bool cut = down_total < listed_total;
+    for (uint32_t b = threadIdx.x; b < C; b += blockDim.x) {
         uint32_t running = 0u;
         for (uint32_t v = 0; v < V; v++) {
-            const uint32_t here = table[(size_t)v * B + b];
-            table[(size_t)v * B + b] = (uint16_t)running;
+            const uint32_t here = table[(size_t)v * C + b];
+            table[(size_t)v * C + b] = (uint16_t)running;
             running += here;
         }
         hist[b] = running;
+        hist_down[b] = cut ? 0u : running;
     }
     __syncthreads();
-    // five exclusive scans over the buckets, a warp each: the compact list, and per stage the grouped list
-    // and the tile list
+    if (cut) {
+        // the entries cut off are the last in source order, so the ranks of the others stand; only the counts change
+#pragma unroll
+        for (uint32_t c = 0; c < kRankChunks; c++) {
+            const uint32_t i = c * blockDim.x + threadIdx.x;
+            if (i < count && bucket[c] != kUnboundSlot && table[(size_t)(i >> 5) * C + B] + owned_before[c] < down_total)
+                atomicAdd(hist_down + bucket[c], 1u);
+        }
+        __syncthreads();
+    }
+    // five exclusive scans over the buckets, a warp each: the compact list of an unpartitioned call, and per
+    // stage the grouped list and the tile list
     const uint32_t warp = threadIdx.x >> 5;
     if (warp < 5u) {
         const uint32_t stage = warp == 0u ? 0u : (warp - 1u) & 1u;
         const bool tiles = warp >= 3u;
         uint32_t* out = warp == 0u ? base_all : tiles ? tile_base[stage] : gbase[stage];
+        const uint32_t* counts = stage == 1u ? hist_down : hist;
         uint32_t carry = 0u;
         for (uint32_t b0 = 0; b0 < B; b0 += 32u) {
             const uint32_t b = b0 + lane;
-            uint32_t v = b < B ? hist[b] : 0u;
+            uint32_t v = b < B ? counts[b] : 0u;
             if (warp != 0u && b < B) {
-                v = kept[stage * B + b] ? v : 0u;
+                v = kept[stage * C + b] ? v : 0u;
                 if (tiles) v = (v + s.n_tile[stage] - 1u) / s.n_tile[stage];
             }
             uint32_t incl = v;
@@ -640,22 +679,42 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
         if (lane == 0u) out[B] = carry;
     }
     __syncthreads();
+    if (threadIdx.x < 14u) {
+        const uint32_t stage = threadIdx.x / 7u, j = threadIdx.x % 7u;
+        const uint32_t visited = stage == 0u ? listed_total : down_total;
+        uint32_t value = 1u;  // word 6; word 5 of a partitioned call
+        if (j == 0u) value = s.tokens;
+        if (j == 1u) value = s.expert_start;
+        if (j == 2u) value = s.expert_count;
+        if (j == 3u) value = visited;
+        if (j == 4u) value = (partitioned ? visited : s.K) * s.tiles_per_route[stage];
+        if (j == 5u && !partitioned) value = s.tokens;
+        s.control[stage][j] = value;
+    }
+    // a down count beyond the compact list makes the down stage read entries that were never written
+    if (threadIdx.x == 0u && down_total > listed_total) raise_status(s.status, NVMOE_STATUS_ROUTE_OUT_OF_RANGE);
     const uint32_t data_words = s.K * (s.I / 2u), frame_words = data_words + s.K;
 #pragma unroll
     for (uint32_t c = 0; c < kRankChunks; c++) {
         const uint32_t i = c * blockDim.x + threadIdx.x;
         if (i >= count) continue;
         const uint32_t b = bucket[c];
-        const uint32_t rank = table[(size_t)(i >> 5) * B + b] + before[c];
-        const uint32_t at = base_all[b] + rank;
-        s.intermediates[(size_t)(at / s.K) * frame_words + data_words + at % s.K] = i;
+        const bool listed = b != kUnboundSlot;
+        uint32_t rank = 0u, at = 0u;
+        if (listed) {
+            rank = table[(size_t)(i >> 5) * C + b] + before[c];
+            at = partitioned ? table[(size_t)(i >> 5) * C + B] + owned_before[c] : base_all[b] + rank;
+            s.intermediates[(size_t)(at / s.K) * frame_words + data_words + at % s.K] = i;
+        }
         for (uint32_t stage = 0; stage < 2u; stage++) {
             uint32_t place = kUnboundSlot;
-            if (kept[stage * B + b]) {
-                place = gbase[stage][b] + rank;
-                s.grouped[stage][place] = i;
-            } else {
-                raise_status(s.status, b == E ? NVMOE_STATUS_ROUTE_OUT_OF_RANGE : NVMOE_STATUS_EXPERT_NOT_RESIDENT);
+            if (listed && (stage == 0u || at < down_total)) {
+                if (kept[stage * C + b]) {
+                    place = gbase[stage][b] + rank;
+                    s.grouped[stage][place] = i;
+                } else {
+                    raise_status(s.status, b == E ? NVMOE_STATUS_ROUTE_OUT_OF_RANGE : NVMOE_STATUS_EXPERT_NOT_RESIDENT);
+                }
             }
             if (s.position[stage]) s.position[stage][i] = place;
         }
@@ -885,7 +944,7 @@ bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts) 
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
     const uint32_t count = s.tokens * s.K;
     const uint32_t rank_threads = layer_schedule_rank_threads(count);
-    if (s.expert_count == 0u && count <= kRankChunks * rank_threads &&
+    if (count <= kRankChunks * rank_threads &&
         layer_schedule_rank_smem_bytes(count, s.num_experts) <= 48u * 1024u) {
         launch_chained(layer_schedule_rank_kernel, dim3(1), dim3(rank_threads),
                        layer_schedule_rank_smem_bytes(count, s.num_experts), stream, s);
