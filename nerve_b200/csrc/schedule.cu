@@ -552,7 +552,8 @@ __global__ void __launch_bounds__(1024) layer_schedule_small_kernel(LayerSchedul
 // The partitioned call (expert_count != 0) lists only owned routes, in source order (one more table column
 // counts them per warp), and its down stage visits the first owned-by-the-down-table-count of them.
 // One round trip to global memory, five block barriers.
-constexpr uint32_t kRankChunks = 4u;  // routes per thread at most (count <= 4 * blockDim)
+constexpr uint32_t kRankChunks = 16u;  // routes per thread at most (count <= 16 * blockDim); the kernel is built for 1, 4 and 16
+constexpr uint32_t kNotListed = 0xffffu;  // bucket field of a route that is in no list
 
 __host__ __device__ inline uint32_t layer_schedule_rank_threads(uint32_t count) { return count <= 256u ? 256u : 1024u; }
 
@@ -564,6 +565,7 @@ __host__ __device__ inline size_t layer_schedule_rank_smem_bytes(uint32_t count,
     return ((warps * columns + 1u) / 2u + 7u * (columns + 1u) + 2u) * sizeof(uint32_t) + 2u * columns;
 }
 
+template <uint32_t CHUNKS>
 __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule s) {
     extern __shared__ uint32_t smem_words[];
     const uint32_t count = s.tokens * s.K;
@@ -592,14 +594,13 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
         const uint32_t stage = i / C, b = i % C;
         kept[i] = (b < E && s.experts[stage][b].w[0] != nullptr) ? 1u : 0u;
     }
-    uint32_t bucket[kRankChunks], before[kRankChunks], owned_before[kRankChunks];
+    // per route: bucket (16 bits) | routes of the same bucket before it in its warp (8) | owned routes before it (8)
+    uint32_t state[CHUNKS];
     __syncthreads();
 #pragma unroll
-    for (uint32_t c = 0; c < kRankChunks; c++) {
+    for (uint32_t c = 0; c < CHUNKS; c++) {
         const uint32_t i = c * blockDim.x + threadIdx.x;
-        bucket[c] = kUnboundSlot;  // not listed
-        before[c] = 0u;
-        owned_before[c] = 0u;
+        state[c] = kNotListed;
         if (c * blockDim.x < count) {  // uniform over the block: whole warps take part in the votes
             bool listed = i < count, owned_down = false;
             uint32_t e = 0u;
@@ -610,7 +611,7 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
                 owned_down = in_range && resource_is_local(s.slots[1], s.slot_words[1], 2u, e);
                 const uint32_t owners = __ballot_sync(0xffffffffu, listed);
                 const uint32_t owners_down = __ballot_sync(0xffffffffu, owned_down);
-                owned_before[c] = __popc(owners & ((1u << lane) - 1u));
+                state[c] |= (uint32_t)__popc(owners & ((1u << lane) - 1u)) << 24;
                 if (lane == 0u) {
                     if (owners) {  // a warp past the end of the routes has no row in the table
                         table[(size_t)(i >> 5) * C + B] = (uint16_t)__popc(owners);
@@ -619,10 +620,10 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
                     if (owners_down) atomicAdd(totals + 1, (uint32_t)__popc(owners_down));
                 }
             }
-            if (listed) bucket[c] = min_u32(e, E);
-            const uint32_t peers = __match_any_sync(0xffffffffu, bucket[c]);
-            before[c] = __popc(peers & ((1u << lane) - 1u));
-            if (listed && lane == (uint32_t)__ffs(peers) - 1u) table[(size_t)(i >> 5) * C + bucket[c]] = (uint16_t)__popc(peers);
+            const uint32_t bucket = listed ? min_u32(e, E) : kNotListed;
+            const uint32_t peers = __match_any_sync(0xffffffffu, bucket);
+            state[c] = (state[c] & 0xff000000u) | ((uint32_t)__popc(peers & ((1u << lane) - 1u)) << 16) | bucket;
+            if (listed && lane == (uint32_t)__ffs(peers) - 1u) table[(size_t)(i >> 5) * C + bucket] = (uint16_t)__popc(peers);
         }
     }
     __syncthreads();
@@ -644,10 +645,11 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
     if (cut) {
         // the entries cut off are the last in source order, so the ranks of the others stand; only the counts change
 #pragma unroll
-        for (uint32_t c = 0; c < kRankChunks; c++) {
+        for (uint32_t c = 0; c < CHUNKS; c++) {
             const uint32_t i = c * blockDim.x + threadIdx.x;
-            if (i < count && bucket[c] != kUnboundSlot && table[(size_t)(i >> 5) * C + B] + owned_before[c] < down_total)
-                atomicAdd(hist_down + bucket[c], 1u);
+            const uint32_t bucket = state[c] & 0xffffu;
+            if (i < count && bucket != kNotListed && table[(size_t)(i >> 5) * C + B] + (state[c] >> 24) < down_total)
+                atomicAdd(hist_down + bucket, 1u);
         }
         __syncthreads();
     }
@@ -695,15 +697,15 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
     if (threadIdx.x == 0u && down_total > listed_total) raise_status(s.status, NVMOE_STATUS_ROUTE_OUT_OF_RANGE);
     const uint32_t data_words = s.K * (s.I / 2u), frame_words = data_words + s.K;
 #pragma unroll
-    for (uint32_t c = 0; c < kRankChunks; c++) {
+    for (uint32_t c = 0; c < CHUNKS; c++) {
         const uint32_t i = c * blockDim.x + threadIdx.x;
         if (i >= count) continue;
-        const uint32_t b = bucket[c];
-        const bool listed = b != kUnboundSlot;
+        const uint32_t b = state[c] & 0xffffu;
+        const bool listed = b != kNotListed;
         uint32_t rank = 0u, at = 0u;
         if (listed) {
-            rank = table[(size_t)(i >> 5) * C + b] + before[c];
-            at = partitioned ? table[(size_t)(i >> 5) * C + B] + owned_before[c] : base_all[b] + rank;
+            rank = table[(size_t)(i >> 5) * C + b] + ((state[c] >> 16) & 0xffu);
+            at = partitioned ? table[(size_t)(i >> 5) * C + B] + (state[c] >> 24) : base_all[b] + rank;
             s.intermediates[(size_t)(at / s.K) * frame_words + data_words + at % s.K] = i;
         }
         for (uint32_t stage = 0; stage < 2u; stage++) {
@@ -937,16 +939,28 @@ void launch_route_compact(const uint32_t* routes, uint32_t* intermediates, const
         intermediate_size, tiles_per_route, num_experts, scratch.block_hist, scratch.bucket_base);
 }
 
+static bool rank_schedule_fits(uint64_t count, uint32_t num_experts) {
+    return count <= (uint64_t)kRankChunks * layer_schedule_rank_threads((uint32_t)count) && num_experts < kNotListed - 1u &&
+           layer_schedule_rank_smem_bytes((uint32_t)count, num_experts) <= 48u * 1024u;
+}
+
+static bool three_sort_schedule_fits(uint64_t count, uint32_t num_experts) {
+    return count <= kSmallSortLimit && layer_schedule_smem_bytes((uint32_t)count, num_experts) <= 48u * 1024u;
+}
+
 bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts) {
-    return (uint64_t)tokens * K <= kSmallSortLimit && layer_schedule_smem_bytes(tokens * K, num_experts) <= 48u * 1024u;
+    const uint64_t count = (uint64_t)tokens * K;
+    return rank_schedule_fits(count, num_experts) || three_sort_schedule_fits(count, num_experts);
 }
 
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
     const uint32_t count = s.tokens * s.K;
-    const uint32_t rank_threads = layer_schedule_rank_threads(count);
-    if (count <= kRankChunks * rank_threads &&
-        layer_schedule_rank_smem_bytes(count, s.num_experts) <= 48u * 1024u) {
-        launch_chained(layer_schedule_rank_kernel, dim3(1), dim3(rank_threads),
+    if (rank_schedule_fits(count, s.num_experts)) {
+        const uint32_t threads = layer_schedule_rank_threads(count);
+        const uint32_t chunks = (count + threads - 1u) / threads;
+        auto kernel = chunks <= 1u ? layer_schedule_rank_kernel<1> : chunks <= 4u ? layer_schedule_rank_kernel<4>
+                                                                                  : layer_schedule_rank_kernel<kRankChunks>;
+        launch_chained(kernel, dim3(1), dim3(threads),
                        layer_schedule_rank_smem_bytes(count, s.num_experts), stream, s);
         return;
     }

@@ -336,7 +336,7 @@ def test_expert_ranges_partition_the_layer(device, path):
     plan.destroy()
 
 
-@pytest.mark.parametrize("tokens", [24, 700])  # 700: more than 4096 slots, the multi-block schedule
+@pytest.mark.parametrize("tokens", [24, 700, 1500])  # 700: several routes per thread of the one-block schedule; 1500: more than 16384 slots, the multi-block schedule
 @pytest.mark.parametrize("path", PATHS)
 def test_preselected_routes_form_reproduces_the_layer(device, path, tokens):
     """The owner's side of an expert-parallel exchange: the routes of a finished router arrive as rows
