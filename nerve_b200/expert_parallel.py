@@ -428,5 +428,18 @@ def bench_main(args, cfg, tokens, metric, unit):
                     "ms_per_step": statistics.mean(e2e)},
             "gpu_launches": int(layer.home.launches() + layer.work.launches()),
         }
+        try:
+            # whole step of one rank against the HBM copy peak: the weights of the experts it owns cross HBM once
+            # per step; the exchanges and the small kernels around them are what the fraction leaves out
+            from bench import measured_peaks
+
+            peaks, kind = measured_peaks()
+            achieved = touched / (ms * 1e-3) / 1e9
+            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "whole step, per rank",
+                                "peak_kind": f"{kind} STREAM-style copy", "algorithmic_bytes_per_launch": touched}
+        except Exception as error:  # the throughput line must not depend on this
+            line["roofline"] = None
+            line["roofline_error"] = str(error)
         print(json.dumps(line))
     dist.destroy_process_group()
