@@ -4,20 +4,23 @@
 
 A step is one pass of the whole layer (router projection, routing, schedule, gate/up + SwiGLU,
 down, combine) over one batch of seeded synthetic tokens.  `value` is timed with the inputs
-resident in HBM (CUDA events on the launching stream, one pair per step, L2 flushed between
-steps); `e2e` is the same metric through the host-buffer call, host<->device copies inside the
-timed region.  The `roofline` object is for the dominant kernel (gate/up), the `cpu_baseline`
-object times the CPU restatement of the reference shaders on this box's host cores.
+resident in HBM: exactly K steps back to back between two CUDA events on the launching stream with
+a synchronise on both sides; that block is repeated until half a second of device time has been
+measured and the median block is reported, with the spread beside it.  `e2e` is the same metric
+through the host-buffer call, host<->device copies inside the timed region.  The `roofline` object
+is for the dominant kernel (gate/up) with the whole-layer figure beside it, `parity` checks the
+very output the timed configuration produces against the CPU checker, `cpu_baseline` times the CPU
+restatement of the reference shaders on this box's host cores, and `extra` holds the other
+configurations of the benchmark (decode batch sizes, prefill, the two large layers).
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
-import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -28,10 +31,12 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 from nerve_b200 import synthetic  # noqa: E402
+from nerve_b200.clocks import ClockSampler  # noqa: E402
 
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-L2_BYTES = 126 * 1024 * 1024  # B200 L2
+DTYPE = "fp8_e4m3 x mxfp4_e2m1 -> f32"
+MIN_TIMED_SECONDS = 0.5
 
 WORKLOADS = {
     # name -> (config, default tokens, bound)
@@ -50,52 +55,33 @@ def measured_peaks() -> tuple[dict, str]:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+def kernel_source_hash() -> str:
+    """Identifies the expert kernels a DRAM-traffic capture was taken on."""
+    h = hashlib.sha256()
+    for name in ("experts_tc.cu", "tcgen05.cuh"):
+        h.update((ROOT / "nerve_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:12]
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.lines: list[str] = []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
-        except OSError:
-            self.proc = None
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        sm, smax, reasons = [], None, set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax = float(parts[1])
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[3:7]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+def captured_traffic(workload: str, tokens: int) -> tuple[dict | None, str]:
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+    profiles/ (one table row per kernel). Returns (None, why) when there is no capture of this workload or
+    the expert kernels have changed since it was taken."""
+    table = ROOT / "profiles" / "dram_traffic_per_launch.md"
+    if not table.exists():
+        return None, "no capture table"
+    found, stale = {}, False
+    for line in table.read_text().splitlines():
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(cells) < 5 or cells[0] != workload or not cells[1].isdigit() or int(cells[1]) != tokens:
+            continue
+        if cells[4] != kernel_source_hash():
+            stale = True
+            continue
+        found[cells[2]] = int(cells[3].replace(" ", "").replace(",", ""))
+    if found:
+        return found, "ncu capture of these kernels, profiles/dram_traffic_per_launch.md"
+    return None, "the capture under profiles/ predates the current expert kernels" if stale else "no capture of this workload"
 
 
 def algorithmic_bytes(cfg: synthetic.MoeConfig, tokens: int, distinct: int) -> dict:
@@ -111,134 +97,131 @@ def layer_flops(cfg: synthetic.MoeConfig, tokens: int) -> float:
     return 2.0 * tokens * cfg.total_k * 3 * cfg.hidden * cfg.intermediate
 
 
-class LayerRunner:
-    """One rank's resident layer: weights, plan, device buffers."""
+# ---- timing ------------------------------------------------------------------------------------------
 
-    def __init__(self, cfg, tokens, seed, expert_path, device_index=0, expert_start=0, expert_count=0, banks=0):
-        from nerve_b200.backend import CudaComputeDevice, ExpertBank, MoePlan
+def timed_blocks(torch, runner, steps, warmup, scratch=None, sample_clocks=False, min_seconds=MIN_TIMED_SECONDS,
+                 max_blocks=400):
+    """Blocks of exactly `steps` layer calls back to back between two CUDA events on the stream they run
+    on, a synchronise on both sides of every block, no per-stage events inside; blocks repeat until
+    `min_seconds` of device time. Returns (ms per step of every block, launches per step, clocks)."""
+    runner.plan.set_profiling(False)
+    stream = torch.cuda.ExternalStream(runner.device.stream(), device=f"cuda:{runner.device.ordinal}")
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(max(warmup, runner.n_banks + 1)):  # every bank's tables are resolved once before timing
+        runner.launch_step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(runner.device.ordinal) if sample_clocks else None
+    if sampler:
+        sampler.start()
+    blocks, total, launches = [], 0.0, 0
+    while total < min_seconds * 1e3 and len(blocks) < max_blocks:
+        if scratch is not None:
+            flush_l2(torch, scratch)
+        before = runner.plan.launches()
+        torch.cuda.synchronize()
+        begin.record(stream)
+        for _ in range(steps):
+            runner.launch_step()
+        end.record(stream)
+        torch.cuda.synchronize()
+        launches = runner.plan.launches() - before
+        ms = begin.elapsed_time(end)
+        total += ms
+        blocks.append(ms / steps)
+    clocks = sampler.stop() if sampler else None
+    runner.plan.set_profiling(True)
+    return blocks, launches, clocks
 
-        self.cfg, self.tokens = cfg, tokens
-        self.device = CudaComputeDevice(device_index)
-        self.case = synthetic.make_case(cfg, tokens, seed=seed, with_weights=False)
-        # weights are generated and uploaded one expert at a time to keep host memory flat
-        owned = range(cfg.total_experts) if not expert_count else range(expert_start, expert_start + expert_count)
-        w = {k: [None] * cfg.total_experts for k in ("w1", "s1", "w3", "s3", "w2", "s2")}
-        H, I = cfg.hidden, cfg.intermediate
-        for e in owned:
-            g = synthetic._stream(seed, f"expert{e}")
-            w["w1"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
-            w["s1"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
-            w["w3"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
-            w["s3"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
-            w["w2"][e] = g.integers(0, 256, (H, I // 2), dtype=np.uint8)
-            w["s2"][e] = g.integers(121, 128, (H, I // 32), dtype=np.uint8)
-        # Several resident copies of the layer's weights ("banks", as a model's successive layers would be),
-        # visited in turn: the weights a step reads were last read a whole cycle ago, and the cycle is
-        # several times the L2 size, so every step streams its weights from HBM without dirtying L2 first.
-        per_expert = 3 * H * I * 17 // 32
-        touched = max(1, min(tokens * cfg.total_k, len(owned))) * per_expert
-        self.n_banks = banks or max(2, min(8, -(-4 * L2_BYTES // touched)))
-        self.banks = [ExpertBank.upload(self.device, w["w1"], w["s1"], w["w3"], w["s3"], w["w2"], w["s2"], present=list(owned))
-                      for _ in range(self.n_banks)]
-        self.bank = self.banks[0]
-        self.cycle_bytes = touched * self.n_banks
-        self.turn = 0
-        self.host_weights = w if os.environ.get("NVMOE_BENCH_KEEP_WEIGHTS") else None
-        self.plan = MoePlan.for_config(self.device, cfg, tokens)
-        if expert_path:
-            self.plan.set_expert_path(expert_path)
-        self.plan.set_profiling(True)
-        c = self.case
-        self.hidden = self.device.resident_buffer_from(c.hidden)
-        self.router_w = self.device.resident_buffer_from(c.router_w)
-        self.router_bias = self.device.resident_buffer_from(c.router_bias) if c.router_bias is not None else None
-        self.select_bias = self.device.resident_buffer_from(c.select_bias) if c.select_bias is not None else None
-        self.output = self.device.create_resident_buffer(tokens * cfg.hidden * 2)
-        self.telemetry = self.device.create_resident_buffer(self.plan.telemetry_words() * 4)
-        # the end-to-end call reads its tokens from, and writes its result to, page-locked host memory
-        import torch
 
-        self._pinned = (torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory(),
-                        torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory())
-        self.hidden_host = self._pinned[0].numpy().view(np.uint16)
-        self.hidden_host[...] = c.hidden
-        self.out_host = self._pinned[1].numpy().view(np.uint16)
-        self.kw = dict(router_weights=self.router_w, router_bias=self.router_bias, bias=self.select_bias,
-                       telemetry=self.telemetry, expert_start=expert_start, expert_count=expert_count)
-
-    def next_bank(self):
-        self.turn += 1
-        return self.banks[self.turn % self.n_banks]
-
-    def step_resident(self) -> dict:
-        self.plan.layer(self.tokens, self.next_bank(), self.hidden, self.output, **self.kw)
-        return self.plan.last_report()
-
-    def launch_step(self) -> None:
-        """One layer call, nothing read back: the stream keeps running."""
-        self.plan.layer(self.tokens, self.next_bank(), self.hidden, self.output, **self.kw)
-
-    def step_host(self) -> float:
-        bank = self.next_bank()
-        t0 = time.perf_counter()
-        self.plan.layer_host(self.tokens, bank, self.hidden_host, self.out_host, **self.kw)
-        return (time.perf_counter() - t0) * 1e3
+def profiled_steps(torch, runner, steps, warmup, scratch=None):
+    """Per-kernel times: an event pair around every stage and around each expert kernel."""
+    runner.plan.set_profiling(True)
+    for _ in range(max(warmup, runner.n_banks + 1)):
+        runner.step_resident()
+    reports = []
+    for _ in range(steps):
+        if scratch is not None:
+            flush_l2(torch, scratch)
+        reports.append(runner.step_resident())  # last_report synchronises the stream
+    return reports
 
 
 def flush_l2(torch, scratch):
-    if scratch is None:
-        return
     scratch.add_(1)  # read + write of a buffer larger than L2
     torch.cuda.synchronize()
 
 
-def cpu_baseline(cfg, tokens, seed, sample_tokens, budget_s=12.0):
+def spread(blocks):
+    return {"blocks": len(blocks), "ms_median": statistics.median(blocks), "ms_min": min(blocks), "ms_max": max(blocks)}
+
+
+# ---- parity of the timed configuration -----------------------------------------------------------------
+
+def parity_of(runner, sample_count=24, rank_slice=None):
+    """Checks the output of one layer call of `runner` against the CPU checker: routes and logits of the
+    whole batch bit for bit, the layer output on a seeded token sample within the stated tolerance."""
+    from oracle import sampled
+
+    cfg, case, tokens = runner.cfg, runner.case, runner.tokens
+    logits_buf = runner.device.create_resident_buffer(tokens * ((cfg.experts + 1) // 2) * 4)
+    runner.plan.layer(tokens, runner.bank, runner.hidden, runner.output, logits=logits_buf, **runner.kw)
+    status = runner.plan.status()
+    want_logits, want_routes, _ = sampled.routing_for_batch(cfg, case.hidden, case.router_w, case.router_bias, case.select_bias)
+    logits_exact = bool(np.array_equal(logits_buf.read(np.uint32).reshape(want_logits.shape), want_logits))
+    routes_exact = bool(np.array_equal(runner.read_routes(), want_routes))
+    logits_buf.destroy()
+    picked = sampled.sample_tokens(tokens, sample_count, seed=tokens)
+    want = sampled.layer_on_sample(cfg, case.hidden, want_logits, case.select_bias, picked,
+                                   lambda e: synthetic.expert_tensors(cfg, runner.seed, e))
+    m = sampled.error_metrics(runner.read_output()[picked], want["output"])
+    ok = routes_exact and logits_exact and status == 0 and sampled.within_tolerance(m)
+    return {"pass": bool(ok), "routes_exact": routes_exact, "logits_exact": logits_exact, "status_bits": status,
+            "rel_l2": m["rel_l2"], "max_abs": m["max_abs"], "max_abs_over_peak": m["max_abs_over_peak"],
+            "output_peak": m["peak"], "mismatched_bf16": m["mismatched"], "values": m["count"],
+            "sample_tokens": int(len(picked)),
+            "tolerance": f"rel_l2 <= {sampled.REL_L2_TOL}, max_abs <= {sampled.MAX_ABS_OVER_PEAK_TOL} of the output peak, "
+                         "against the f64-accumulated checker on the same quantised operands"}
+
+
+# ---- CPU arm --------------------------------------------------------------------------------------------
+
+def cpu_baseline(cfg, tokens, seed, sample_tokens, budget_s=12.0, threads=None):
     """Times the CPU restatement of the reference shaders on a bounded sample of the workload: `sample_tokens`
     tokens first (a probe of the host's speed), then as many tokens of the workload as about `budget_s`
     seconds take, passed over repeatedly if the whole workload takes less."""
     from oracle import moe_oracle as mo
 
+    if threads:
+        mo.lib().oracle_set_threads(int(threads))
     probe = _cpu_layer_pass(cfg, tokens, seed, min(tokens, sample_tokens), passes=1)
     rate = probe["value"]
     sample = int(max(1, min(tokens, rate * budget_s)))
     passes = int(max(1, min(50, budget_s * rate / sample)))
     result = _cpu_layer_pass(cfg, tokens, seed, sample, passes)
     # one host core, on a sample a few per cent of that size
-    threads = mo.lib().oracle_set_threads(1)
+    before = mo.lib().oracle_set_threads(1)
     try:
-        few = int(max(1, min(tokens, rate * budget_s / (8.0 * max(1, threads)))))
+        few = int(max(1, min(tokens, rate * budget_s / (8.0 * max(1, before)))))
         result["single_core_value"] = _cpu_layer_pass(cfg, tokens, seed, few, passes=1)["value"]
     finally:
-        mo.lib().oracle_set_threads(threads)
+        mo.lib().oracle_set_threads(before)
     return result
 
 
 def _cpu_layer_pass(cfg, tokens, seed, sample, passes):
     from oracle import moe_oracle as mo
 
-    router_params, expert_params = mo.router_params_from, mo.expert_params_from
     case = synthetic.make_case(cfg, sample, seed=seed, with_weights=False)
+    rp, ep = mo.router_params_from(cfg), mo.expert_params_from(cfg, tier=0)  # tier 0: the shaders' f32 accumulation order
     logits = mo.linear_bf16(case.hidden, case.router_w, case.router_bias)
-    routes, _ = mo.route(router_params(cfg), logits, case.select_bias)
+    routes, _ = mo.route(rp, logits, case.select_bias)
     used = sorted(set((routes.reshape(-1) & 0xFFFF).tolist()))
-    full = case
-    H, I = cfg.hidden, cfg.intermediate
-    empty = np.zeros((1, 1), dtype=np.uint8)
-    w = {k: [empty] * cfg.total_experts for k in ("w1", "s1", "w3", "s3", "w2", "s2")}
-    for e in used:
-        g = synthetic._stream(seed, f"expert{e}")
-        w["w1"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
-        w["s1"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
-        w["w3"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
-        w["s3"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
-        w["w2"][e] = g.integers(0, 256, (H, I // 2), dtype=np.uint8)
-        w["s2"][e] = g.integers(121, 128, (H, I // 32), dtype=np.uint8)
-    weights = mo.ExpertWeights(w["w1"], w["s1"], w["w3"], w["s3"], w["w2"], w["s2"])
-    rp, ep = router_params(cfg), expert_params(cfg, tier=0)  # tier 0: the shaders' f32 accumulation order
+    w = synthetic.expert_tensor_lists(cfg, seed, used, placeholder=np.zeros((1, 1), dtype=np.uint8))
+    weights = mo.ExpertWeights(*(w[k] for k in synthetic.EXPERT_TENSOR_NAMES))
     t0 = time.perf_counter()
     for _ in range(passes):
-        logits = mo.linear_bf16(full.hidden, full.router_w, full.router_bias)
-        mo.moe_layer(rp, ep, full.hidden, logits, full.select_bias, weights)
+        logits = mo.linear_bf16(case.hidden, case.router_w, case.router_bias)
+        mo.moe_layer(rp, ep, case.hidden, logits, case.select_bias, weights)
     seconds = time.perf_counter() - t0
     return {"value": passes * sample / seconds, "unit": UNIT, "cores": mo.lib().oracle_max_threads(), "kind": "port",
             "sample": f"{sample} of {tokens} tokens, whole layer, {passes} pass(es), {seconds:.2f} s",
@@ -246,14 +229,19 @@ def _cpu_layer_pass(cfg, tokens, seed, sample, passes):
 
 
 def run_reference_arm(args, cfg, tokens):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference has no CPU execution of this layer and its GPU path is Vulkan, so this arm times the CPU
+    restatement of its shaders on all the host's cores. Under a multi-process launcher only rank 0 runs; the
+    launcher's OMP_NUM_THREADS=1 is overridden, and the workload is the N ranks' tokens."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
+    world = max(args.gpus, int(os.environ.get("WORLD_SIZE", "1")))
+    tokens = tokens * world  # the GPU arm's weak scaling: every rank brings `tokens` tokens
+    cores = os.cpu_count() or 1
     sample_tokens = max(1, min(tokens, args.reference_sample))
     values = []
     budget = min(10.0, 120.0 / max(1, args.warmup + args.steps))  # the whole run stays within a few minutes
     for _ in range(args.warmup + args.steps):
-        values.append(cpu_baseline(cfg, tokens, args.seed, sample_tokens, budget_s=budget))
+        values.append(cpu_baseline(cfg, tokens, args.seed, sample_tokens, budget_s=budget, threads=cores))
     timed = values[args.warmup:] or values
     value = statistics.mean(v["value"] for v in timed)
     base = dict(timed[-1])
@@ -261,15 +249,328 @@ def run_reference_arm(args, cfg, tokens):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * base["sample_tokens"] / value, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x mxfp4_e2m1 -> f32", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "hidden": cfg.hidden, "intermediate": cfg.intermediate,
-                   "experts": cfg.experts, "k": cfg.total_k,
-                   "note": "CPU restatement of the reference shaders (the reference has no CPU backend); each step is a bounded token sample of the workload"},
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": workload_config(args, cfg, tokens // world, world),
+        "note": "CPU restatement of the reference shaders (the reference has no CPU backend); each step is a "
+                "bounded token sample of the workload",
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def workload_config(args, cfg, tokens, world=1):
+    """The same object in both arms' lines: what is computed, not how."""
+    return {"workload": args.workload, "tokens": tokens, "tokens_per_rank": tokens, "global_tokens": tokens * world,
+            "hidden": cfg.hidden, "intermediate": cfg.intermediate, "experts": cfg.experts, "k": cfg.total_k,
+            "parallelism": "single device" if world == 1 else f"ep{world}"}
+
+
+# ---- one workload on one GPU ------------------------------------------------------------------------------
+
+def roofline_of(cfg, tokens, bound, ms, gate_ms, down_ms, distinct, peaks, peak_kind, probe, workload):
+    ab = algorithmic_bytes(cfg, tokens, distinct)
+    if bound == "hbm":
+        traffic, traffic_note = captured_traffic(workload, tokens)
+        achieved = ab["gate_up"] / (gate_ms * 1e-3) / 1e9
+        hbm = peaks["hbm_gbs"]
+        return {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                "traffic": traffic["gate_up"] if traffic and "gate_up" in traffic else None, "traffic_source": traffic_note,
+                "kernel": "gate_up", "peak_kind": f"{peak_kind} STREAM-style copy",
+                "algorithmic_bytes_per_launch": ab["gate_up"], "kernel_ms": gate_ms,
+                "down_kernel": {"achieved": ab["down"] / (down_ms * 1e-3) / 1e9, "kernel_ms": down_ms,
+                                "frac": ab["down"] / (down_ms * 1e-3) / 1e9 / hbm,
+                                "traffic": traffic["down"] if traffic and "down" in traffic else None,
+                                "algorithmic_bytes_per_launch": ab["down"]},
+                "layer": {"achieved": ab["layer"] / (ms * 1e-3) / 1e9, "frac": ab["layer"] / (ms * 1e-3) / 1e9 / hbm,
+                          "algorithmic_bytes_per_step": ab["layer"]}}
+    flops_gate = 2.0 * tokens * cfg.total_k * 2 * cfg.hidden * cfg.intermediate
+    achieved = flops_gate / (gate_ms * 1e-3) / 1e12
+    # the denominator is the measured rate of the instruction kind that runs (the tensor-pipe probe of this
+    # same process); the cuBLAS bf16 figures are given beside it: the FP8-rate kinds run at twice the bf16
+    # rate, mxf4 (which this path cannot use: the reference's activations are E4M3) at four times
+    peak = probe["tflops"] if probe else peaks["bf16_tflops"] * 2.0
+    kind = ("measured tcgen05.mma kind::mxf8f6f4 block-scaled rate, all SMs, operands in shared memory"
+            if probe else f"2 x {peak_kind} cuBLAS bf16 burst rate (no probe)")
+    def fracs(tf):
+        return {"achieved": tf, "frac": tf / peak, "frac_of_2x_bf16_burst": tf / (peaks["bf16_tflops"] * 2.0),
+                "frac_of_mxf4_rate": tf / (2.0 * peak)}
+    down_tf = flops_gate / 2.0 / (down_ms * 1e-3) / 1e12
+    layer_tf = layer_flops(cfg, tokens) / (ms * 1e-3) / 1e12
+    return {"bound": "tensor", **fracs(achieved), "peak": peak, "unit": "TFLOP/s", "traffic": None, "kernel": "gate_up",
+            "mma_kind": "mxf8f6f4 (E4M3 activations x E2M1 weights, UE8M0 scale per 32)", "peak_kind": kind,
+            "kernel_ms": gate_ms, "flops_per_launch": flops_gate,
+            "down_kernel": {**fracs(down_tf), "kernel_ms": down_ms},
+            "layer": {**fracs(layer_tf), "flops_per_step": layer_flops(cfg, tokens)}}
+
+
+def measure_workload(torch, args, workload, tokens, peaks, peak_kind, probe, share=None, steps=None, min_seconds=MIN_TIMED_SECONDS,
+                     scratch=None, sample_clocks=False, with_e2e=False, parity_tokens=24):
+    """Everything the line reports about one configuration on one GPU. Returns (result dict, runner)."""
+    from nerve_b200.resident_layer import LayerRunner
+
+    cfg_name, default_tokens, bound = WORKLOADS[workload]
+    cfg = synthetic.CONFIGS[cfg_name]
+    tokens = tokens or default_tokens
+    steps = steps or args.steps
+    runner = LayerRunner(cfg, tokens, args.seed, args.expert_path, banks=args.banks, share=share)
+    blocks, launches, clocks = timed_blocks(torch, runner, steps, args.warmup, scratch, sample_clocks, min_seconds)
+    ms = statistics.median(blocks)
+    reports = profiled_steps(torch, runner, min(steps, 10), 3, scratch)
+    gate_ms = statistics.mean(rep["gate_up_kernel_ms"] for rep in reports)
+    down_ms = statistics.mean(rep["down_kernel_ms"] for rep in reports)
+    distinct = reports[-1]["distinct_experts"]
+    result = {
+        "tokens": tokens, "tokens_per_s": tokens / (ms * 1e-3), "ms_per_step": ms, "timing": spread(blocks),
+        "steps_per_block": steps, "launches_per_block": launches, "launches_per_step": launches / steps,
+        "distinct_experts": distinct, "expert_path": "tcgen05" if reports[-1]["tensor_path"] else "cuda-cores",
+        "roofline": roofline_of(cfg, tokens, bound, ms, gate_ms, down_ms, distinct, peaks, peak_kind, probe, workload),
+        "stage_ms": {k: statistics.mean(rep["stage_ms"][k] for rep in reports) for k in reports[-1]["stage_ms"]},
+        "profiled_ms_per_step": statistics.mean(rep["total_ms"] for rep in reports),
+        "clocks": clocks,
+        "l2": (f"inputs larger than L2: {runner.n_banks} resident weight bank(s) visited in turn, "
+               f"{runner.cycle_bytes / 1e6:.0f} MB of weights read between two reads of the same bytes"
+               + ("; plus a 256 MB buffer rewritten between timed blocks" if scratch is not None else "")),
+    }
+    if with_e2e:
+        runner.plan.set_profiling(False)
+        for _ in range(max(3, runner.n_banks + 1)):
+            runner.step_host()
+        e2e_ms, t_end = [], time.perf_counter() + 0.3
+        while len(e2e_ms) < steps or (time.perf_counter() < t_end and len(e2e_ms) < 5000):
+            e2e_ms.append(runner.step_host())
+        e2e = statistics.median(e2e_ms)
+        result["e2e"] = {"value": tokens / (e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": tokens * cfg.hidden * 2,
+                         "d2h_bytes_per_step": tokens * cfg.hidden * 2, "ms_per_step": e2e, "calls": len(e2e_ms),
+                         "ms_min": min(e2e_ms), "ms_max": max(e2e_ms)}
+    if parity_tokens and not args.no_parity:
+        result["parity"] = parity_of(runner, parity_tokens)
+    return result, runner
+
+
+def compact(result):
+    """The figures of an `extra` entry."""
+    r = result["roofline"]
+    out = {"tokens": result["tokens"], "tokens_per_s": result["tokens_per_s"], "ms_per_step": result["ms_per_step"],
+           "timing": result["timing"], "launches_per_step": result["launches_per_step"],
+           "distinct_experts": result["distinct_experts"], "gate_up_kernel_ms": r["kernel_ms"],
+           "down_kernel_ms": r["down_kernel"]["kernel_ms"], "stage_ms": result["stage_ms"], "l2": result["l2"]}
+    if r["bound"] == "hbm":
+        out.update({"bound": "hbm", "layer_hbm_frac": r["layer"]["frac"], "gate_up_hbm_frac": r["frac"],
+                    "down_hbm_frac": r["down_kernel"]["frac"]})
+    else:
+        out.update({"bound": "tensor", "peak_tflops": r["peak"], "peak_kind": r["peak_kind"],
+                    "gate_up": {k: r[k] for k in ("achieved", "frac", "frac_of_2x_bf16_burst", "frac_of_mxf4_rate")},
+                    "down": {k: r["down_kernel"][k] for k in ("achieved", "frac", "frac_of_2x_bf16_burst", "frac_of_mxf4_rate")},
+                    "layer": {k: r["layer"][k] for k in ("achieved", "frac", "frac_of_2x_bf16_burst", "frac_of_mxf4_rate")}})
+    if "parity" in result:
+        out["parity"] = result["parity"]
+    return out
+
+
+def release(runner, banks_too=True):
+    runner.release()
+    if banks_too:
+        for bank in runner.banks:
+            bank.destroy()
+        runner.device.close()
+
+
+def run_single_gpu(args, cfg, tokens, bound):
+    import torch
+
+    from nerve_b200.backend import CudaComputeDevice
+
+    torch.cuda.init()
+    peaks, peak_kind = measured_peaks()
+    # --l2 flush: additionally rewrite a 256 MB buffer between timed blocks (leaves L2 full of dirty lines
+    # whose write-back then competes with the first step's reads); default: the rotating weight banks alone
+    scratch = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda:0") if args.l2 == "flush" else None
+    probe = None
+    if not args.no_probe:
+        dev = CudaComputeDevice(0)
+        probe = dev.probe_mma_rate(128, 8192)
+        probe["narrow_tile"] = dev.probe_mma_rate(96, 8192)
+        dev.close()
+
+    head, runner = measure_workload(torch, args, args.workload, tokens, peaks, peak_kind, probe, scratch=scratch,
+                                    sample_clocks=True, with_e2e=True)
+    line = {
+        "metric": METRIC, "value": head["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE, "data": "synthetic",
+        "config": workload_config(args, cfg, tokens),
+        "run": {"distinct_experts": head["distinct_experts"], "expert_path": head["expert_path"], "l2": head["l2"],
+                "parallelism": "single device"},
+        "timing": head["timing"] | {"rule": f"blocks of {args.steps} steps repeated until {MIN_TIMED_SECONDS} s of device time; "
+                                            "ms_per_step is the median block"},
+        "clocks": head["clocks"], "roofline": head["roofline"], "e2e": head["e2e"],
+        "gpu_launches": head["launches_per_block"], "launches_per_step": head["launches_per_step"],
+        "stage_ms": head["stage_ms"], "profiled_ms_per_step": head["profiled_ms_per_step"],
+    }
+    if "parity" in head:
+        line["parity"] = head["parity"]
+    if probe:
+        line["tensor_pipe_probe"] = probe
+
+    if not args.no_extra and args.workload == "gpt-oss-20b-decode":
+        extra = {}
+        small = argparse.Namespace(**{**vars(args), "warmup": 3})
+        for t in (1, 8, 32):
+            res, r = measure_workload(torch, small, args.workload, t, peaks, peak_kind, probe, share=runner,
+                                      steps=max(5, args.steps), min_seconds=0.15, parity_tokens=t)
+            extra[f"decode_T{t}"] = compact(res)
+            release(r, banks_too=False)
+        release(runner)
+        runner = None
+        for key, workload in (("prefill_T4096", "gpt-oss-20b-prefill"), ("gpt_oss_120b_T8192", "gpt-oss-120b"),
+                              ("deepseek_v3_T16384", "deepseek-v3")):
+            try:
+                big = argparse.Namespace(**{**vars(args), "warmup": 3, "banks": 1 if workload == "deepseek-v3" else args.banks})
+                res, r = measure_workload(torch, big, workload, 0, peaks, peak_kind, probe, steps=3, min_seconds=0.1,
+                                          parity_tokens=12)
+                extra[key] = compact(res)
+                release(r)
+            except Exception as error:  # the headline line must not depend on an extra
+                extra[key] = {"error": f"{type(error).__name__}: {error}"}
+        line["extra"] = extra
+    if runner is not None:
+        release(runner)
+
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(cfg, tokens, args.seed, args.reference_sample, threads=os.cpu_count())
+    print(json.dumps(line))
+
+
+# ---- N GPUs: the layer expert-sharded over the ranks ------------------------------------------------------------
+
+def run_expert_parallel(args, cfg, tokens):
+    """bench.py --gpus N: the layer expert-sharded over N ranks, tokens per rank fixed (weak scaling)."""
+    import torch
+    import torch.distributed as dist
+
+    from nerve_b200.expert_parallel import ExpertParallelLayer
+    from nerve_b200.resident_layer import L2_BYTES
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    # enough resident copies of this rank's experts that a step's weights were last read 4 x L2 ago
+    per_expert = cfg.expert_weight_bytes
+    owned = cfg.experts // world + cfg.always_count
+    touched = max(1, min(tokens * world * cfg.total_k, owned)) * per_expert
+    banks = args.banks or max(2, min(8, -(-4 * L2_BYTES // touched)))
+    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks,
+                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"))
+    for _ in range(max(args.warmup, 3, banks + 1)):
+        layer.step(dist)
+    torch.cuda.synchronize()
+    dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+
+    def block(step_fn):
+        # exactly `steps` steps back to back between two events on the stream they run on, a barrier and a
+        # synchronise on both sides, the slowest rank's time
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        before = layer.home.launches() + layer.work.launches()
+        start.record(layer.stream)
+        for _ in range(args.steps):
+            step_fn()
+        stop.record(layer.stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([start.elapsed_time(stop) / args.steps], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), layer.home.launches() + layer.work.launches() - before
+
+    def repeat(step_fn, min_seconds):
+        # every rank sees the same (all-reduced) block times, so every rank stops after the same block
+        blocks, total, launches = [], 0.0, 0
+        while total < min_seconds * 1e3 and len(blocks) < 200:
+            ms, launches = block(step_fn)
+            blocks.append(ms)
+            total += ms * args.steps
+        return blocks, launches
+
+    blocks, launches = repeat(lambda: layer.step(dist), MIN_TIMED_SECONDS)
+    clocks = sampler.stop() if sampler else None
+    # end to end: tokens start in pinned host memory, the result is read back
+    host_in = torch.from_numpy(layer.hidden_host.view(np.int16)).pin_memory()
+    host_out = torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory()
+
+    def host_step():
+        with torch.cuda.stream(layer.stream):
+            layer.t_hidden.copy_(host_in, non_blocking=True)
+            layer.step(dist)
+            host_out.copy_(layer.t_output, non_blocking=True)
+
+    e2e_blocks, _ = repeat(host_step, 0.2)
+    ms, e2e_ms = statistics.median(blocks), statistics.median(e2e_blocks)
+
+    # parity of this rank's slice of the global batch against the CPU checker (outside every timed region)
+    parity = None
+    if not args.no_parity:
+        from oracle import sampled
+
+        layer.step(dist)
+        got = layer.output()
+        with torch.cuda.stream(layer.stream):
+            layer._route()  # this rank's routes into buffers the host can read (the library's step keeps its own)
+        torch.cuda.synchronize()
+        case = layer.case
+        want_logits, want_routes, _ = sampled.routing_for_batch(cfg, case.hidden, case.router_w, case.router_bias, case.select_bias)
+        mine = np.arange(rank * tokens, (rank + 1) * tokens)
+        picked = mine[sampled.sample_tokens(tokens, 8, seed=rank)]
+        want = sampled.layer_on_sample(cfg, case.hidden, want_logits, case.select_bias, picked,
+                                       lambda e: synthetic.expert_tensors(cfg, args.seed, e))
+        m = sampled.error_metrics(got[picked - rank * tokens], want["output"])
+        routes_exact = bool(np.array_equal(layer.t_routes.cpu().numpy().view(np.uint32), want_routes[mine]))
+        ok = torch.tensor([1 if (sampled.within_tolerance(m) and routes_exact) else 0], device=f"cuda:{local}")
+        worst = torch.tensor([m["rel_l2"], m["max_abs_over_peak"], m["max_abs"]], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        parity = {"pass": bool(ok.item()), "routes_exact": routes_exact, "rel_l2": float(worst[0]), "max_abs_over_peak": float(worst[1]),
+                  "max_abs": float(worst[2]), "sample_tokens": int(len(picked)) * world,
+                  "note": "every rank checks a seeded sample of its own tokens against the CPU checker; worst rank shown"}
+
+    if rank == 0:
+        total_tokens = tokens * world
+        peaks, kind = measured_peaks()
+        achieved = touched / (ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": total_tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": workload_config(args, cfg, tokens, world),
+            "run": {
+                "experts_per_rank": cfg.experts // world,
+                "parallelism": f"ep{world}: experts sharded by contiguous range, tokens data-parallel, "
+                               "NCCL all-to-all dispatch and combine",
+                "exchange": layer.mode,
+                "l2": f"inputs larger than L2: {banks} resident weight banks per rank visited in turn, "
+                      f"{touched * banks / 1e6:.0f} MB of weights read between two reads of the same bytes"},
+            "timing": spread(blocks), "clocks": clocks,
+            "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": tokens * cfg.hidden * 2,
+                    "d2h_bytes_per_step": tokens * cfg.hidden * 2, "ms_per_step": e2e_ms, "timing": spread(e2e_blocks)},
+            "gpu_launches": int(launches), "launches_per_step": launches / args.steps,
+            # whole step of one rank against the HBM copy peak: the weights of the experts it owns cross HBM once
+            # per step; the exchanges and the small kernels around them are what the fraction leaves out
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "whole step, per rank",
+                         "peak_kind": f"{kind} STREAM-style copy", "algorithmic_bytes_per_launch": touched},
+        }
+        if parity:
+            line["parity"] = parity
+        print(json.dumps(line))
+    dist.destroy_process_group()
 
 
 def main() -> None:
@@ -282,12 +583,14 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--expert-path", type=int, default=0, help="0 automatic, 1 CUDA cores, 2 tcgen05")
-    ap.add_argument("--reference-sample", type=int, default=16, help="tokens per step of the CPU arm")
-    ap.add_argument("--no-extra", action="store_true", help="skip the additional batch sizes")
+    ap.add_argument("--reference-sample", type=int, default=16, help="tokens of the CPU arm's first probe")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other batch sizes and configurations")
     ap.add_argument("--l2", default="rotate", choices=["rotate", "flush"],
-                    help="rotate: inputs larger than L2 (weight banks visited in turn); flush: also rewrite a 256 MB buffer between steps")
+                    help="rotate: inputs larger than L2 (weight banks visited in turn); flush: also rewrite a 256 MB buffer between blocks")
     ap.add_argument("--banks", type=int, default=0, help="resident weight copies visited in turn (0 = enough for 4 x L2 per cycle)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the check of the timed output against the CPU checker")
+    ap.add_argument("--no-probe", action="store_true", help="skip the tensor-pipe peak probe")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -297,143 +600,10 @@ def main() -> None:
 
     if args.impl == "reference":
         run_reference_arm(args, cfg, tokens)
-        return
-
-    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        from nerve_b200 import expert_parallel
-
-        expert_parallel.bench_main(args, cfg, tokens, METRIC, UNIT)
-        return
-
-    import torch
-
-    torch.cuda.init()
-    peaks, peak_kind = measured_peaks()
-    runner = LayerRunner(cfg, tokens, args.seed, args.expert_path, banks=args.banks)
-    # --l2 flush: additionally rewrite a 256 MB buffer between timed steps (leaves L2 full of dirty lines
-    # whose write-back then competes with the step's reads); default: the rotating weight banks alone
-    scratch = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda:0") if args.l2 == "flush" else None
-
-    def timed_steps(r, steps, warmup, sample_clocks=False):
-        for _ in range(max(warmup, r.n_banks + 1)):  # every bank's tables are resolved once before timing
-            r.step_resident()
-            r.device.synchronize()
-        sampler = ClockSampler(0) if sample_clocks else None
-        if sampler:
-            sampler.start()
-        reports = []
-        for _ in range(steps):
-            flush_l2(torch, scratch)
-            reports.append(r.step_resident())  # last_report synchronises the stream
-        clocks = sampler.stop() if sampler else None
-        return reports, clocks
-
-    def timed_block(r, steps, warmup, sample_clocks=False):
-        """The contract's timed region: exactly `steps` layer calls back to back between two CUDA events on
-        the stream they run on, a synchronise on both sides, no per-stage events inside."""
-        r.plan.set_profiling(False)
-        stream = torch.cuda.ExternalStream(r.device.stream(), device="cuda:0")
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for _ in range(max(warmup, r.n_banks + 1)):
-            r.launch_step()
-        torch.cuda.synchronize()
-        sampler = ClockSampler(0) if sample_clocks else None
-        if sampler:
-            sampler.start()
-        if scratch is not None:
-            flush_l2(torch, scratch)
-        before = r.plan.launches()
-        begin.record(stream)
-        for _ in range(steps):
-            r.launch_step()
-        end.record(stream)
-        torch.cuda.synchronize()
-        clocks = sampler.stop() if sampler else None
-        r.plan.set_profiling(True)
-        return begin.elapsed_time(end) / steps, r.plan.launches() - before, clocks
-
-    # whole-layer throughput first (no profiling events in the stream), then per-kernel times from a
-    # second pass with an event pair around each stage and each expert kernel
-    ms, launches, clocks = timed_block(runner, args.steps, args.warmup, sample_clocks=True)
-    reports, _ = timed_steps(runner, args.steps, args.warmup)
-    profiled_ms = statistics.mean(rep["total_ms"] for rep in reports)
-    gate_ms = statistics.mean(rep["gate_up_kernel_ms"] for rep in reports)
-    down_ms = statistics.mean(rep["down_kernel_ms"] for rep in reports)
-    distinct = reports[-1]["distinct_experts"]
-    value = tokens / (ms * 1e-3)
-
-    # end to end: host buffers in and out, copies inside the timed region
-    runner.plan.set_profiling(False)
-    for _ in range(max(3, runner.n_banks + 1)):
-        runner.step_host()
-    e2e_ms = []
-    for _ in range(args.steps):
-        flush_l2(torch, scratch)
-        e2e_ms.append(runner.step_host())
-    e2e_value = tokens / (statistics.mean(e2e_ms) * 1e-3)
-
-    ab = algorithmic_bytes(cfg, tokens, distinct)
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised under
-    # profiles/ (taken on this workload); other workloads have no capture and report null
-    ncu_traffic = {("gpt-oss-20b-decode", 64): {"gate_up": 289069568, "down": 146978816}}.get((args.workload, tokens))
-    if bound == "hbm":
-        achieved = ab["gate_up"] / (gate_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": ncu_traffic["gate_up"] if ncu_traffic else None,
-                    "kernel": "gate_up",
-                    "peak_kind": f"{peak_kind} STREAM-style copy",
-                    "algorithmic_bytes_per_launch": ab["gate_up"], "kernel_ms": gate_ms,
-                    "down_kernel": {"achieved": ab["down"] / (down_ms * 1e-3) / 1e9, "kernel_ms": down_ms,
-                                    "frac": ab["down"] / (down_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
-                    "layer": {"achieved": ab["layer"] / (ms * 1e-3) / 1e9, "frac": ab["layer"] / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
+    elif args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_expert_parallel(args, cfg, tokens)
     else:
-        flops_gate = 2.0 * tokens * cfg.total_k * 2 * cfg.hidden * cfg.intermediate
-        achieved = flops_gate / (gate_ms * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"] * 2.0  # FP8-rate kinds run at twice the measured bf16 rate
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": "gate_up", "mma_kind": "mxf8f6f4 (E4M3 activations x E2M1 weights)",
-                    "peak_kind": f"2 x {peak_kind} cuBLAS bf16 burst rate; against the mxf4 rate (4 x bf16) the fraction halves",
-                    "kernel_ms": gate_ms, "frac_of_mxf4_rate": achieved / (peaks["bf16_tflops"] * 4.0),
-                    "down_kernel": {"achieved": flops_gate / 2.0 / (down_ms * 1e-3) / 1e12, "kernel_ms": down_ms,
-                                    "frac": flops_gate / 2.0 / (down_ms * 1e-3) / 1e12 / peak},
-                    "layer": {"achieved": layer_flops(cfg, tokens) / (ms * 1e-3) / 1e12,
-                              "frac": layer_flops(cfg, tokens) / (ms * 1e-3) / 1e12 / peak}}
-
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp8_e4m3 x mxfp4_e2m1 -> f32", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "hidden": cfg.hidden, "intermediate": cfg.intermediate,
-                   "experts": cfg.experts, "k": cfg.total_k, "distinct_experts": distinct,
-                   "expert_path": "tcgen05" if reports[-1]["tensor_path"] else "cuda-cores",
-                   "l2": (f"inputs larger than L2: {runner.n_banks} resident weight banks visited in turn, "
-                          f"{runner.cycle_bytes / 1e6:.0f} MB of weights read between two reads of the same bytes"
-                          + ("; plus a 256 MB buffer rewritten between timed steps" if args.l2 == "flush" else "")),
-                   "parallelism": "single device"},
-        "clocks": clocks, "roofline": roofline,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": tokens * cfg.hidden * 2,
-                "d2h_bytes_per_step": tokens * cfg.hidden * 2, "ms_per_step": statistics.mean(e2e_ms)},
-        "gpu_launches": launches,
-        "stage_ms": {k: statistics.mean(rep["stage_ms"][k] for rep in reports) for k in reports[-1]["stage_ms"]},
-        "profiled_ms_per_step": profiled_ms,
-    }
-
-    if not args.no_extra and args.workload == "gpt-oss-20b-decode":
-        extra = {}
-        for t in (1, 8, 32):
-            r = LayerRunner(cfg, t, args.seed, args.expert_path, banks=args.banks)
-            t_ms, _, _ = timed_block(r, max(5, args.steps // 2), 3)
-            reps, _ = timed_steps(r, max(5, args.steps // 2), 3)
-            d = reps[-1]["distinct_experts"]
-            b = algorithmic_bytes(cfg, t, d)
-            extra[f"decode_T{t}"] = {"tokens_per_s": t / (t_ms * 1e-3), "ms_per_step": t_ms, "distinct_experts": d,
-                                     "layer_hbm_frac": b["layer"] / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                     "gate_up_hbm_frac": b["gate_up"] / (statistics.mean(x["gate_up_kernel_ms"] for x in reps) * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-        line["extra"] = extra
-
-    if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(cfg, tokens, args.seed, args.reference_sample)
-    print(json.dumps(line))
+        run_single_gpu(args, cfg, tokens, bound)
 
 
 if __name__ == "__main__":

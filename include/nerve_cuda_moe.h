@@ -166,6 +166,12 @@ void nvmoe_plan_destroy(nvmoe_plan* plan);
 int nvmoe_plan_status(nvmoe_plan* plan, uint32_t* status_bits);
 /* Chooses the expert kernels: 0 = automatic, 1 = CUDA-core dequant-GEMV, 2 = tcgen05 grouped MMA. */
 int nvmoe_plan_set_expert_path(nvmoe_plan* plan, int path);
+/* Every wait inside the tensor-core expert kernels (on a pipeline stage, an accumulator) gives up after
+ * this many SM clock cycles, raises NVMOE_STATUS_WAIT_EXPIRED and winds the kernel down; the context
+ * stays usable and the next call starts clean. Default (and 0): 4e9 cycles, about two seconds. The
+ * counterpart of the reference's queue-progress watchdog
+ * (runtime-rs/src/vulkan_compute/queue_progress_watchdog.rs:18-60), inside the kernel. */
+int nvmoe_plan_set_wait_limit(nvmoe_plan* plan, uint64_t clock_cycles);
 /* With profiling on, nvmoe_layer brackets every stage with CUDA events (nvmoe_work_report.stage_ms),
  * the counterpart of the per-step GPU timestamps of
  * runtime-rs/src/vulkan_compute/compute_device_sequence.rs:27-190. Off by default. */
@@ -289,7 +295,8 @@ typedef struct nvmoe_layer_args {
 int nvmoe_layer(nvmoe_plan* plan, const nvmoe_layer_args* args);
 
 /* Host-buffer form of nvmoe_layer: copies `hidden` in from host memory and `output` back inside
- * the call (pinned staging owned by the plan) — the call a runtime makes per decode step. */
+ * the call (pinned staging owned by the plan) — the call a runtime makes per decode step. The wait for
+ * the result is bounded (60 s, NVMOE_ERR_TIMEOUT after that). */
 int nvmoe_layer_host(nvmoe_plan* plan, const nvmoe_layer_args* args, const void* hidden_host,
                      void* output_host);
 
@@ -312,7 +319,11 @@ typedef struct nvmoe_work_report {
     uint64_t weight_bytes_touched;
 } nvmoe_work_report;
 int nvmoe_plan_last_report(nvmoe_plan* plan, nvmoe_work_report* report);
-/* Diagnostics of the last tensor-core expert kernels: counters of CTA 0, twelve words for
+/* ---- diagnostics (unstable: not part of the drop-in surface, may change between builds) --------------
+ * The expert kernels that run by default are compiled without any of these; arming the per-CTA trace
+ * switches the plan to instantiations that carry them.
+ *
+ * Diagnostics of the last tensor-core expert kernels (valid once the trace is armed): counters of CTA 0, twelve words for
  * gate/up then twelve for down: cycles {producer wait, producer total, MMA wait-operands, MMA
  * wait-accumulator, MMA total}, stages, cycles {epilogue wait, epilogue total}, then global-timer
  * nanoseconds {kernel entry, MMA loop begin, MMA loop end, latest exit of any CTA}. Synchronises
@@ -323,8 +334,29 @@ int nvmoe_plan_debug_counters(nvmoe_plan* plan, uint64_t* out24);
  * consumed, SM id} of the most recent kernels into `out` (room for max_ctas CTAs per stage).
  * Synchronises the stream. No reference counterpart. */
 int nvmoe_plan_debug_cta_trace(nvmoe_plan* plan, uint64_t* out, uint32_t max_ctas, uint32_t* ctas);
+/* Makes CTA 0 of the gate/up tensor-core kernel leave out its first pipeline-stage arrival, so that its
+ * consumer's bounded wait runs out: the way the give-up path (nvmoe_plan_set_wait_limit) is tested
+ * without faulting or hanging anything. The call's output is incomplete and NVMOE_STATUS_WAIT_EXPIRED is
+ * raised; switch it off again for the next call. */
+int nvmoe_plan_debug_withhold_arrival(nvmoe_plan* plan, int enabled);
 /* Kernels launched through this plan since it was created. */
 uint64_t nvmoe_plan_launch_count(const nvmoe_plan* plan);
+
+/* Measured peak of the tensor-core instruction the expert kernels issue (tcgen05.mma kind::mxf8f6f4,
+ * block-scaled, 128 x n_tile x 32 per instruction, E2M1 weights x E4M3 activations): one CTA per SM
+ * issues k_groups x 8 instructions on operands resident in shared memory, alternating two accumulators
+ * as the gate/up kernel does. tflops is the rate over all SMs (CUDA events, best of two runs): the
+ * denominator of the tensor-bound roofline for the instruction kind that runs. No reference counterpart. */
+typedef struct nvmoe_mma_probe {
+    uint32_t n_tile;
+    uint32_t ctas;
+    uint64_t mmas_per_cta;
+    float elapsed_ms;
+    double cycles_per_mma;        /* slowest CTA's cycles / instructions issued */
+    double tflops;
+    double sm_clock_mhz_nominal;  /* the device's advertised SM clock, for reading cycles_per_mma */
+} nvmoe_mma_probe;
+int nvmoe_probe_mma_rate(nvmoe_device* device, uint32_t n_tile, uint32_t k_groups, nvmoe_mma_probe* out);
 
 /*
  * Expert-parallel exchange, the all-to-all form of the reference's expert-range ownership

@@ -73,6 +73,13 @@ class CudaComputeDevice:
     def synchronize(self, timeout_ns: int = 60_000_000_000) -> None:
         self._check(self._lib.nvmoe_sync(self._h, timeout_ns))
 
+    def probe_mma_rate(self, n_tile: int = 128, k_groups: int = 8192) -> dict:
+        """Measured rate of the block-scaled tensor-core instruction of the expert kernels over all SMs."""
+        r = capi.MmaProbe()
+        self._check(self._lib.nvmoe_probe_mma_rate(self._h, n_tile, k_groups, ctypes.byref(r)))
+        return {"n_tile": r.n_tile, "ctas": r.ctas, "mmas_per_cta": r.mmas_per_cta, "elapsed_ms": r.elapsed_ms,
+                "cycles_per_mma": r.cycles_per_mma, "tflops": r.tflops, "sm_clock_mhz_nominal": r.sm_clock_mhz_nominal}
+
     def close(self) -> None:
         if self._h:
             self._lib.nvmoe_device_close(self._h)
@@ -156,24 +163,38 @@ class ExpertBank:
     down_addresses: ResidentBuffer
     down_slots: ResidentBuffer
 
+    def destroy(self) -> None:
+        """Frees the tables and every tensor of the bank."""
+        for buf in (self.gate_up_addresses, self.gate_up_slots, self.down_addresses, self.down_slots, *self.resources):
+            buf.destroy()
+        self.resources = []
+
     @staticmethod
     def upload(device: CudaComputeDevice, w1, s1, w3, s3, w2, s2, present=None) -> "ExpertBank":
         n = len(w1)
-        present = list(range(n)) if present is None else list(present)
-        keep, gres, dres = [], [], []
+        present = set(range(n) if present is None else present)
+        per_expert = [[device.resident_buffer_from(t[e]) for t in (w1, s1, w3, s3, w2, s2)] if e in present else None
+                      for e in range(n)]
+        return ExpertBank.from_resident(device, per_expert)
+
+    @staticmethod
+    def from_resident(device: CudaComputeDevice, per_expert: list) -> "ExpertBank":
+        """Tables over tensors that are already resident: `per_expert[e]` is the expert's six buffers
+        (w1, w1 scales, w3, w3 scales, w2, w2 scales) or None for an expert this device does not hold."""
+        n = len(per_expert)
+        gres, dres = [], []
         gslots = np.full(n * 4, UNBOUND_PARAMETER_SLOT, dtype=np.uint32)
         dslots = np.full(n * 2, UNBOUND_PARAMETER_SLOT, dtype=np.uint32)
-        for e in present:
-            for j, arr in enumerate((w1[e], s1[e], w3[e], s3[e])):
-                buf = device.resident_buffer_from(arr)
+        for e, tensors in enumerate(per_expert):
+            if tensors is None:
+                continue
+            for j, buf in enumerate(tensors[:4]):
                 gslots[e * 4 + j] = len(gres)
                 gres.append(buf)
-            for j, arr in enumerate((w2[e], s2[e])):
-                buf = device.resident_buffer_from(arr)
+            for j, buf in enumerate(tensors[4:]):
                 dslots[e * 2 + j] = len(dres)
                 dres.append(buf)
-        keep = gres + dres
-        return ExpertBank(keep, address_table(device, gres), device.resident_buffer_from(gslots),
+        return ExpertBank(gres + dres, address_table(device, gres), device.resident_buffer_from(gslots),
                           address_table(device, dres), device.resident_buffer_from(dslots))
 
 
@@ -275,6 +296,14 @@ class MoePlan:
     def set_expert_path(self, path: int) -> None:
         """0 automatic, 1 CUDA-core dequant-GEMV, 2 tcgen05 grouped MMA."""
         self._call("nvmoe_plan_set_expert_path", path)
+
+    def set_wait_limit(self, clock_cycles: int) -> None:
+        """SM clock cycles after which a bounded wait inside the tensor-core kernels gives up (0 = default)."""
+        self._call("nvmoe_plan_set_wait_limit", clock_cycles)
+
+    def debug_withhold_arrival(self, enabled: bool) -> None:
+        """Test aid: CTA 0 of the gate/up kernel leaves out one stage arrival, so that a bounded wait runs out."""
+        self._call("nvmoe_plan_debug_withhold_arrival", int(enabled))
 
     def set_profiling(self, enabled: bool) -> None:
         self._call("nvmoe_plan_set_profiling", int(enabled))

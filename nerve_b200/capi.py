@@ -56,6 +56,13 @@ class WorkReport(ctypes.Structure):
     ]
 
 
+class MmaProbe(ctypes.Structure):
+    _fields_ = [
+        ("n_tile", c_uint32), ("ctas", c_uint32), ("mmas_per_cta", c_uint64), ("elapsed_ms", c_float),
+        ("cycles_per_mma", ctypes.c_double), ("tflops", ctypes.c_double), ("sm_clock_mhz_nominal", ctypes.c_double),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 PROTOTYPES = {
     "nvmoe_geometry_default": (None, [POINTER(Geometry), c_uint32, c_uint32, c_uint32, c_uint32]),
@@ -76,6 +83,8 @@ PROTOTYPES = {
     "nvmoe_plan_status": (c_int, [c_void_p, POINTER(c_uint32)]),
     "nvmoe_plan_set_expert_path": (c_int, [c_void_p, c_int]),
     "nvmoe_plan_set_profiling": (c_int, [c_void_p, c_int]),
+    "nvmoe_plan_set_wait_limit": (c_int, [c_void_p, c_uint64]),
+    "nvmoe_plan_debug_withhold_arrival": (c_int, [c_void_p, c_int]),
     "nvmoe_router_linear": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route_compact": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -93,6 +102,7 @@ PROTOTYPES = {
     "nvmoe_plan_launch_count": (c_uint64, [c_void_p]),
     "nvmoe_plan_debug_cta_trace": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p]),
     "nvmoe_plan_debug_counters": (c_int, [c_void_p, POINTER(c_uint64)]),
+    "nvmoe_probe_mma_rate": (c_int, [c_void_p, c_uint32, c_uint32, POINTER(MmaProbe)]),
     "nvmoe_buffer_wrap": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_void_p)]),
     "nvmoe_device_set_stream": (c_int, [c_void_p, c_void_p]),
     "nvmoe_ep_pack": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p,

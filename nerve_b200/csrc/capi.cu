@@ -111,6 +111,7 @@ struct ExpertSet {
     }
 };
 constexpr size_t kMaxExpertSets = 64;
+constexpr int kHostWaitSeconds = 60;  // how long the host-buffer layer call waits for its result
 
 enum Stage { kStageLinear, kStageRoute, kStageSchedule, kStageQuantX, kStageGateUp, kStageQuantI, kStageDown, kStageReduce, kStageCount };
 
@@ -145,6 +146,8 @@ struct nvmoe_plan {
     bool profile_stages = false;
     nvmoe_work_report report{};
     uint32_t launches = 0;
+    long long wait_cycles = 4000000000ll;  // limit of the bounded in-kernel waits of the tensor path (about 2 s)
+    uint32_t debug_flags = 0;
 };
 
 namespace {
@@ -549,6 +552,20 @@ int nvmoe_plan_set_expert_path(nvmoe_plan* p, int path) {
     return NVMOE_OK;
 }
 
+int nvmoe_plan_set_wait_limit(nvmoe_plan* p, uint64_t clock_cycles) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    if (clock_cycles > (1ull << 40)) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "wait limit of %llu cycles is beyond 2^40",
+                                               (unsigned long long)clock_cycles);
+    p->wait_cycles = clock_cycles ? (long long)clock_cycles : 4000000000ll;
+    return NVMOE_OK;
+}
+
+int nvmoe_plan_debug_withhold_arrival(nvmoe_plan* p, int enabled) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    p->debug_flags = enabled ? (p->debug_flags | 1u) : (p->debug_flags & ~1u);
+    return NVMOE_OK;
+}
+
 int nvmoe_plan_set_profiling(nvmoe_plan* p, int enabled) {
     if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
     p->profile_stages = enabled != 0;
@@ -842,6 +859,8 @@ static int run_experts(nvmoe_plan* p, const ExpertCall& c) {
     el.tile_list = el.tile_count + 64;
     el.tokens = T;
     el.g = g;
+    el.wait_cycles = p->wait_cycles;
+    el.debug_flags = p->debug_flags;
     if (tensor) {
         const uint32_t size_index = tc_token_tile_index(tc_token_tile_for(T, p->K, p->experts, gate_up));
         el.act_tmap = el.tmaps ? p->act_maps.as<uint8_t>() + (set * 4u + size_index) * 128u : nullptr;
@@ -1227,23 +1246,76 @@ int nvmoe_layer_host(nvmoe_plan* p, const nvmoe_layer_args* args, const void* hi
     NVMOE_TRY(nvmoe_layer(p, &local));
     NVMOE_CUDA(d, cudaMemcpyAsync(direct_out ? output_host : p->pinned_out, p->output_dev.ptr, bytes, cudaMemcpyDeviceToHost,
                                   d->stream));
-    // the caller waits for this result: poll for it (a decode step is over in well under a millisecond; a
-    // blocking wait would add the wake-up of a sleeping thread to every step), then fall back to a blocking wait
+    // The caller waits for this result. A decode step is over in well under a millisecond, so poll for it
+    // first (a blocking wait would add the wake-up of a sleeping thread to every step); after two
+    // milliseconds yield the core between polls; and give up after kHostWaitSeconds, like nvmoe_sync.
     NVMOE_CUDA(d, cudaEventRecord(d->sync_event, d->stream));
     {
-        const auto give_up = std::chrono::steady_clock::now() + std::chrono::milliseconds(20);
-        cudaError_t q;
-        while ((q = cudaEventQuery(d->sync_event)) == cudaErrorNotReady && std::chrono::steady_clock::now() < give_up) {
+        const auto start = std::chrono::steady_clock::now();
+        const auto spin_until = start + std::chrono::milliseconds(2);
+        const auto give_up = start + std::chrono::seconds(kHostWaitSeconds);
+        for (;;) {
+            const cudaError_t q = cudaEventQuery(d->sync_event);
+            if (q == cudaSuccess) break;
+            if (q != cudaErrorNotReady) return fail(d, NVMOE_ERR_CUDA, "device failed while waiting: %s", cudaGetErrorString(q));
+            const auto now = std::chrono::steady_clock::now();
+            if (now >= give_up)
+                return fail(d, NVMOE_ERR_TIMEOUT, "the layer did not finish within %d s", kHostWaitSeconds);
+            if (now >= spin_until) std::this_thread::sleep_for(std::chrono::microseconds(50));
         }
-        if (q != cudaSuccess && q != cudaErrorNotReady)
-            return fail(d, NVMOE_ERR_CUDA, "device failed while waiting: %s", cudaGetErrorString(q));
     }
-    NVMOE_CUDA(d, cudaStreamSynchronize(d->stream));
     if (!direct_out) std::memcpy(output_host, p->pinned_out, bytes);
     return NVMOE_OK;
 }
 
 uint64_t nvmoe_plan_launch_count(const nvmoe_plan* p) { return p ? p->launches : 0u; }
+
+int nvmoe_probe_mma_rate(nvmoe_device* d, uint32_t n_tile, uint32_t k_groups, nvmoe_mma_probe* out) {
+    if (!d || !out) return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "null device or result pointer");
+    if (n_tile < 16u || n_tile > 128u || n_tile % 16u || k_groups == 0u || k_groups > (1u << 20))
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "probe: token tile %u (16..128 by 16) or %u K groups (1..2^20) out of range",
+                    n_tile, k_groups);
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    int sms = 0;
+    NVMOE_CUDA(d, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->ordinal));
+    int khz = 0;
+    NVMOE_CUDA(d, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, d->ordinal));
+    DeviceArray scratch;
+    NVMOE_CUDA(d, scratch.ensure((size_t)sms * sizeof(long long) + 64u));
+    uint32_t* status = reinterpret_cast<uint32_t*>(scratch.as<long long>() + sms);
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    cudaError_t err = cudaMemsetAsync(scratch.ptr, 0, scratch.bytes, d->stream);
+    for (int i = 0; i < 2 && err == cudaSuccess; i++) err = cudaEventCreate(&ev[i]);
+    float best_ms = 0.0f;
+    for (int run = 0; run < 3 && err == cudaSuccess; run++) {  // the first run also loads the kernel
+        err = cudaEventRecord(ev[0], d->stream);
+        if (err == cudaSuccess) err = launch_mma_rate_probe(n_tile, k_groups, (uint32_t)sms, scratch.as<long long>(), status, d->stream);
+        if (err == cudaSuccess) err = cudaEventRecord(ev[1], d->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);
+        float ms = 0.0f;
+        if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, ev[0], ev[1]);
+        if (run > 0 && (best_ms == 0.0f || ms < best_ms)) best_ms = ms;
+    }
+    std::vector<long long> cycles((size_t)sms + 8u);
+    if (err == cudaSuccess) err = cudaMemcpy(cycles.data(), scratch.ptr, (size_t)sms * sizeof(long long) + 4u, cudaMemcpyDeviceToHost);
+    for (cudaEvent_t e : ev)
+        if (e) cudaEventDestroy(e);
+    const uint32_t raised = err == cudaSuccess ? *reinterpret_cast<uint32_t*>(cycles.data() + sms) : 0u;
+    scratch.release();
+    if (err != cudaSuccess) return fail(d, NVMOE_ERR_CUDA, "tensor-pipe probe failed: %s", cudaGetErrorString(err));
+    if (raised) return fail(d, NVMOE_ERR_DEVICE_STATUS, "tensor-pipe probe: a bounded wait gave up (status %u)", raised);
+    long long slowest = 0;
+    for (int i = 0; i < sms; i++) slowest = cycles[i] > slowest ? cycles[i] : slowest;
+    const double mmas = (double)k_groups * 8.0;  // four K steps into each of two accumulators per group
+    out->n_tile = n_tile;
+    out->ctas = (uint32_t)sms;
+    out->mmas_per_cta = (uint64_t)mmas;
+    out->elapsed_ms = best_ms;
+    out->cycles_per_mma = (double)slowest / mmas;
+    out->tflops = 2.0 * 128.0 * n_tile * 32.0 * mmas * sms / ((double)best_ms * 1e-3) / 1e12;
+    out->sm_clock_mhz_nominal = (double)khz / 1e3;
+    return NVMOE_OK;
+}
 
 int nvmoe_plan_debug_counters(nvmoe_plan* p, uint64_t* out24) {
     uint64_t* out8 = out24;

@@ -209,11 +209,18 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     uint32_t* tile_list;         // tensor path scratch: routes / 16 + experts + 1 words
     uint32_t* tile_count;        // tensor path scratch: one word
     uint32_t tokens;             // upper bound (max over what control may hold)
+    long long wait_cycles;       // tensor path: clock cycles after which a bounded in-kernel wait gives up
+    uint32_t debug_flags;        // tensor path: bit 0 = CTA 0 leaves out its first stage arrival (exercises the give-up path)
     nvmoe_geometry g;
 };
 void configure_simt_kernels();
 void launch_gate_up_simt(const ExpertLaunch& p, cudaStream_t stream);
 void launch_down_simt(const ExpertLaunch& p, cudaStream_t stream);
+
+// probe.cu: a run of `groups` x 8 block-scaled MMAs (128 x n_tile x 32, two alternating accumulators)
+// on every one of `ctas` CTAs; cycles[cta] = clock cycles from first issue to completion
+cudaError_t launch_mma_rate_probe(uint32_t n_tile, uint32_t groups, uint32_t ctas, long long* cycles, uint32_t* status,
+                                  cudaStream_t stream);
 
 // reduce.cu: moe_reduce_batch1_bf16. `computed` (optional, [tokens * K]) marks with 0xffffffff the routes
 // whose rows were never written: they count as zeros, so the rows need no clearing beforehand.

@@ -134,10 +134,13 @@ struct Barriers {
     uint32_t abort;
 };
 
-template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA, bool ROW_PAIR>
+// TRACE compiles the diagnostics in (cycle counters of CTA 0, per-CTA global-timer stamps): the
+// instantiation that runs unless a plan's trace was armed has none of them in its loops.
+template <bool GATE_UP, uint32_t N_TILE, bool USE_TMA, bool ROW_PAIR, bool TRACE>
 __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::kThreads), 1)
     experts_tc_kernel(ExpertLaunch p, TileList list) {
     using C = Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>;
+    const long long wait_limit = p.wait_cycles;
     constexpr uint32_t kProducerThreads = C::kProducerThreads, kRowsPerPass = C::kRowsPerPass;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -162,7 +165,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
     };
     // cycle counters of CTA 0, one writer per role (diagnostics; words 16.. of the tile-count block)
     uint64_t* trace = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(list.count) + 16) + (GATE_UP ? 0 : 12);
-    if (blockIdx.x == 0u && threadIdx.x == 0u) trace[8] = global_timer_ns();  // kernel entry of CTA 0
+    if (TRACE && blockIdx.x == 0u && threadIdx.x == 0u) trace[8] = global_timer_ns();  // kernel entry of CTA 0
 
     // ---- one-time setup ---------------------------------------------------------------------
     if (threadIdx.x == 0u) {
@@ -203,23 +206,51 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
         if (USE_TMA && lane == 0u) {
             uint32_t slot = 0u, empty_parity = 1u;
             bool alive = true;
-            for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
-                const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
-                const uint32_t m_tile = tile % m_tiles;
-                const int row0 = (int)(m_tile * C::kTileRows);
+            // What the lane needs to know about a tile. The list entry of a tile is fetched two tiles ahead and
+            // what hangs on it (the expert's offset, scale and tensor-map addresses) one tile ahead, so that the
+            // chain of dependent loads is over by the time the tile starts: a lane that stalled on it at every
+            // tile boundary would leave the memory pipe without new requests for about a microsecond per tile.
+            // (The prefetch only loads: whatever is computed from a loaded value is computed when the tile
+            // starts, because a thread stalls at the first instruction that needs a load's result.)
+            struct Meta {
+                uint32_t pair, m_tile, expert_begin;
+                const uint8_t* ts[C::kSources];
+            };
+            auto entry_of = [&](uint32_t tile) {
+                uint32_t pair = 0u;
+                if (tile < tile_count) pair = __ldg(list.tiles + tile / m_tiles);
+                return pair;
+            };
+            auto meta_of = [&](uint32_t tile, uint32_t pair, Meta& m) {
+                m.pair = pair;
+                m.m_tile = tile % m_tiles;
                 const uint32_t expert = pair >> 16;
-                const uint8_t* maps = p.tmaps + (size_t)expert * C::kSources * 128u;
+                m.expert_begin = __ldg(p.work.expert_offsets + expert);
+#pragma unroll
+                for (uint32_t src = 0; src < C::kSources; src++) m.ts[src] = p.work.experts[expert].ts[src];
+            };
+            Meta cur{}, nxt{};
+            uint32_t pair_nxt = entry_of(blockIdx.x + gridDim.x);
+            if (blockIdx.x < tile_count) meta_of(blockIdx.x, entry_of(blockIdx.x), cur);
+            // (debug) leave out the very first arrival of CTA 0: its consumer's bounded wait must then give up
+            bool withhold = (p.debug_flags & 1u) != 0u && blockIdx.x == 0u;
+            uint32_t stage_it = 0u;  // stages this lane has gone through (stage n used slot n % kStages, phase n / kStages)
+            for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x) {
+                const uint32_t pair_nxt2 = entry_of(tile + 2u * gridDim.x);
+                if (tile + gridDim.x < tile_count) meta_of(tile + gridDim.x, pair_nxt, nxt);
+                const uint32_t m_tile = cur.m_tile;
+                const int row0 = (int)(m_tile * C::kTileRows);
+                const uint8_t* maps = p.tmaps + (size_t)(cur.pair >> 16) * C::kSources * 128u;
                 // first operand row of this token tile in the expert-grouped activation matrix
-                const int token0 = (int)(__ldg(p.work.expert_offsets + expert) + (pair & 0xffffu) * N_TILE);
-                const ExpertPtrs* ptrs = p.work.experts + expert;
+                const int token0 = (int)(cur.expert_begin + (cur.pair & 0xffffu) * N_TILE);
                 const uint8_t* scale_blocks[C::kMatrices];
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                    scale_blocks[mx] = ptrs->ts[C::source_of(mx)] + (size_t)scale_tile(m_tile, mx) * k_blocks * kScaleBlockBytes;
+                    scale_blocks[mx] = cur.ts[C::source_of(mx)] + (size_t)scale_tile(m_tile, mx) * k_blocks * kScaleBlockBytes;
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kSources; mx++) tensormap_acquire(maps + mx * 128u);
                 for (uint32_t ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag)) {
+                    if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag, wait_limit)) {
                         alive = false;
                         break;
                     }
@@ -230,6 +261,9 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                         whole += ((ks * C::kSub + sub + 1u) * kBlockK <= k_dim) ? 1u : 0u;
                         present += (ks * C::kSub + sub < k_blocks) ? 1u : 0u;
                     }
+                    if (withhold) {
+                        withhold = false;
+                    } else {
                     // token rows (zeros past the edge of K) and weight scale blocks of every K block present
                     const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
                     mbar_arrive_expect_tx(&bars->full[slot], whole * C::kMatrices * kTmaBoxBytes +
@@ -249,10 +283,25 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                             bulk_copy_g2s(block + C::kMatrices * kATileBytes + C::kBTileBytes + mx * kScaleBlockBytes,
                                           scale_blocks[mx] + (size_t)kb * kScaleBlockBytes, kScaleBlockBytes, &bars->full[slot]);
                     }
+                    }
+                    stage_it++;
                     if (++slot == C::kStages) {
                         slot = 0u;
                         empty_parity ^= 1u;
                     }
+                }
+                cur = nxt;
+                pair_nxt = pair_nxt2;
+            }
+            if (!alive) {
+                // The pipeline was aborted with copies of this lane possibly still on their way into shared
+                // memory: the CTA must not retire under them. Wait, bounded, on the stage barriers of the last
+                // round this lane armed; a barrier that also lacks an aborted role's arrivals never completes,
+                // and the time spent on it is the grace period instead.
+                const uint32_t rounds = stage_it < C::kStages ? stage_it : C::kStages;
+                for (uint32_t back = 1u; back <= rounds; back++) {
+                    const uint32_t nth = stage_it - back;
+                    mbar_wait_winddown(&bars->full[nth % C::kStages], (nth / C::kStages) & 1u, kWinddownCycles / C::kStages);
                 }
             }
         }
@@ -293,7 +342,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
         };
         uint32_t it = 0u, slot = 0u, empty_parity = 1u;  // a fresh barrier passes a wait on parity 1
         long long trace_wait = 0;
-        const long long trace_begin = clock64();
+        const long long trace_begin = TRACE ? clock64() : 0;
         const uint32_t my_dst = swizzle128_offset(my_r, my_c);
         bool alive = true;
         Meta cur, nxt;
@@ -311,12 +360,12 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             }
             const size_t row_step = (size_t)kRowsPerPass * row_bytes;
             for (uint32_t ks = 0; ks < k_stages; ks++, it++) {
-                const long long w0 = clock64();
-                if (!mbar_wait_warp(&bars->empty[slot], empty_parity, abort_flag)) {
+                const long long w0 = TRACE ? clock64() : 0;
+                if (!mbar_wait_warp(&bars->empty[slot], empty_parity, abort_flag, wait_limit)) {
                     alive = false;
                     break;
                 }
-                trace_wait += clock64() - w0;
+                if (TRACE) trace_wait += clock64() - w0;
 #pragma unroll
                 for (uint32_t sub = 0; sub < C::kSub; sub++) {
                 const uint32_t kb = ks * C::kSub + sub;
@@ -388,7 +437,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             cur = nxt;
         }
         cp_async_wait_all();  // nothing of this thread may still be landing when the CTA retires
-        if (blockIdx.x == 0u && pt == 0u) {
+        if (TRACE && blockIdx.x == 0u && pt == 0u) {
             trace[0] = (uint64_t)trace_wait;                    // producer: cycles waiting for a free stage
             trace[1] = (uint64_t)(clock64() - trace_begin);     // producer: cycles in its loop
         }
@@ -410,23 +459,23 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             uint32_t it = 0u, acc_it = 0u, slot = 0u, full_parity = 0u;
             bool alive = true;
             long long trace_full = 0, trace_acc = 0;
-            const long long trace_begin = clock64();
-            if (blockIdx.x == 0u) trace[9] = global_timer_ns();  // MMA loop begins
-            const uint64_t cta_begin = p.cta_trace ? global_timer_ns() : 0u;
+            const long long trace_begin = TRACE ? clock64() : 0;
+            if (TRACE && blockIdx.x == 0u) trace[9] = global_timer_ns();  // MMA loop begins
+            const uint64_t cta_begin = (TRACE && p.cta_trace) ? global_timer_ns() : 0u;
             for (uint32_t tile = blockIdx.x; tile < tile_count && alive; tile += gridDim.x, acc_it++) {
                 const uint32_t acc = acc_it % C::kAccStages;
-                const long long a0 = clock64();
-                if (!mbar_wait(&bars->acc_empty[acc], ((acc_it / C::kAccStages) & 1u) ^ 1u, abort_flag)) break;
-                trace_acc += clock64() - a0;
+                const long long a0 = TRACE ? clock64() : 0;
+                if (!mbar_wait(&bars->acc_empty[acc], ((acc_it / C::kAccStages) & 1u) ^ 1u, abort_flag, wait_limit)) break;
+                if (TRACE) trace_acc += clock64() - a0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccColumns;
                 for (uint32_t ks = 0; ks < k_stages; ks++, it++) {
-                    const long long f0 = clock64();
-                    if (!mbar_wait(&bars->full[slot], full_parity, abort_flag)) {
+                    const long long f0 = TRACE ? clock64() : 0;
+                    if (!mbar_wait(&bars->full[slot], full_parity, abort_flag, wait_limit)) {
                         alive = false;
                         break;
                     }
-                    trace_full += clock64() - f0;
+                    if (TRACE) trace_full += clock64() - f0;
                     tc_fence_after();
 #pragma unroll
                     for (uint32_t sub = 0; sub < C::kSub; sub++) {
@@ -459,10 +508,12 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 }
                 if (alive) tc_commit(&bars->acc_full[acc]);
             }
-            // nothing of this CTA may still be using tensor memory when it is released
+            // Nothing of this CTA may still be reading shared memory or using tensor memory when they are
+            // released: the commit arrives once every MMA and scale copy issued above has retired. This wait has
+            // its own limit and does not look at the abort flag, which is already set on the give-up path.
             tc_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0u, abort_flag);
-            if (p.cta_trace) {  // per-CTA diagnostics: loop begin, loop end, stages, SM id
+            mbar_wait_winddown(&bars->drain, 0u, kWinddownCycles);
+            if (TRACE && p.cta_trace) {  // per-CTA diagnostics: loop begin, loop end, stages, SM id
                 uint32_t smid;
                 asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
                 uint64_t* mine = p.cta_trace + (size_t)((GATE_UP ? 0u : gridDim.x) + blockIdx.x) * 4u;
@@ -471,7 +522,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 mine[2] = it;
                 mine[3] = smid;
             }
-            if (blockIdx.x == 0u) {
+            if (TRACE && blockIdx.x == 0u) {
                 trace[2] = (uint64_t)trace_full;                 // MMA thread: cycles waiting for operands
                 trace[3] = (uint64_t)trace_acc;                  // MMA thread: cycles waiting for a free accumulator
                 trace[4] = (uint64_t)(clock64() - trace_begin);  // MMA thread: cycles in its loop
@@ -487,7 +538,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
         const uint32_t frame_words = K * (I / 2u) + K;
         uint32_t acc_it = 0u;
         long long trace_epi_wait = 0;
-        const long long trace_begin = clock64();
+        const long long trace_begin = TRACE ? clock64() : 0;
         for (uint32_t tile = blockIdx.x; tile < tile_count; tile += gridDim.x, acc_it++) {
             const uint32_t pair = list.tiles[tile / m_tiles];
             const uint32_t m_tile = tile % m_tiles;
@@ -496,9 +547,9 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             const uint32_t first = e_begin + n_tile * N_TILE;
             const uint32_t valid = min(N_TILE, e_end - first);
             const uint32_t acc = acc_it % C::kAccStages;
-            const long long e0 = clock64();
-            if (!mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag)) break;
-            trace_epi_wait += clock64() - e0;
+            const long long e0 = TRACE ? clock64() : 0;
+            if (!mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag, wait_limit)) break;
+            if (TRACE) trace_epi_wait += clock64() - e0;
             tc_fence_after();
             const uint32_t row = m_tile * C::kTileRows + quad * 32u + lane;  // (with row pairs: of the first half)
             const bool row_ok = row < out_rows;
@@ -604,7 +655,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[acc]);
         }
-        if (blockIdx.x == 0u && threadIdx.x == 0u) {
+        if (TRACE && blockIdx.x == 0u && threadIdx.x == 0u) {
             trace[6] = (uint64_t)trace_epi_wait;                 // epilogue: cycles waiting for an accumulator
             trace[7] = (uint64_t)(clock64() - trace_begin);      // epilogue: cycles in its loop
         }
@@ -618,7 +669,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
         tmem_dealloc(tmem_base, C::kTmemColumns);
     }
     // latest exit over all CTAs (the timer only grows, so the last launch wins)
-    if (threadIdx.x == 0u) atomicMax(reinterpret_cast<unsigned long long*>(trace + 11), (unsigned long long)global_timer_ns());
+    if (TRACE && threadIdx.x == 0u) atomicMax(reinterpret_cast<unsigned long long*>(trace + 11), (unsigned long long)global_timer_ns());
 }
 
 // Re-tiles the packaged [rows][cols/32] scale bytes of one expert matrix into 512-byte blocks, one
@@ -685,9 +736,14 @@ void launch_n(const ExpertLaunch& p, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (g_sm_count[dev & 15] == 0) cudaDeviceGetAttribute(&g_sm_count[dev & 15], cudaDevAttrMultiProcessorCount, dev);
-    launch_chained(experts_tc_kernel<GATE_UP, N_TILE, USE_TMA, row_pair<GATE_UP, N_TILE>()>, dim3(g_sm_count[dev & 15]),
-                   dim3(C::kThreads), C::kSmemBytes, stream,
-        p, TileList{p.tile_list, p.tile_count});
+    // the traced instantiation only when a plan's trace was armed (and only for the TMA form)
+    if (USE_TMA && p.cta_trace != nullptr) {
+        launch_chained(experts_tc_kernel<GATE_UP, N_TILE, USE_TMA, row_pair<GATE_UP, N_TILE>(), USE_TMA>, dim3(g_sm_count[dev & 15]),
+                       dim3(C::kThreads), C::kSmemBytes, stream, p, TileList{p.tile_list, p.tile_count});
+    } else {
+        launch_chained(experts_tc_kernel<GATE_UP, N_TILE, USE_TMA, row_pair<GATE_UP, N_TILE>(), false>, dim3(g_sm_count[dev & 15]),
+                       dim3(C::kThreads), C::kSmemBytes, stream, p, TileList{p.tile_list, p.tile_count});
+    }
 }
 
 template <bool GATE_UP>
@@ -714,9 +770,11 @@ void launch(const ExpertLaunch& p, cudaStream_t stream) {
 template <bool GATE_UP, uint32_t N_TILE>
 void configure_one() {
     constexpr bool kPair = row_pair<GATE_UP, N_TILE>();
-    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, true, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, true, kPair, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)Config<GATE_UP, N_TILE, true, kPair>::kSmemBytes);
-    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, false, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, true, kPair, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Config<GATE_UP, N_TILE, true, kPair>::kSmemBytes);
+    cudaFuncSetAttribute(experts_tc_kernel<GATE_UP, N_TILE, false, kPair, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)Config<GATE_UP, N_TILE, false, kPair>::kSmemBytes);
 }
 

@@ -53,16 +53,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` (shared memory) lets one role tell the others that it gave up, so
 // that a broken pipeline unwinds in one timeout instead of one per role.  Returns false when the
-// wait expired or was aborted.
-constexpr long long kWaitCycles = 4000000000ll;  // about two seconds at B200 clocks
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// wait expired (after `limit` clock cycles) or was aborted.
+constexpr long long kDefaultWaitCycles = 4000000000ll;  // about two seconds at B200 clocks
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
         for (int i = 0; i < 64; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - start > kWaitCycles) {
+        if (clock64() - start > limit) {
             *abort_flag = 1u;
             return false;
         }
@@ -71,12 +71,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // The same wait for a whole warp: one lane polls, the verdict is shared, so that a waiting warp
 // costs one polling thread instead of thirty-two.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, long long limit) {
     uint32_t ok = 0u;
-    if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
+    if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag, limit) ? 1u : 0u;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     return ok != 0u;
 }
+
+// Wind-down wait: for a role that is leaving after the pipeline was aborted and must first see what it
+// has in flight (bulk copies, tensor-core operations) finish.  It ignores the abort flag, which is set
+// by then, and gives up after `limit` cycles on its own; what it waits for completes within
+// microseconds unless the barrier also counts arrivals that an aborted role will never make, in which
+// case the time spent here is itself the grace period for the copies.
+__device__ __forceinline__ bool mbar_wait_winddown(uint64_t* bar, uint32_t parity, long long limit) {
+    const long long start = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - start > limit) return false;
+    }
+}
+constexpr long long kWinddownCycles = 4000000ll;  // about two milliseconds
 
 // ---- generic-proxy staging into shared memory ---------------------------------------------------
 

@@ -147,7 +147,8 @@ class ExpertParallelLayer:
         import torch
 
         from . import synthetic
-        from .backend import CudaComputeDevice, ExpertBank, MoePlan, ResidentBuffer, geometry_from_config
+        from .backend import CudaComputeDevice, MoePlan, ResidentBuffer
+        from .resident_layer import upload_expert_banks
 
         self.torch = torch
         self.cfg, self.rank, self.world, self.tokens = cfg, rank, world, tokens_per_rank
@@ -179,21 +180,9 @@ class ExpertParallelLayer:
         local = slice(rank * T, (rank + 1) * T)
         self.hidden_host = np.ascontiguousarray(case.hidden[local])
         mine = owned_experts(self.owner, rank)
-        empty = [None] * cfg.total_experts
-        w = {k: list(empty) for k in ("w1", "s1", "w3", "s3", "w2", "s2")}
-        I = cfg.intermediate
-        for e in mine:
-            g = synthetic._stream(seed, f"expert{e}")
-            w["w1"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
-            w["s1"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
-            w["w3"][e] = g.integers(0, 256, (I, H // 2), dtype=np.uint8)
-            w["s3"][e] = g.integers(121, 128, (I, H // 32), dtype=np.uint8)
-            w["w2"][e] = g.integers(0, 256, (H, I // 2), dtype=np.uint8)
-            w["s2"][e] = g.integers(121, 128, (H, I // 32), dtype=np.uint8)
         # `banks` resident copies of this rank's experts, used in turn (a benchmark's way of keeping the
         # weights of a step out of L2, as the other layers of a model would)
-        self.banks = [ExpertBank.upload(self.device, w["w1"], w["s1"], w["w3"], w["s3"], w["w2"], w["s2"], present=mine)
-                      for _ in range(max(1, banks))]
+        self.banks = upload_expert_banks(self.device, cfg, seed, set(mine), max(1, banks))
         self.bank = self.banks[0]
         self.turn = 0
         self.home = MoePlan.for_config(self.device, cfg, T)
@@ -335,111 +324,3 @@ class ExpertParallelLayer:
     def output(self) -> np.ndarray:
         self.torch.cuda.synchronize()
         return self.t_output.cpu().numpy().view(np.uint16)
-
-
-def bench_main(args, cfg, tokens, metric, unit):
-    """bench.py --gpus N: the layer expert-sharded over N ranks, tokens per rank fixed (weak scaling)."""
-    import json
-    import statistics
-
-    import torch
-    import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", str(rank)))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    # enough resident copies of this rank's experts that a step's weights were last read 4 x L2 ago
-    per_expert = 3 * cfg.hidden * cfg.intermediate * 17 // 32
-    owned = cfg.experts // world + cfg.always_count
-    touched = max(1, min(tokens * world * cfg.total_k, owned)) * per_expert
-    banks = getattr(args, "banks", 0) or max(2, min(8, -(-4 * 126 * 1024 * 1024 // touched)))
-    layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks,
-                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"))
-    for _ in range(max(args.warmup, 3, banks + 1)):
-        layer.step(dist)
-    torch.cuda.synchronize()
-    dist.barrier()
-    times = []
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = None
-    if rank == 0:
-        import sys
-        from pathlib import Path
-
-        sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
-        from bench import ClockSampler
-
-        sampler = ClockSampler(local)
-        sampler.start()
-    # exactly `steps` steps back to back between two events on the stream they run on, a barrier and a
-    # synchronise on both sides, the slowest rank's time
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    start.record(layer.stream)
-    for _ in range(args.steps):
-        layer.step(dist)
-    stop.record(layer.stream)
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([start.elapsed_time(stop) / args.steps], device=f"cuda:{local}")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    times.append(float(t.item()))
-    clocks = sampler.stop() if sampler else None
-    # end to end: tokens start in pinned host memory, the result is read back
-    host_in = torch.from_numpy(layer.hidden_host.view(np.int16)).pin_memory()
-    host_out = torch.empty((tokens, cfg.hidden), dtype=torch.int16).pin_memory()
-    e2e = []
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    start.record(layer.stream)
-    for _ in range(args.steps):
-        with torch.cuda.stream(layer.stream):
-            layer.t_hidden.copy_(host_in, non_blocking=True)
-            layer.step(dist)
-            host_out.copy_(layer.t_output, non_blocking=True)
-    stop.record(layer.stream)
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([start.elapsed_time(stop) / args.steps], device=f"cuda:{local}")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e.append(float(t.item()))
-    ms = statistics.mean(times)
-    if rank == 0:
-        total_tokens = tokens * world
-        line = {
-            "metric": metric, "value": total_tokens / (ms * 1e-3), "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp8_e4m3 x mxfp4_e2m1 -> f32", "data": "synthetic",
-            "config": {"workload": args.workload, "tokens_per_rank": tokens, "global_tokens": total_tokens,
-                       "hidden": cfg.hidden, "intermediate": cfg.intermediate, "experts": cfg.experts, "k": cfg.total_k,
-                       "experts_per_rank": cfg.experts // world,
-                       "parallelism": f"ep{world}: experts sharded by contiguous range, tokens data-parallel, "
-                                      "NCCL all-to-all dispatch and combine",
-                       "exchange": layer.mode,
-                       "l2": f"inputs larger than L2: {banks} resident weight banks per rank visited in turn, "
-                             f"{touched * banks / 1e6:.0f} MB of weights read between two reads of the same bytes"},
-            "clocks": clocks,
-            "e2e": {"value": total_tokens / (statistics.mean(e2e) * 1e-3), "unit": unit,
-                    "h2d_bytes_per_step": tokens * cfg.hidden * 2, "d2h_bytes_per_step": tokens * cfg.hidden * 2,
-                    "ms_per_step": statistics.mean(e2e)},
-            "gpu_launches": int(layer.home.launches() + layer.work.launches()),
-        }
-        try:
-            # whole step of one rank against the HBM copy peak: the weights of the experts it owns cross HBM once
-            # per step; the exchanges and the small kernels around them are what the fraction leaves out
-            from bench import measured_peaks
-
-            peaks, kind = measured_peaks()
-            achieved = touched / (ms * 1e-3) / 1e9
-            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "whole step, per rank",
-                                "peak_kind": f"{kind} STREAM-style copy", "algorithmic_bytes_per_launch": touched}
-        except Exception as error:  # the throughput line must not depend on this
-            line["roofline"] = None
-            line["roofline_error"] = str(error)
-        print(json.dumps(line))
-    dist.destroy_process_group()

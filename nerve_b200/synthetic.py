@@ -153,14 +153,31 @@ def make_case(cfg: MoeConfig, tokens: int, seed: int = 0, with_weights: bool = T
     case = MoeCase(cfg, tokens, seed, hidden, router_w, router_bias, select_bias)
     if with_weights:
         for e in range(cfg.total_experts):
-            g = _stream(seed, f"expert{e}")
-            case.w1.append(g.integers(0, 256, (I, H // 2), dtype=np.uint8))
-            case.s1.append(g.integers(121, 128, (I, H // 32), dtype=np.uint8))
-            case.w3.append(g.integers(0, 256, (I, H // 2), dtype=np.uint8))
-            case.s3.append(g.integers(121, 128, (I, H // 32), dtype=np.uint8))
-            case.w2.append(g.integers(0, 256, (H, I // 2), dtype=np.uint8))
-            case.s2.append(g.integers(121, 128, (H, I // 32), dtype=np.uint8))
+            for name, tensor in zip(EXPERT_TENSOR_NAMES, expert_tensors(cfg, seed, e)):
+                getattr(case, name).append(tensor)
     return case
+
+
+EXPERT_TENSOR_NAMES = ("w1", "s1", "w3", "s3", "w2", "s2")
+
+
+def expert_tensors(cfg: MoeConfig, seed: int, expert: int) -> tuple:
+    """The six packaged tensors (w1, s1, w3, s3, w2, s2) of one expert, drawn from that expert's own
+    sub-stream: any subset of the experts can be generated, in any order, and always holds the same bytes."""
+    H, I = cfg.hidden, cfg.intermediate
+    g = _stream(seed, f"expert{expert}")
+    return (g.integers(0, 256, (I, H // 2), dtype=np.uint8), g.integers(121, 128, (I, H // 32), dtype=np.uint8),
+            g.integers(0, 256, (I, H // 2), dtype=np.uint8), g.integers(121, 128, (I, H // 32), dtype=np.uint8),
+            g.integers(0, 256, (H, I // 2), dtype=np.uint8), g.integers(121, 128, (H, I // 32), dtype=np.uint8))
+
+
+def expert_tensor_lists(cfg: MoeConfig, seed: int, experts, placeholder=None) -> dict:
+    """name -> list over all resources, holding the tensors of `experts` and `placeholder` elsewhere."""
+    w = {k: [placeholder] * cfg.total_experts for k in EXPERT_TENSOR_NAMES}
+    for e in experts:
+        for name, tensor in zip(EXPERT_TENSOR_NAMES, expert_tensors(cfg, seed, e)):
+            w[name][e] = tensor
+    return w
 
 
 def expert_histogram(routes: np.ndarray, total_experts: int) -> np.ndarray:

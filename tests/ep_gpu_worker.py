@@ -15,8 +15,8 @@ def main() -> int:
     import torch
     import torch.distributed as dist
 
-    from bench import LayerRunner
     from nerve_b200 import synthetic
+    from nerve_b200.resident_layer import LayerRunner
     from nerve_b200.expert_parallel import ExpertParallelLayer
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])

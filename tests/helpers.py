@@ -1,10 +1,14 @@
 """Shared plumbing of the parity tests: one synthetic case on the device and in the checker."""
 from __future__ import annotations
 
+import json
+from pathlib import Path
+
 import numpy as np
 
 from nerve_b200 import synthetic
 from oracle import moe_oracle as mo
+from oracle import sampled
 
 
 router_params = mo.router_params_from
@@ -25,27 +29,30 @@ def oracle_layer(case: synthetic.MoeCase, tier: int = 1, expert_start: int = 0, 
     return {"logits": logits, "output": out, "routes": routes, "expert_outputs": outputs, "intermediates": inter}
 
 
-def error_metrics(got_bf16: np.ndarray, want_bf16: np.ndarray) -> dict:
-    g = mo.bf16_to_f32(got_bf16).astype(np.float64).reshape(-1)
-    w = mo.bf16_to_f32(want_bf16).astype(np.float64).reshape(-1)
-    diff = np.abs(g - w)
-    scale = max(np.abs(w).max(), 1e-30)
-    return {
-        "max_abs": float(diff.max()),
-        "max_abs_over_peak": float(diff.max() / scale),
-        "rel_l2": float(np.sqrt((diff ** 2).sum()) / max(np.sqrt((w ** 2).sum()), 1e-30)),
-        "mismatched": int((got_bf16.reshape(-1) != want_bf16.reshape(-1)).sum()),
-        "count": int(w.size),
-    }
-
+error_metrics = sampled.error_metrics
 
 # north_star tolerance for bf16 outputs against the f64-accumulated dequantised reference on the
-# same quantised operands: rel-L2 <= 5e-3 and max-abs <= 2e-2 of the output's peak magnitude
-REL_L2_TOL = 5e-3
-MAX_ABS_TOL = 2e-2
+# same quantised operands: rel-L2 <= 5e-3 and max-abs <= 2e-2 of the output's peak magnitude (the
+# absolute max-abs is recorded beside it; see oracle/sampled.py for why the relative reading is gated)
+REL_L2_TOL = sampled.REL_L2_TOL
+MAX_ABS_TOL = sampled.MAX_ABS_OVER_PEAK_TOL
 
 
 def assert_close(got_bf16, want_bf16, what=""):
     m = error_metrics(got_bf16, want_bf16)
-    assert m["rel_l2"] <= REL_L2_TOL and m["max_abs_over_peak"] <= MAX_ABS_TOL, (what, m)
+    assert sampled.within_tolerance(m), (what, m)
+    if what:
+        record_metrics(what, m)
     return m
+
+
+def record_metrics(case_id: str, metrics: dict) -> None:
+    """Appends the measured error of one parity case to gpurun_out/parity_metrics.jsonl (the folder a GPU
+    run brings back), so that the figures behind a green run can be kept."""
+    folder = Path(__file__).resolve().parent.parent / "gpurun_out"
+    try:
+        folder.mkdir(exist_ok=True)
+        with open(folder / "parity_metrics.jsonl", "a") as f:
+            f.write(json.dumps({"case": case_id, **metrics}) + "\n")
+    except OSError:
+        pass

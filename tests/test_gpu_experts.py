@@ -384,3 +384,33 @@ def test_preselected_routes_form_reproduces_the_layer(device, path, tokens):
         assert not got_rows[unused].any(), "slots without a route must come back as zero rows"
     plan.destroy()
     work.destroy()
+
+
+def test_bounded_wait_gives_up_and_the_plan_recovers(device):
+    """A wait inside the tensor-core kernel that nothing will ever satisfy (CTA 0 leaves out one stage
+    arrival) runs out after the plan's wait limit: the kernel returns, the status word says so, the
+    context stays usable and the next ordinary call on the same plan is bit-identical to the one before.
+    Nothing here faults, traps or hangs: the wait is bounded and simply expires."""
+    cfg = synthetic.CONFIGS["tiny"]
+    tokens = 64
+    case = synthetic.make_case(cfg, tokens, seed=3)
+    plan = make_plan(device, cfg, tokens, 2)
+    bank = ExpertBank.upload(device, case.w1, case.s1, case.w3, case.s3, case.w2, case.s2)
+    hidden = device.resident_buffer_from(case.hidden)
+    rw = device.resident_buffer_from(case.router_w)
+    out = device.create_resident_buffer(tokens * cfg.hidden * 2)
+    plan.layer(tokens, bank, hidden, out, router_weights=rw)
+    assert plan.status() == 0
+    before = out.read(np.uint16).copy()
+    plan.set_wait_limit(2_000_000)  # about a millisecond
+    plan.debug_withhold_arrival(True)
+    plan.layer(tokens, bank, hidden, out, router_weights=rw)
+    device.synchronize(timeout_ns=20_000_000_000)
+    assert plan.status() & 8, "NVMOE_STATUS_WAIT_EXPIRED must be raised when a bounded wait gives up"
+    plan.debug_withhold_arrival(False)
+    plan.set_wait_limit(0)
+    for _ in range(2):
+        plan.layer(tokens, bank, hidden, out, router_weights=rw)
+        assert plan.status() == 0
+        np.testing.assert_array_equal(out.read(np.uint16), before)
+    plan.destroy()

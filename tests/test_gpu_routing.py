@@ -126,7 +126,9 @@ def _random_routes(rng, tokens, K, experts):
 
 
 @pytest.mark.parametrize("tokens,K,experts,I", [(1, 4, 32, 64), (64, 4, 32, 2880), (1000, 4, 32, 64), (2500, 9, 257, 32),
-                                                (4096, 4, 32, 32)])
+                                                (4096, 4, 32, 32),
+                                                (8192, 4, 128, 32),     # 32 768 routes: the gpt-oss-120b batch
+                                                (16384, 9, 257, 32)])   # 147 456 routes: the DeepSeek-V3 batch
 def test_compact_rank_mode_matches_reference_ranking(device, tokens, K, experts, I):
     rng = np.random.default_rng(tokens + K)
     cfg = _cfg(experts, K, hidden=64, intermediate=I, act_block=32)

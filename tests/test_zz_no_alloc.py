@@ -1,13 +1,15 @@
 """The route scheduler entry that allocates nothing on the device (fixed scratch array in the library).
 
 Collected last on purpose: it has to pass alone and after every other GPU test has used the same
-device, plans and scratch.  Checked against nvmoe_route_compact, the entry it is a variant of.
+device, plans and scratch.  Checked against nvmoe_route_compact, the entry it is a variant of, against
+the CPU checker's scheduler, and for leaving the device's free memory exactly as it found it.
 """
 import numpy as np
 import pytest
 
 from nerve_b200 import synthetic
 from nerve_b200.backend import CudaComputeDevice, CudaError, MoePlan, geometry_from_config
+from oracle import moe_oracle as mo
 
 pytestmark = pytest.mark.gpu
 
@@ -56,6 +58,40 @@ def test_static_scratch_entry_matches_route_compact_twice_in_a_row(device, token
         np.testing.assert_array_equal(got_frames, want_frames, err_msg=f"call {call}")
         np.testing.assert_array_equal(got_control, want_control, err_msg=f"call {call}")
         assert want_control[3] == tokens * K
+        # and both equal the checker's restatement of the scheduler shader
+        oracle_frames = np.zeros((tokens, plan.frame_words), dtype=np.uint32)
+        oracle_control = np.array([tokens, 0, 0, 0, 0, 0, 0], dtype=np.uint32)
+        mo.route_compact(routes, oracle_frames, oracle_control, 32, K, 1)
+        np.testing.assert_array_equal(got_frames, oracle_frames, err_msg=f"call {call} vs checker")
+        np.testing.assert_array_equal(got_control, oracle_control, err_msg=f"call {call} vs checker")
+    plan.destroy()
+
+
+def test_static_scratch_entry_leaves_free_device_memory_unchanged(device):
+    """The point of the entry: a caller that has given all free device memory away can still call it.
+    After one warm-up call (which loads the kernels and looks the array's address up) a call must not move
+    the device's free-memory figure by a single byte."""
+    import torch
+
+    tokens, K, experts = 2048, 4, 32  # the multi-block sort, the form that needs scratch
+    rng = np.random.default_rng(77)
+    plan = MoePlan(device, geometry_from_config(_cfg(experts, K, 32), tokens))
+    routes = _routes(rng, tokens, K, experts)
+    rb = device.resident_buffer_from(routes)
+    ib = device.create_resident_buffer(tokens * plan.frame_words * 4)
+    cb = device.resident_buffer_from(np.array([tokens, 0, 0, 0, 0, 0, 0], dtype=np.uint32))
+    plan.moe_route_compact_static(tokens, rb, ib, cb)  # warm-up
+    device.synchronize()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(device.ordinal)
+    for _ in range(3):
+        cb.write_bytes(np.array([tokens, 0, 0, 0, 0, 0, 0], dtype=np.uint32))
+        plan.moe_route_compact_static(tokens, rb, ib, cb)
+        device.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(device.ordinal)
+    assert free_after == free_before, (free_before, free_after)
+    for b in (rb, ib, cb):
+        b.destroy()
     plan.destroy()
 
 
