@@ -71,7 +71,8 @@ typedef enum nvmoe_status {
 typedef enum nvmoe_router_kind {
     NVMOE_ROUTER_SCORE_TOPK = 0,   /* moe_router_score_topk_batch1_bf16.comp.template */
     NVMOE_ROUTER_TOPK_SOFTMAX = 1, /* moe_topk_bf16.comp.template (softmax over the k selected) */
-    NVMOE_ROUTER_TOPK_ROUTED = 2   /* moe_topk_routed_batch1_bf16.comp.template */
+    NVMOE_ROUTER_TOPK_ROUTED = 2,  /* moe_topk_routed_batch1_bf16.comp.template */
+    NVMOE_ROUTER_PRESELECTED = 3   /* moe_router_preselected_batch1_bf16.comp.template (nvmoe_route_preselected) */
 } nvmoe_router_kind;
 
 typedef enum nvmoe_router_activation {
@@ -191,6 +192,26 @@ int nvmoe_router_linear(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buff
 int nvmoe_route(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* logits,
                 nvmoe_buffer* routes, const nvmoe_buffer* bias, nvmoe_buffer* telemetry);
 
+/* op `parameter_table_resource_preselection`
+ * (runtime-rs/shaders/resource_preselect_table_batch1.comp.template:35-97): every token's routed
+ * resources looked up in a [vocab_size][routed_k] table of 32-bit (table_word_stride 1) or 64-bit
+ * (2) integers, always-selected ids appended, ascending. bindings: 0 token ids [T] u32, 1 resource
+ * routes [T][K] u32, 2 table, 3 telemetry (optional). A token id beyond the table, an index beyond the
+ * routed resources or a repeated index invalidates the token: its words become 0xffffffff, nothing is
+ * counted, NVMOE_STATUS_ROUTE_OUT_OF_RANGE is raised. */
+int nvmoe_resource_preselect_table(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* token_ids,
+                                   nvmoe_buffer* resource_routes, const nvmoe_buffer* table, uint32_t vocab_size,
+                                   uint32_t table_word_stride, nvmoe_buffer* telemetry);
+
+/* op `moe_route` with selection "preselected_resource_indices"
+ * (runtime-rs/shaders/moe_router_preselected_batch1_bf16.comp.template:56-91): route words for resources
+ * chosen elsewhere, weight = activation(logit) normalised over the routed selections in their stored
+ * order. bindings: 0 logits, 1 resource routes, 2 routes. The plan's router_kind must be
+ * NVMOE_ROUTER_PRESELECTED. An invalid token of the preselection gives route words 0x0000ffff (weight 0,
+ * an id every expert kernel skips) where the shader would read past its logits row. */
+int nvmoe_route_preselected(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* logits,
+                            const nvmoe_buffer* resource_routes, nvmoe_buffer* routes);
+
 /* Route scheduler in front of gate/up (runtime-rs/shaders/moe_route_compact_batch1.comp.template:26-105).
  * bindings: 1 routes, 2 intermediates, 3 slots (optional), 31 control. The caller writes
  * {batch_width, expert_start, expert_count, 0,0,0,0} into control first; expert_count == 0 selects
@@ -259,6 +280,34 @@ int nvmoe_down(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* inter
  * bindings: 0 expert outputs, 1 output. */
 int nvmoe_reduce(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* expert_outputs,
                  nvmoe_buffer* output);
+
+/* ---- the nodes either side of the MoE chain (nerve/circuit_lowering_sparse_experts.py:173-209,
+ * nerve/circuit_lowering_nodes.py:541-599) ----------------------------------------------------------- */
+
+/* op `rms_norm`, the block's ffn_norm (runtime-rs/shaders/rms_norm_batch_bf16.comp.template:55-108).
+ * bindings: 0 input [rows][element_count] bf16, 1 output, 2 weight [element_count] bf16.
+ * y = bf16(x * rsqrt(mean(x^2) + eps) * (w + weight_offset)). */
+int nvmoe_rms_norm(nvmoe_plan* plan, uint32_t rows, uint32_t element_count, const nvmoe_buffer* input,
+                   nvmoe_buffer* output, const nvmoe_buffer* weight, float eps, float weight_offset);
+
+/* ops `bounded_silu_multiply` (limit > 0: runtime-rs/shaders/bounded_silu_multiply_batch_bf16.comp.template:26-53)
+ * and `silu_multiply` (limit == 0: runtime-rs/shaders/silu_multiply_batch_bf16.comp.template:24-52, which
+ * rounds the activated gate to bf16 before the product). bindings: 0 gate, 1 up, 2 output. */
+int nvmoe_silu_multiply(nvmoe_plan* plan, uint32_t rows, uint32_t element_count, const nvmoe_buffer* gate,
+                        const nvmoe_buffer* up, nvmoe_buffer* output, float limit);
+
+/* op `residual_add` (runtime-rs/shaders/add_batch_bf16.comp.template:36-50). bindings: 0 a, 1 b, 2 output. */
+int nvmoe_residual_add(nvmoe_plan* plan, uint32_t rows, uint32_t element_count, const nvmoe_buffer* a,
+                       const nvmoe_buffer* b, nvmoe_buffer* output);
+
+/* op `linear` of the dense shared expert over a packaged MXFP4 matrix (weights I8 [rows][cols/2], scales
+ * F8_E8M0 [rows][cols/32], the experts' own tensor contract). bindings: 0 input [T][cols] bf16, 1 output
+ * [T][rows] bf16, 2 weights, 3 scales. The reference has no dense MXFP4 linear shader (its dense linears are
+ * bf16 or block-scaled FP8); this one computes what the MoE node computes for a resource every token selects
+ * with weight one (independent_sparse_moe_down_batch1_mxfp4.comp.template:507-610): activations quantised
+ * to E4M3 per geometry.act_block, f32 accumulation, one bf16 rounding, on the same kernels. */
+int nvmoe_dense_linear(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* input, nvmoe_buffer* output,
+                       const nvmoe_buffer* weights, const nvmoe_buffer* scales, uint32_t rows, uint32_t cols);
 
 /*
  * The whole chain of nerve/circuit_lowering_sparse_experts.py:80-172 in one call:

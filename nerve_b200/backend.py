@@ -324,6 +324,27 @@ class MoePlan:
     def moe_route(self, batch_width, logits, routes, bias=None, telemetry=None):
         self._call("nvmoe_route", batch_width, _h(logits), _h(routes), _h(bias), _h(telemetry))
 
+    def parameter_table_resource_preselection(self, batch_width, token_ids, resource_routes, table, vocab_size,
+                                              table_word_stride=1, telemetry=None):
+        self._call("nvmoe_resource_preselect_table", batch_width, _h(token_ids), _h(resource_routes), _h(table), vocab_size,
+                   table_word_stride, _h(telemetry))
+
+    def moe_route_preselected(self, batch_width, logits, resource_routes, routes):
+        self._call("nvmoe_route_preselected", batch_width, _h(logits), _h(resource_routes), _h(routes))
+
+    def rms_norm(self, rows, element_count, input, output, weight, eps, weight_offset=0.0):
+        self._call("nvmoe_rms_norm", rows, element_count, _h(input), _h(output), _h(weight), eps, weight_offset)
+
+    def silu_multiply(self, rows, element_count, gate, up, output, limit=0.0):
+        """`bounded_silu_multiply` with limit > 0, `silu_multiply` with limit 0."""
+        self._call("nvmoe_silu_multiply", rows, element_count, _h(gate), _h(up), _h(output), limit)
+
+    def residual_add(self, rows, element_count, a, b, output):
+        self._call("nvmoe_residual_add", rows, element_count, _h(a), _h(b), _h(output))
+
+    def dense_linear(self, batch_width, input, output, weights, scales, rows, cols):
+        self._call("nvmoe_dense_linear", batch_width, _h(input), _h(output), _h(weights), _h(scales), rows, cols)
+
     def moe_route_compact(self, batch_width, routes, intermediates, control, slots=None):
         self._call("nvmoe_route_compact", batch_width, _h(routes), _h(intermediates), _h(slots), _h(control))
 
@@ -361,6 +382,48 @@ class MoePlan:
 
     def ep_unpack(self, batch_width, returned_rows, send_index, expert_outputs):
         self._call("nvmoe_ep_unpack", batch_width, _h(returned_rows), _h(send_index), _h(expert_outputs))
+
+    # -- a node chain, entry point by entry point ------------------------------------------------
+    # argument order of every entry point a dispatch list may name: (binding names..., scalar names...)
+    _ENTRY_ARGUMENTS = {
+        "nvmoe_router_linear": (("hidden", "logits", "router_weights", "router_bias"), ()),
+        "nvmoe_route": (("logits", "routes", "bias", "telemetry"), ()),
+        "nvmoe_resource_preselect_table": (("token_ids", "resource_routes", "table"), ("vocab_size", "table_word_stride", "telemetry")),
+        "nvmoe_route_preselected": (("logits", "resource_routes", "routes"), ()),
+        "nvmoe_route_compact": (("routes", "intermediates", "slots", "control"), ()),
+        "nvmoe_gate_up": (("hidden", "routes", "intermediates", "addresses", "slots", "control"), ()),
+        "nvmoe_route_count": (("routes", "slots", "control"), ()),
+        "nvmoe_down": (("intermediates", "routes", "outputs", "addresses", "slots", "control"), ()),
+        "nvmoe_reduce": (("expert_outputs", "output"), ()),
+        "nvmoe_dense_linear": (("input", "output", "weights", "scales"), ("rows", "cols")),
+        "nvmoe_silu_multiply": (("#element_count", "gate", "up", "output"), ("limit",)),
+        "nvmoe_residual_add": (("#element_count", "a", "b", "output"), ()),
+    }
+
+    def run_dispatch(self, dispatch, batch_width: int, buffers: dict, expert_start: int = 0, expert_count: int = 0) -> None:
+        """Runs the dispatch list of ``node_chain.plan_from_nodes`` one entry point per node, the way a runtime
+        that walks the component's kernel steps would: ``buffers`` maps every signal and parameter id the list
+        names (plus ``<node>.address_table`` / ``<node>.parameter_slots`` of the two expert nodes) to a resident
+        buffer. The 7-word control blocks of the scheduler stages are created here and written as the reference
+        host writes them ({batch_width, expert_start, expert_count, 0, 0, 0, 0})."""
+        control_words = np.array([batch_width, expert_start, expert_count, 0, 0, 0, 0], dtype=np.uint32)
+        for step in dispatch.steps:
+            names, scalar_names = self._ENTRY_ARGUMENTS[step.entry]
+            bound = dict(step.bindings)
+            args = [batch_width]
+            for name in names:
+                if name.startswith("#"):
+                    args.append(step.scalars[name[1:]])
+                    continue
+                key = bound.get(name)
+                if key is not None and key.endswith(".control") and key not in buffers:
+                    buffers[key] = self.device.resident_buffer_from(control_words)
+                elif key is not None and key.endswith(".control") and step.entry in ("nvmoe_route_compact", "nvmoe_route_count"):
+                    buffers[key].write_bytes(control_words)
+                args.append(_h(buffers.get(key)) if key is not None else None)
+            for name in scalar_names:
+                args.append(_h(buffers.get(dict(step.bindings).get(name))) if name == "telemetry" else step.scalars[name])
+            self._call(step.entry, *args)
 
     def launches(self) -> int:
         """Kernels this plan has launched since it was created."""

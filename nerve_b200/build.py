@@ -18,7 +18,7 @@ CSRC = PACKAGE_DIR / "csrc"
 INCLUDE = PACKAGE_DIR.parent / "include"
 LIB_PATH = PACKAGE_DIR / "libnerve_cuda_moe.so"
 
-SOURCES = ["capi.cu", "router.cu", "schedule.cu", "quantize.cu", "experts_simt.cu", "experts_tc.cu", "reduce.cu", "probe.cu"]
+SOURCES = ["capi.cu", "router.cu", "schedule.cu", "quantize.cu", "experts_simt.cu", "experts_tc.cu", "reduce.cu", "probe.cu", "ffn_tail.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

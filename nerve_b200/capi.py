@@ -87,6 +87,12 @@ PROTOTYPES = {
     "nvmoe_plan_debug_withhold_arrival": (c_int, [c_void_p, c_int]),
     "nvmoe_router_linear": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvmoe_resource_preselect_table": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "nvmoe_route_preselected": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "nvmoe_rms_norm": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_float, c_float]),
+    "nvmoe_silu_multiply": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_float]),
+    "nvmoe_residual_add": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "nvmoe_dense_linear": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32]),
     "nvmoe_route_compact": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route_compact_static": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_route_count": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),

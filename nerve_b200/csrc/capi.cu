@@ -148,6 +148,18 @@ struct nvmoe_plan {
     uint32_t launches = 0;
     long long wait_cycles = 4000000000ll;  // limit of the bounded in-kernel waits of the tensor path (about 2 s)
     uint32_t debug_flags = 0;
+    // dense linears run as one always-selected resource of a plan of their own shape (nvmoe_dense_linear)
+    struct DenseLinear {
+        uint32_t rows = 0, cols = 0;
+        nvmoe_plan* plan = nullptr;
+        nvmoe_buffer* addresses = nullptr;
+        nvmoe_buffer* slots = nullptr;
+        DeviceArray unit_routes;
+        const void* weights = nullptr;
+        const void* scales = nullptr;
+        uint64_t weights_version = 0, scales_version = 0;
+    };
+    std::vector<DenseLinear> dense;
 };
 
 namespace {
@@ -217,13 +229,15 @@ int validate_geometry(const nvmoe_geometry& g) {
         return bad("intermediate_size %u must be a positive multiple of 32", g.intermediate_size);
     if (!(0u < g.routed_k && g.routed_k <= g.routed_experts && g.routed_experts <= kMaxExperts))
         return bad("invalid routing geometry r%u k%u", g.routed_experts, g.routed_k);
-    if (g.router_kind > NVMOE_ROUTER_TOPK_ROUTED) return bad("unknown router_kind %u", g.router_kind);
+    if (g.router_kind > NVMOE_ROUTER_PRESELECTED) return bad("unknown router_kind %u", g.router_kind);
+    if (g.router_kind == NVMOE_ROUTER_PRESELECTED && g.activation == NVMOE_ACT_SOFTMAX)
+        return bad("a preselected router needs an activation that is evaluated per resource (sigmoid or sqrt-softplus)");
     if (g.activation > NVMOE_ACT_SQRT_SOFTPLUS) return bad("unknown router activation %u", g.activation);
     if (g.router_kind == NVMOE_ROUTER_TOPK_ROUTED && g.activation == NVMOE_ACT_SQRT_SOFTPLUS)
         return bad("the routed top-k router scores with sigmoid or softmax only");
     if (g.bias_dtype > NVMOE_BIAS_BF16) return bad("unknown bias dtype %u", g.bias_dtype);
-    if (g.always_count && g.router_kind != NVMOE_ROUTER_SCORE_TOPK)
-        return bad("always-selected resources need the score_topk router");
+    if (g.always_count && g.router_kind != NVMOE_ROUTER_SCORE_TOPK && g.router_kind != NVMOE_ROUTER_PRESELECTED)
+        return bad("always-selected resources need the score_topk or the preselected router");
     if (g.always_count && !(g.always_weight > 0.0f) ) return bad("always-selected weight must be positive and finite");
     if (g.routed_experts + g.always_count > kMaxExperts) return bad("total resource count exceeds %u", kMaxExperts);
     if (g.routed_k + g.always_count > kMaxTopK) return bad("more than %u routes per token", kMaxTopK);
@@ -516,6 +530,12 @@ void nvmoe_plan_destroy(nvmoe_plan* p) {
     if (!p) return;
     cudaSetDevice(p->device->ordinal);
     cudaStreamSynchronize(p->device->stream);
+    for (auto& dl : p->dense) {
+        nvmoe_plan_destroy(dl.plan);
+        nvmoe_buffer_destroy(dl.addresses);
+        nvmoe_buffer_destroy(dl.slots);
+        dl.unit_routes.release();
+    }
     for (auto& stage_sets : p->sets)
         for (auto& es : stage_sets) es->release();
     DeviceArray* all[] = {&p->status, &p->grouped[0], &p->grouped[1], &p->offsets[0],
@@ -598,6 +618,8 @@ int nvmoe_route(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* logits, nvmoe_buf
     const nvmoe_geometry& g = p->g;
     NVMOE_TRY(check_buffer(p, logits, (size_t)T * ((g.routed_experts + 1u) / 2u) * 4u, "logits"));
     NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    if (g.router_kind == NVMOE_ROUTER_PRESELECTED)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "this plan's router takes preselected resources: call nvmoe_route_preselected");
     const bool uses_bias = g.bias_dtype != NVMOE_BIAS_NONE && g.router_kind != NVMOE_ROUTER_TOPK_SOFTMAX;
     if (uses_bias)
         NVMOE_TRY(check_buffer(p, bias, (size_t)g.routed_experts * (g.bias_dtype == NVMOE_BIAS_F32 ? 4u : 2u), "selection bias"));
@@ -989,6 +1011,198 @@ int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, 
                   nullptr, p->device->stream);
     p->launches++;
     return post_launch(p, "reduce");
+}
+
+// ---- token-id table routing -----------------------------------------------------------------------
+
+int nvmoe_resource_preselect_table(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* token_ids, nvmoe_buffer* resource_routes,
+                                   const nvmoe_buffer* table, uint32_t vocab_size, uint32_t table_word_stride,
+                                   nvmoe_buffer* telemetry) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    if (vocab_size == 0u || (table_word_stride != 1u && table_word_stride != 2u))
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "preselection table of %u rows with %u-word elements (1 = I32, 2 = I64)",
+                    vocab_size, table_word_stride);
+    NVMOE_TRY(check_buffer(p, token_ids, (size_t)T * 4u, "token ids"));
+    NVMOE_TRY(check_buffer(p, resource_routes, (size_t)T * p->K * 4u, "resource routes"));
+    NVMOE_TRY(check_buffer(p, table, (size_t)vocab_size * g.routed_k * table_word_stride * 4u, "preselection table"));
+    if (telemetry) {
+        const size_t r = p->experts;
+        NVMOE_TRY(check_buffer(p, telemetry, (r + r * (r - 1u) / 2u) * 4u, "telemetry"));
+    }
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_preselect_table((const uint32_t*)token_ids->ptr, (const uint32_t*)table->ptr, table_word_stride, vocab_size,
+                           g.routed_experts, g.routed_k, g.always_count, T, (uint32_t*)resource_routes->ptr,
+                           telemetry ? (uint32_t*)telemetry->ptr : nullptr, p->status.as<uint32_t>(), p->device->stream);
+    p->launches++;
+    return post_launch(p, "resource preselection");
+}
+
+int nvmoe_route_preselected(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* logits, const nvmoe_buffer* resource_routes,
+                            nvmoe_buffer* routes) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    if (g.router_kind != NVMOE_ROUTER_PRESELECTED)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "this plan's router selects by score: call nvmoe_route");
+    NVMOE_TRY(check_buffer(p, logits, (size_t)T * ((g.routed_experts + 1u) / 2u) * 4u, "logits"));
+    NVMOE_TRY(check_buffer(p, resource_routes, (size_t)T * p->K * 4u, "resource routes"));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_route_preselected((const uint32_t*)logits->ptr, (const uint32_t*)resource_routes->ptr, T, (uint32_t*)routes->ptr,
+                             p->status.as<uint32_t>(), g, p->device->stream);
+    p->launches++;
+    return post_launch(p, "preselected router");
+}
+
+// ---- the nodes either side of the MoE chain ----------------------------------------------------------
+
+int nvmoe_rms_norm(nvmoe_plan* p, uint32_t rows, uint32_t element_count, const nvmoe_buffer* input, nvmoe_buffer* output,
+                   const nvmoe_buffer* weight, float eps, float weight_offset) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    if (rows == 0u || element_count == 0u || element_count % 2u)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "rms_norm: %u rows of %u elements (an even, positive count is required)", rows,
+                    element_count);
+    if (!(eps >= 0.0f)) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "rms_norm: epsilon must not be negative");
+    NVMOE_TRY(check_buffer(p, input, (size_t)rows * element_count * 2u, "input"));
+    NVMOE_TRY(check_buffer(p, output, (size_t)rows * element_count * 2u, "output"));
+    NVMOE_TRY(check_buffer(p, weight, (size_t)element_count * 2u, "norm weight"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_rms_norm((const uint16_t*)input->ptr, (const uint16_t*)weight->ptr, (uint16_t*)output->ptr, rows, element_count, eps,
+                    weight_offset, p->device->stream);
+    p->launches++;
+    return post_launch(p, "rms_norm");
+}
+
+static int pairwise_checks(nvmoe_plan* p, uint32_t rows, uint32_t element_count, const nvmoe_buffer* a, const nvmoe_buffer* b,
+                           const nvmoe_buffer* out, const char* what) {
+    if (rows == 0u || element_count == 0u || element_count % 2u)
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "%s: %u rows of %u elements (an even, positive count is required)", what,
+                    rows, element_count);
+    const size_t bytes = (size_t)rows * element_count * 2u;
+    NVMOE_TRY(check_buffer(p, a, bytes, "first input"));
+    NVMOE_TRY(check_buffer(p, b, bytes, "second input"));
+    NVMOE_TRY(check_buffer(p, out, bytes, "output"));
+    return NVMOE_OK;
+}
+
+int nvmoe_silu_multiply(nvmoe_plan* p, uint32_t rows, uint32_t element_count, const nvmoe_buffer* gate, const nvmoe_buffer* up,
+                        nvmoe_buffer* output, float limit) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    if (!(limit >= 0.0f)) return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "silu_multiply: the clamp limit must not be negative");
+    NVMOE_TRY(pairwise_checks(p, rows, element_count, gate, up, output, "silu_multiply"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_silu_multiply((const uint16_t*)gate->ptr, (const uint16_t*)up->ptr, (uint16_t*)output->ptr, (size_t)rows * element_count,
+                         limit, p->device->stream);
+    p->launches++;
+    return post_launch(p, "silu_multiply");
+}
+
+int nvmoe_residual_add(nvmoe_plan* p, uint32_t rows, uint32_t element_count, const nvmoe_buffer* a, const nvmoe_buffer* b,
+                       nvmoe_buffer* output) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(pairwise_checks(p, rows, element_count, a, b, output, "residual_add"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_add_bf16((const uint16_t*)a->ptr, (const uint16_t*)b->ptr, (uint16_t*)output->ptr, (size_t)rows * element_count,
+                    p->device->stream);
+    p->launches++;
+    return post_launch(p, "residual_add");
+}
+
+// A dense linear over packaged MXFP4 weights is the down projection of one always-selected resource
+// with route weight one: the same quantisation, kernels and rounding as an expert's, on a plan of the
+// linear's own shape that this plan keeps.
+int nvmoe_dense_linear(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* input, nvmoe_buffer* output, const nvmoe_buffer* weights,
+                       const nvmoe_buffer* scales, uint32_t rows, uint32_t cols) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    nvmoe_device* d = p->device;
+    if (rows == 0u || cols == 0u || rows % 32u || cols % 32u || cols % p->g.act_block)
+        return fail(d, NVMOE_ERR_INVALID_ARGUMENT, "dense linear %u x %u: both sizes must be multiples of 32 and the input size of the "
+                    "activation block %u", rows, cols, p->g.act_block);
+    NVMOE_TRY(check_buffer(p, input, (size_t)T * cols * 2u, "input"));
+    NVMOE_TRY(check_buffer(p, output, (size_t)T * rows * 2u, "output"));
+    NVMOE_TRY(check_buffer(p, weights, (size_t)rows * (cols / 2u), "weights"));
+    NVMOE_TRY(check_buffer(p, scales, (size_t)rows * (cols / 32u), "weight scales"));
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    nvmoe_plan::DenseLinear* dl = nullptr;
+    for (auto& entry : p->dense)
+        if (entry.rows == rows && entry.cols == cols) dl = &entry;
+    if (!dl) {
+        nvmoe_plan::DenseLinear fresh;
+        fresh.rows = rows;
+        fresh.cols = cols;
+        nvmoe_geometry g{};
+        nvmoe_geometry_default(&g, rows, cols, 1u, 1u);
+        g.act_block = p->g.act_block;
+        g.max_tokens = p->g.max_tokens;
+        NVMOE_TRY(nvmoe_plan_create(d, &g, &fresh.plan));
+        fresh.plan->expert_path = p->expert_path;
+        int rc = nvmoe_buffer_create(d, 64u, &fresh.addresses);
+        if (rc == NVMOE_OK) rc = nvmoe_buffer_create(d, 8u, &fresh.slots);
+        const uint32_t slot_words[2] = {0u, 1u};
+        if (rc == NVMOE_OK) rc = nvmoe_buffer_write(fresh.slots, 0, slot_words, 8u);
+        if (rc == NVMOE_OK && fresh.unit_routes.ensure((size_t)g.max_tokens * 4u) != cudaSuccess)
+            rc = fail(d, NVMOE_ERR_OUT_OF_MEMORY, "dense linear: out of device memory");
+        if (rc == NVMOE_OK) {
+            std::vector<uint32_t> ones(g.max_tokens, 0x3f80u << 16);  // weight 1.0, resource 0
+            if (cudaMemcpy(fresh.unit_routes.ptr, ones.data(), ones.size() * 4u, cudaMemcpyHostToDevice) != cudaSuccess)
+                rc = fail(d, NVMOE_ERR_CUDA, "dense linear: could not write the unit routes");
+        }
+        if (rc != NVMOE_OK) {
+            nvmoe_plan_destroy(fresh.plan);
+            nvmoe_buffer_destroy(fresh.addresses);
+            nvmoe_buffer_destroy(fresh.slots);
+            fresh.unit_routes.release();
+            return rc;
+        }
+        p->dense.push_back(fresh);
+        dl = &p->dense.back();
+    }
+    nvmoe_plan* sub = dl->plan;
+    sub->expert_path = p->expert_path;
+    sub->wait_cycles = p->wait_cycles;
+    if (dl->weights != weights->ptr || dl->scales != scales->ptr || dl->weights_version != weights->version ||
+        dl->scales_version != scales->version) {
+        // the two address records of the one resource: {address, byte count, generation, resident, representation}
+        uint64_t records[8] = {(uint64_t)(uintptr_t)weights->ptr, (uint64_t)rows * (cols / 2u), 1u + weights->version, 1u,
+                               (uint64_t)(uintptr_t)scales->ptr,  (uint64_t)rows * (cols / 32u), 1u + scales->version, 1u};
+        NVMOE_TRY(nvmoe_buffer_write(dl->addresses, 0, records, sizeof records));
+        dl->weights = weights->ptr;
+        dl->scales = scales->ptr;
+        dl->weights_version = weights->version;
+        dl->scales_version = scales->version;
+    }
+    cudaStream_t st = d->stream;
+    const bool tensor = use_tensor_path(sub);
+    ExpertSet* es = nullptr;
+    NVMOE_TRY(prepare_expert_set(sub, false, dl->addresses, dl->slots, tensor, &es));
+    uint32_t* region = sub->tile_list.as<uint32_t>() + tile_region_words(sub);
+    launch_dense_schedule(T, tc_token_tile_for(T, 1u, 1u, false), sub->grouped[1].as<uint32_t>(), sub->offsets[1].as<uint32_t>(),
+                          sub->position[1].as<uint32_t>(), tensor ? region + 64 : nullptr, tensor ? region : nullptr, st);
+    sub->launches++;
+    NVMOE_TRY(post_launch(sub, "dense linear schedule"));
+    if (tensor) {
+        launch_quantize_grouped(input->ptr, false, sub->grouped[1].as<uint32_t>(), sub->offsets[1].as<uint32_t>(), 1u, T, 1u, cols, cols,
+                                sub->g.act_block, sub->grouped_q[1].as<uint8_t>(), sub->grouped_e8m0[1].as<uint32_t>(), st);
+    } else {
+        launch_quantize((const uint16_t*)input->ptr, T, cols, sub->g.act_block, cols, sub->iq.as<uint8_t>(), sub->i_scales.as<float>(),
+                        sub->i_e8m0.as<uint32_t>(), st);
+    }
+    sub->launches++;
+    NVMOE_TRY(post_launch(sub, "dense linear quantise"));
+    ExpertCall call;
+    call.gate_up = false;
+    call.T = T;
+    call.routes = dl->unit_routes.as<uint32_t>();
+    call.outputs = (uint16_t*)output->ptr;
+    call.prepared = es;
+    call.scheduled = true;
+    NVMOE_TRY(run_experts(sub, call));
+    p->launches += sub->launches;
+    sub->launches = 0;
+    return NVMOE_OK;
 }
 
 // ---- expert-parallel exchange helpers -----------------------------------------------------------

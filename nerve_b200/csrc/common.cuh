@@ -217,6 +217,20 @@ void configure_simt_kernels();
 void launch_gate_up_simt(const ExpertLaunch& p, cudaStream_t stream);
 void launch_down_simt(const ExpertLaunch& p, cudaStream_t stream);
 
+// ffn_tail.cu: the nodes either side of the MoE chain and the token-id table routing
+void launch_rms_norm(const uint16_t* input, const uint16_t* weight, uint16_t* output, uint32_t rows, uint32_t hidden, float eps,
+                     float weight_offset, cudaStream_t stream);
+void launch_silu_multiply(const uint16_t* gate, const uint16_t* up, uint16_t* out, size_t elements, float limit, cudaStream_t stream);
+void launch_add_bf16(const uint16_t* a, const uint16_t* b, uint16_t* out, size_t elements, cudaStream_t stream);
+void launch_preselect_table(const uint32_t* token_ids, const uint32_t* table, uint32_t word_stride, uint32_t vocab, uint32_t routed,
+                            uint32_t k, uint32_t always, uint32_t tokens, uint32_t* selections, uint32_t* telemetry, uint32_t* status,
+                            cudaStream_t stream);
+void launch_route_preselected(const uint32_t* logits, const uint32_t* selections, uint32_t tokens, uint32_t* routes, uint32_t* status,
+                              const nvmoe_geometry& g, cudaStream_t stream);
+// every row a route of expert 0 in row order: grouped list, offsets [0, rows], inverse, (expert, token tile) list
+void launch_dense_schedule(uint32_t rows, uint32_t n_tile, uint32_t* grouped, uint32_t* offsets, uint32_t* position, uint32_t* tiles,
+                           uint32_t* tile_count, cudaStream_t stream);
+
 // probe.cu: a run of `groups` x 8 block-scaled MMAs (128 x n_tile x 32, two alternating accumulators)
 // on every one of `ctas` CTAs; cycles[cta] = clock cycles from first issue to completion
 cudaError_t launch_mma_rate_probe(uint32_t n_tile, uint32_t groups, uint32_t ctas, long long* cycles, uint32_t* status,

@@ -200,6 +200,15 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
     grid_dependency_sync();
     const uint32_t pair_count = *list.count;
     const uint32_t tile_count = pair_count * m_tiles;
+    if (USE_TMA) {
+        // The per-expert tensor maps were written to global memory by an earlier kernel. A thread block must
+        // acquire such a map once before any of its threads hands it to the TMA unit; further uses by the
+        // block need no fence. All threads share the maps out, so that the block pays one fence latency here
+        // instead of one per map in the lane that issues the loads.
+        for (uint32_t m = threadIdx.x; m < p.work.num_experts * C::kSources; m += blockDim.x) tensormap_acquire(p.tmaps + (size_t)m * 128u);
+        if (threadIdx.x == 0u) tensormap_acquire(p.act_tmap);
+        __syncthreads();
+    }
 
     if (warp == 5u) {
         // ===== TMA issue (one lane): whole 128 x 128 boxes of weight codes, padded and swizzled by the unit =====
@@ -247,8 +256,6 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++)
                     scale_blocks[mx] = cur.ts[C::source_of(mx)] + (size_t)scale_tile(m_tile, mx) * k_blocks * kScaleBlockBytes;
-#pragma unroll
-                for (uint32_t mx = 0; mx < C::kSources; mx++) tensormap_acquire(maps + mx * 128u);
                 for (uint32_t ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag, wait_limit)) {
                         alive = false;

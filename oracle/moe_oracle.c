@@ -822,3 +822,152 @@ void oracle_sum_f32_scale_packed_bf16(const float* partials, const uint32_t* sca
         }
     }
 }
+
+/* ------------------------------------------------------------------------------------------ */
+/* token-id table routing: resource_preselect_table_batch1.comp.template:35-97 and             */
+/* moe_router_preselected_batch1_bf16.comp.template:56-91                                      */
+
+/* Looks every token's routed resources up in a [vocab][k] table of 32- or 64-bit integers
+ * (word_stride 1 or 2), appends the always-selected ids, sorts ascending (:74-82) and counts the
+ * selection telemetry (:83-96).  A token id beyond the table, an index beyond the routed
+ * resources, a non-zero high word or a repeated index makes the whole token invalid: its
+ * selections become 0xffffffff (:67-73) and nothing is counted.  Returns the invalid tokens. */
+int oracle_resource_preselect_table(const uint32_t* token_ids, const uint32_t* table_words,
+                                    uint32_t word_stride, uint32_t vocab, uint32_t routed,
+                                    uint32_t k, uint32_t always, uint32_t tokens,
+                                    uint32_t* selections, uint32_t* telemetry) {
+    uint32_t total_k = k + always, total_resources = routed + always;
+    int invalid_tokens = 0;
+    for (uint32_t t = 0; t < tokens; t++) {
+        uint32_t ids[64];
+        uint32_t token_id = token_ids[t];
+        int invalid = token_id >= vocab;
+        for (uint32_t lane = 0; lane < k && !invalid; lane++) {
+            size_t element = (size_t)token_id * k + lane;
+            uint32_t index = table_words[element * word_stride];
+            uint32_t high = word_stride == 2u ? table_words[element * word_stride + 1u] : 0u;
+            if (index >= routed || high != 0u) invalid = 1;
+            for (uint32_t previous = 0; previous < lane; previous++)
+                if (index == table_words[((size_t)token_id * k + previous) * word_stride]) invalid = 1;
+            ids[lane] = index < routed ? index : routed - 1u;
+        }
+        uint32_t* out = selections + (size_t)t * total_k;
+        if (invalid) {
+            for (uint32_t r = 0; r < total_k; r++) out[r] = 0xffffffffu;
+            invalid_tokens++;
+            continue;
+        }
+        for (uint32_t a = 0; a < always; a++) ids[k + a] = routed + a;
+        for (uint32_t r = 1; r < total_k; r++) {
+            uint32_t index = ids[r], ins = r;
+            while (ins > 0u && ids[ins - 1u] > index) {
+                ids[ins] = ids[ins - 1u];
+                ins--;
+            }
+            ids[ins] = index;
+        }
+        for (uint32_t r = 0; r < total_k; r++) {
+            out[r] = ids[r];
+            if (telemetry) telemetry[ids[r]]++;
+        }
+        if (telemetry)
+            for (uint32_t l = 0; l < total_k; l++)
+                for (uint32_t rr = l + 1u; rr < total_k; rr++) {
+                    uint32_t left = ids[l], right = ids[rr];
+                    uint32_t preceding = left * (2u * total_resources - left - 1u) / 2u;
+                    telemetry[total_resources + preceding + right - left - 1u]++;
+                }
+    }
+    return invalid_tokens;
+}
+
+/* Route words of preselected resources: weight = activation(logit) of each routed selection
+ * (sigmoid, or sqrt(softplus)), normalised over the routed selections in their stored order and
+ * scaled, always-selected resources at their constant weight (:72-90).  A selection whose index is
+ * not a routed resource where one is expected (the 0xffffffff of an invalid token) gives the route
+ * word 0x0000ffff (weight 0, an id no expert kernel accepts) instead of the shader's read past
+ * the logits row. */
+void oracle_route_preselected(const oracle_router* p, const uint32_t* logit_words,
+                              const uint32_t* selections, uint32_t tokens, uint32_t* routes) {
+    uint32_t E = p->routed_experts, k = p->routed_k, total_k = k + p->always_count;
+    uint32_t words = (E + 1u) / 2u;
+    for (uint32_t t = 0; t < tokens; t++) {
+        const uint32_t* sel = selections + (size_t)t * total_k;
+        uint32_t* out = routes + (size_t)t * total_k;
+        float values[64];
+        int bad = 0;
+        for (uint32_t r = 0; r < k; r++)
+            if ((sel[r] & 0xffffu) >= E) bad = 1;
+        if (bad) {
+            for (uint32_t r = 0; r < total_k; r++) out[r] = 0x0000ffffu;
+            continue;
+        }
+        for (uint32_t r = 0; r < k; r++) {
+            float v = unpack_bf16(logit_words + (size_t)t * words, sel[r] & 0xffffu);
+            values[r] = p->activation == 0u ? nvmoe_sigmoidf(v) : sqrtf(nvmoe_softplusf(v));
+        }
+        float den = 0.0f;
+        if (p->normalize_selected)
+            for (uint32_t r = 0; r < k; r++) den = den + values[r];
+        for (uint32_t r = 0; r < total_k; r++) {
+            float w = p->always_weight;
+            if (r < k) w = p->normalize_selected ? values[r] / den * p->routed_scale : values[r] * p->routed_scale;
+            out[r] = (nvmoe_f32_to_bf16(w) << 16) | (sel[r] & 0xffffu);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* the steps either side of the MoE node chain                                                 */
+
+/* rms_norm_batch_bf16.comp.template:55-108: 64 lanes stride over the row with fma(x, x, sum)
+ * (:63-75), the lane sums are added (subgroupAdd then a sum over subgroups, :76-90: taken as the
+ * pinned butterfly over 64 lanes), inv_rms = 1 / sqrt(total / H + eps) out of an IEEE division and
+ * square root, and y = bf16(x * inv_rms * (w + offset)) (:92-107). */
+void oracle_rms_norm(const uint16_t* input, const uint16_t* weight, uint16_t* output, uint32_t rows,
+                     uint32_t hidden, float eps, float weight_offset) {
+#pragma omp parallel for schedule(static)
+    for (int64_t rr = 0; rr < (int64_t)rows; rr++) {
+        const uint16_t* x = input + (size_t)rr * hidden;
+        float lanes[64];
+        for (uint32_t lane = 0; lane < 64u; lane++) {
+            float sum = 0.0f;
+            for (uint32_t i = lane; i < hidden; i += 64u) {
+                float v = nvmoe_bf16_to_f32(x[i]);
+                sum = fmaf(v, v, sum);
+            }
+            lanes[lane] = sum;
+        }
+        float total = butterfly_sum64(lanes);
+        float inv_rms = 1.0f / sqrtf(total / (float)hidden + eps);
+        for (uint32_t i = 0; i < hidden; i++) {
+            float w = nvmoe_bf16_to_f32(weight[i]) + weight_offset;
+            output[(size_t)rr * hidden + i] = (uint16_t)nvmoe_f32_to_bf16(nvmoe_bf16_to_f32(x[i]) * inv_rms * w);
+        }
+    }
+}
+
+/* limit > 0: bounded_silu_multiply_batch_bf16.comp.template:26-30 (gate = min(gate, L), up clamped to
+ * +-L, one rounding at the end); limit == 0: silu_multiply_batch_bf16.comp.template:24-27,45-51,
+ * where the activated gate is rounded to bf16 before it meets the up value. */
+void oracle_silu_multiply(const uint16_t* gate, const uint16_t* up, uint16_t* out, uint64_t count, float limit) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)count; i++) {
+        float g = nvmoe_bf16_to_f32(gate[i]), u = nvmoe_bf16_to_f32(up[i]);
+        float value;
+        if (limit > 0.0f) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            value = g / (1.0f + nvmoe_expf(-g)) * u;
+        } else {
+            value = nvmoe_round_bf16(g / (1.0f + nvmoe_expf(-g))) * u;
+        }
+        out[i] = (uint16_t)nvmoe_f32_to_bf16(value);
+    }
+}
+
+/* add_batch_bf16.comp.template:36-50 (op residual_add) */
+void oracle_add_bf16(const uint16_t* a, const uint16_t* b, uint16_t* out, uint64_t count) {
+    for (uint64_t i = 0; i < count; i++)
+        out[i] = (uint16_t)nvmoe_f32_to_bf16(nvmoe_bf16_to_f32(a[i]) + nvmoe_bf16_to_f32(b[i]));
+}

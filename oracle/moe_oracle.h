@@ -109,6 +109,27 @@ void oracle_sum_f32_scale_packed_bf16(const float* partials, const uint32_t* sca
                                       uint32_t participant_count, uint32_t lane_count,
                                       uint32_t elements_per_scale, uint32_t scale_bit_offset);
 
+/* resource_preselect_table_batch1.comp.template:35-97; returns the number of invalid tokens */
+int oracle_resource_preselect_table(const uint32_t* token_ids, const uint32_t* table_words,
+                                    uint32_t word_stride, uint32_t vocab, uint32_t routed,
+                                    uint32_t k, uint32_t always, uint32_t tokens,
+                                    uint32_t* selections, uint32_t* telemetry);
+
+/* moe_router_preselected_batch1_bf16.comp.template:56-91 */
+void oracle_route_preselected(const oracle_router* p, const uint32_t* logit_words,
+                              const uint32_t* selections, uint32_t tokens, uint32_t* routes);
+
+/* rms_norm_batch_bf16.comp.template:55-108 */
+void oracle_rms_norm(const uint16_t* input, const uint16_t* weight, uint16_t* output, uint32_t rows,
+                     uint32_t hidden, float eps, float weight_offset);
+
+/* bounded_silu_multiply_batch_bf16.comp.template:26-53 (limit > 0) or
+ * silu_multiply_batch_bf16.comp.template:24-52 (limit == 0) */
+void oracle_silu_multiply(const uint16_t* gate, const uint16_t* up, uint16_t* out, uint64_t count, float limit);
+
+/* add_batch_bf16.comp.template:36-50 */
+void oracle_add_bf16(const uint16_t* a, const uint16_t* b, uint16_t* out, uint64_t count);
+
 /* scalar helpers exported for table tests */
 uint32_t oracle_e2m1_to_e4m3(uint32_t nibble);
 float oracle_e2m1_value(uint32_t nibble);

@@ -350,6 +350,72 @@ def sum_f32_scale_packed_bf16(partials: np.ndarray, scales: np.ndarray, element_
     return out
 
 
+def resource_preselect_table(token_ids: np.ndarray, table: np.ndarray, routed: int, k: int, always: int = 0,
+                             telemetry: np.ndarray | None = None):
+    """Returns (selections [T, k + always] uint32, invalid token count). `table` is [vocab, k] int32 or int64."""
+    assert table.dtype in (np.int32, np.int64) and table.ndim == 2 and table.shape[1] == k
+    ids = _c(token_ids, np.uint32)
+    words = np.ascontiguousarray(table).view(np.uint32)
+    stride = table.dtype.itemsize // 4
+    out = np.zeros((ids.size, k + always), dtype=np.uint32)
+    lib().oracle_resource_preselect_table.restype = ctypes.c_int
+    bad = lib().oracle_resource_preselect_table(_p(ids), _p(words), ctypes.c_uint32(stride), ctypes.c_uint32(table.shape[0]),
+                                                ctypes.c_uint32(routed), ctypes.c_uint32(k), ctypes.c_uint32(always),
+                                                ctypes.c_uint32(ids.size), _p(out), _p(telemetry))
+    return out, bad
+
+
+def route_preselected(p: RouterParams, logit_words: np.ndarray, selections: np.ndarray) -> np.ndarray:
+    lw = _c(logit_words, np.uint32)
+    sel = _c(selections, np.uint32)
+    routes = np.zeros_like(sel)
+    cp = p.c()
+    lib().oracle_route_preselected(ctypes.byref(cp), _p(lw), _p(sel), ctypes.c_uint32(lw.shape[0]), _p(routes))
+    return routes
+
+
+def rms_norm(x_bf16: np.ndarray, weight_bf16: np.ndarray, eps: float, weight_offset: float = 0.0) -> np.ndarray:
+    x = _c(x_bf16, np.uint16)
+    w = _c(weight_bf16, np.uint16)
+    out = np.zeros_like(x)
+    lib().oracle_rms_norm(_p(x), _p(w), _p(out), ctypes.c_uint32(x.shape[0]), ctypes.c_uint32(x.shape[1]),
+                          ctypes.c_float(eps), ctypes.c_float(weight_offset))
+    return out
+
+
+def silu_multiply(gate_bf16: np.ndarray, up_bf16: np.ndarray, limit: float = 0.0) -> np.ndarray:
+    g, u = _c(gate_bf16, np.uint16), _c(up_bf16, np.uint16)
+    out = np.zeros_like(g)
+    lib().oracle_silu_multiply(_p(g), _p(u), _p(out), ctypes.c_uint64(g.size), ctypes.c_float(limit))
+    return out
+
+
+def add_bf16(a_bf16: np.ndarray, b_bf16: np.ndarray) -> np.ndarray:
+    a, b = _c(a_bf16, np.uint16), _c(b_bf16, np.uint16)
+    out = np.zeros_like(a)
+    lib().oracle_add_bf16(_p(a), _p(b), _p(out), ctypes.c_uint64(a.size))
+    return out
+
+
+def dense_linear_mxfp4(x_bf16: np.ndarray, weight: np.ndarray, scales: np.ndarray, act_block: int, tier: int = 1) -> np.ndarray:
+    """A dense linear over packaged MXFP4 weights [rows, cols/2] + [rows, cols/32] with the expert kernels'
+    arithmetic (activations quantised per `act_block`, f32 or f64 accumulation, one bf16 rounding): the down
+    projection of a single always-selected resource with route weight 1."""
+    x = _c(x_bf16, np.uint16)
+    tokens, cols = x.shape
+    rows = weight.shape[0]
+    ep = ExpertParams(hidden_size=rows, intermediate_size=cols, num_experts=1, experts_per_token=1, act_block=act_block, tier=tier)
+    frames = np.zeros((tokens, ep.frame_words), dtype=np.uint32)
+    frames[:, : cols // 2] = x.view(np.uint32)
+    frames[:, cols // 2] = np.arange(tokens, dtype=np.uint32)
+    routes = np.full((tokens, 1), 0x3F80 << 16, dtype=np.uint32)
+    w, sc = _c(weight, np.uint8), _c(scales, np.uint8)
+    out = np.zeros((tokens, 1, rows), dtype=np.uint16)
+    control = np.array([tokens, 0, 0, 0, 0, 0, 0], dtype=np.uint32)
+    down(ep, frames, routes, out, address_table([w, sc]), np.array([0, 1], dtype=np.uint32), control)
+    return out.reshape(tokens, rows)
+
+
 def dequant_mxfp4(packed: np.ndarray, scales: np.ndarray) -> np.ndarray:
     pk = _c(packed, np.uint8)
     sc = _c(scales, np.uint8)

@@ -109,27 +109,32 @@ def numpy_decoder() -> dict:
 
 
 def node_chain() -> dict:
+    """The node lists the compiler emits for the route-native MoE body (score-selected routing, and the
+    token-id-table form with its preselection node), with the packaged weight + scale parameter pairs."""
     from nerve.circuit_lowering_sparse_experts import independent_sparse_moe_body
 
     experts = list(range(4))
-    parameters = {}
+    parameters = {"moe_router": {}, "moe_router_selection_bias": {}, "moe_route_table": {}}
     for e in experts:
         for proj in ("w1", "w2", "w3"):
-            parameters[f"routed_expert_{e:03d}_{proj}_weight"] = {}
-            parameters[f"routed_expert_{e:03d}_{proj}_weight_scale"] = {}
-    parameters["moe_router_weight"] = {}
-    feed_forward = {
-        "routing": {"selection": "topk", "activation": "sigmoid", "normalize_selected": True,
-                    "routed_scaling_factor": 2.5},
-        "expert_ids": experts, "intermediate_size": 128, "hidden_size": 128,
-        "experts_per_token": 2, "swiglu_limit": 10.0,
-    }
-    try:
+            parameters[f"routed_expert_{e:03d}_{proj}"] = {}
+            parameters[f"routed_expert_{e:03d}_{proj}_scale"] = {}
+    for proj in ("w1", "w2", "w3"):
+        parameters[f"shared_expert_{proj}"] = {}
+        parameters[f"shared_expert_{proj}_scale"] = {}
+
+    def chain(selection: str) -> list:
+        feed_forward = {
+            "routing": {"selection": selection, "activation": "sigmoid", "normalize_selected": True,
+                        "routed_scaling_factor": 2.5},
+            "expert_ids": experts, "intermediate_size": 128, "hidden_size": 128,
+            "experts_per_token": 2, "swiglu_limit": 10.0,
+        }
         body = independent_sparse_moe_body(feed_forward=feed_forward, parameters=parameters)
-    except Exception as error:  # the helper wants a fuller parameter map than this sketch gives
-        return {"error": repr(error)}
-    return {"nodes": [{"id": n["id"], "op": n["op"], "inputs": n["inputs"], "outputs": n["outputs"],
-                       "params": n.get("params", []), "attrs": n.get("attrs", {})} for n in body]}
+        return [{"id": n["id"], "op": n["op"], "inputs": n["inputs"], "outputs": n["outputs"],
+                 "params": n.get("params", []), "attrs": n.get("attrs", {})} for n in body]
+
+    return {"nodes": chain("score_topk"), "token_id_table_nodes": chain("token_id_table")}
 
 
 def rust_known_answers() -> dict:
