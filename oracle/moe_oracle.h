@@ -30,7 +30,7 @@ typedef struct oracle_router {
     uint32_t routed_k;
     uint32_t always_count;
     float always_weight;
-    uint32_t kind;       /* 0 score_topk, 1 topk_softmax, 2 topk_routed */
+    uint32_t kind;       /* 0 score_topk, 1 topk_softmax, 2 topk_routed, 3 preselected (oracle_route_preselected) */
     uint32_t activation; /* 0 sigmoid, 1 softmax, 2 sqrt(softplus) */
     uint32_t normalize_selected;
     uint32_t bias_dtype; /* 0 none, 1 f32, 2 bf16 */

@@ -143,11 +143,11 @@ class RouterParams:
 
     @property
     def total_k(self) -> int:
-        return self.routed_k + (self.always_count if self.kind == 0 else 0)
+        return self.routed_k + (self.always_count if self.kind in (0, 3) else 0)
 
     @property
     def total_resources(self) -> int:
-        return self.routed_experts + (self.always_count if self.kind == 0 else 0)
+        return self.routed_experts + (self.always_count if self.kind in (0, 3) else 0)
 
     def telemetry_words(self) -> int:
         r = self.total_resources
@@ -155,7 +155,7 @@ class RouterParams:
 
     def c(self) -> _Router:
         return _Router(
-            self.routed_experts, self.routed_k, self.always_count if self.kind == 0 else 0,
+            self.routed_experts, self.routed_k, self.always_count if self.kind in (0, 3) else 0,
             self.always_weight, self.kind, self.activation, self.normalize_selected,
             self.bias_dtype, self.routed_scale, self.logit_softcap, self.n_group, self.topk_group,
         )
