@@ -39,7 +39,12 @@
  *   slot table      expert*P + parameter -> record index or 0xffffffff; P = 4 for gate/up
  *                   (w1, w1 scales, w3, w3 scales), P = 2 for down (w2, w2 scales)
  *   expert weight   I8 [rows][cols/2], low nibble = even column; scales F8_E8M0 [rows][cols/32]
- *                   (nerve/model_package_independent_experts.py:182-257)
+ *                   (nerve/model_package_independent_experts.py:182-257). A record whose representation
+ *                   word is 1 holds the same matrix pre-expanded to one E4M3 byte per element
+ *                   [rows][cols] (same scales); both matrices of a gate/up pair share one form. A native
+ *                   FP8 resource (geometry.native_fp8_resources) holds E4M3 [rows][cols] with E8M0 scales
+ *                   [ceil(rows/128)][ceil(cols/128)]
+ *                   (independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:166-228,250-355)
  *   telemetry       [R_total counts | R_total(R_total-1)/2 pair counts] u32
  */
 #ifndef NERVE_CUDA_MOE_H
@@ -121,6 +126,9 @@ typedef struct nvmoe_geometry {
     uint32_t down_tile_rows;     /* TILE_ROWS of the down shader (64) */
     float reduce_scale;          /* ROUTED_SCALE of moe_reduce (1.0 when the router already scaled) */
     uint32_t max_tokens;         /* largest batch_width any call will pass */
+    uint32_t native_fp8_resources; /* how many resources at the end of the id range hold native FP8 weights
+                                    (E4M3 [rows][cols] with one E8M0 scale per 128 x 128 block): the reference's
+                                    NATIVE_FP8_RESOURCE_START = total resources - this count. 0 = none. */
 } nvmoe_geometry;
 
 /* Fills a geometry with the reference defaults for the given sizes. */

@@ -135,14 +135,17 @@ class ResidentBuffer:
             self._h = None
 
 
-def address_table(device: CudaComputeDevice, resources: list) -> ResidentBuffer:
-    """32-byte records {address, byte_count, generation = 1, resident = 1, representation = 0}, the
+def address_table(device: CudaComputeDevice, resources: list, representations: list | None = None) -> ResidentBuffer:
+    """32-byte records {address, byte_count, generation = 1, resident = 1, representation}, the
     way the reference's conformance tests publish them
-    (runtime-rs/src/vulkan_compute/mxfp4_tests.rs:1633-1652)."""
+    (runtime-rs/src/vulkan_compute/mxfp4_tests.rs:1633-1652). representation 0 = compact MXFP4, 1 =
+    the same matrix pre-expanded to E4M3 bytes."""
     words = np.zeros(max(len(resources), 1) * 8, dtype=np.uint32)
     for slot, res in enumerate(resources):
         if res is None:
             continue
+        if representations is not None:
+            words[slot * 8 + 7] = representations[slot]
         address, count = res.device_address(), res.byte_capacity
         words[slot * 8 + 0] = address & 0xFFFFFFFF
         words[slot * 8 + 1] = address >> 32
@@ -170,19 +173,20 @@ class ExpertBank:
         self.resources = []
 
     @staticmethod
-    def upload(device: CudaComputeDevice, w1, s1, w3, s3, w2, s2, present=None) -> "ExpertBank":
+    def upload(device: CudaComputeDevice, w1, s1, w3, s3, w2, s2, present=None, expanded=()) -> "ExpertBank":
         n = len(w1)
         present = set(range(n) if present is None else present)
         per_expert = [[device.resident_buffer_from(t[e]) for t in (w1, s1, w3, s3, w2, s2)] if e in present else None
                       for e in range(n)]
-        return ExpertBank.from_resident(device, per_expert)
+        return ExpertBank.from_resident(device, per_expert, expanded)
 
     @staticmethod
-    def from_resident(device: CudaComputeDevice, per_expert: list) -> "ExpertBank":
+    def from_resident(device: CudaComputeDevice, per_expert: list, expanded=()) -> "ExpertBank":
         """Tables over tensors that are already resident: `per_expert[e]` is the expert's six buffers
-        (w1, w1 scales, w3, w3 scales, w2, w2 scales) or None for an expert this device does not hold."""
+        (w1, w1 scales, w3, w3 scales, w2, w2 scales) or None for an expert this device does not hold.
+        The weight records of the experts in `expanded` are tagged representation 1 (pre-expanded E4M3 bytes)."""
         n = len(per_expert)
-        gres, dres = [], []
+        gres, dres, greps, dreps = [], [], [], []
         gslots = np.full(n * 4, UNBOUND_PARAMETER_SLOT, dtype=np.uint32)
         dslots = np.full(n * 2, UNBOUND_PARAMETER_SLOT, dtype=np.uint32)
         for e, tensors in enumerate(per_expert):
@@ -191,11 +195,13 @@ class ExpertBank:
             for j, buf in enumerate(tensors[:4]):
                 gslots[e * 4 + j] = len(gres)
                 gres.append(buf)
+                greps.append(1 if (e in expanded and j % 2 == 0) else 0)
             for j, buf in enumerate(tensors[4:]):
                 dslots[e * 2 + j] = len(dres)
                 dres.append(buf)
-        return ExpertBank(gres + dres, address_table(device, gres), device.resident_buffer_from(gslots),
-                          address_table(device, dres), device.resident_buffer_from(dslots))
+                dreps.append(1 if (e in expanded and j % 2 == 0) else 0)
+        return ExpertBank(gres + dres, address_table(device, gres, greps), device.resident_buffer_from(gslots),
+                          address_table(device, dres, dreps), device.resident_buffer_from(dslots))
 
 
 def _load_framework_nccl() -> None:
@@ -262,6 +268,7 @@ def geometry_from_config(cfg: MoeConfig, max_tokens: int) -> capi.Geometry:
     g.swiglu_up_offset = cfg.swiglu_up_offset
     g.act_block = cfg.act_block
     g.max_tokens = max_tokens
+    g.native_fp8_resources = cfg.native_fp8_resources
     return g
 
 

@@ -26,7 +26,7 @@ class Geometry(ctypes.Structure):
         ("n_group", c_uint32), ("topk_group", c_uint32), ("swiglu_limit", c_float),
         ("swiglu_alpha", c_float), ("swiglu_up_offset", c_float), ("act_block", c_uint32),
         ("gate_tile_rows", c_uint32), ("down_tile_rows", c_uint32), ("reduce_scale", c_float),
-        ("max_tokens", c_uint32),
+        ("max_tokens", c_uint32), ("native_fp8_resources", c_uint32),
     ]
 
 

@@ -100,6 +100,7 @@ struct ExpertSet {
     uint64_t key[4] = {0, 0, 0, 0};  // address table uid, version, slot table uid, version
     bool cacheable = false;
     bool resolved = false;
+    bool resolved_for_tensor = false;  // the path the cached resolution was made for (its limits differ)
     bool tensor_ready = false;
     uint64_t last_use = 0;
     DeviceArray ptrs, derived, stamps, tmaps;
@@ -250,6 +251,8 @@ int validate_geometry(const nvmoe_geometry& g) {
         return bad("act_block %u must be a multiple of 32 dividing hidden and intermediate sizes", g.act_block);
     if (g.gate_tile_rows == 0u || g.down_tile_rows == 0u) return bad("tile rows must be positive");
     if (g.max_tokens == 0u) return bad("max_tokens is zero");
+    if (g.native_fp8_resources > g.routed_experts + g.always_count)
+        return bad("%u native FP8 resources among %u", g.native_fp8_resources, g.routed_experts + g.always_count);
     if ((uint64_t)g.max_tokens * (g.routed_k + g.always_count) > 0x7fffffffull) return bad("max_tokens * routes overflows");
     return NVMOE_OK;
 }
@@ -501,13 +504,17 @@ int nvmoe_plan_create(nvmoe_device* d, const nvmoe_geometry* geometry, nvmoe_pla
                 p->act_maps.release();  // no tensor maps on this system: the tensor path copies with cp.async
             }
         }
-        want(p->tmap_templates, 256);
+        want(p->tmap_templates, 512);
         if (err == cudaSuccess) {
-            unsigned char maps[256];
+            // per stage: the map of the compact form, then the map of the one-byte-per-element forms (left zero
+            // when the shape has no whole 128-column blocks: such resources are then treated as not resident)
+            unsigned char maps[512] = {0};
             p->tma[0] = tc_encode_weight_map(maps, p->tmap_templates.ptr, g.intermediate_size, g.hidden_size);
-            p->tma[1] = tc_encode_weight_map(maps + 128, p->tmap_templates.ptr, g.hidden_size, g.intermediate_size);
+            p->tma[1] = tc_encode_weight_map(maps + 256, p->tmap_templates.ptr, g.hidden_size, g.intermediate_size);
+            tc_encode_weight_map_bytes(maps + 128, p->tmap_templates.ptr, g.intermediate_size, g.hidden_size);
+            tc_encode_weight_map_bytes(maps + 384, p->tmap_templates.ptr, g.hidden_size, g.intermediate_size);
             if (!p->act_maps.ptr) p->tma[0] = p->tma[1] = false;
-            err = cudaMemcpyAsync(p->tmap_templates.ptr, maps, 256, cudaMemcpyHostToDevice, d->stream);
+            err = cudaMemcpyAsync(p->tmap_templates.ptr, maps, 512, cudaMemcpyHostToDevice, d->stream);
             if (err == cudaSuccess) err = cudaStreamSynchronize(d->stream);  // `maps` is a stack buffer
         }
     }
@@ -759,10 +766,11 @@ static int prepare_expert_set(nvmoe_plan* p, bool gate_up, const nvmoe_buffer* a
     NVMOE_TRY(expert_set_for(p, set, addresses, slots, tensor, &es));
     const uint64_t rows = gate_up ? g.intermediate_size : g.hidden_size;
     const uint64_t cols = gate_up ? g.hidden_size : g.intermediate_size;
-    if (!es->resolved) {
+    if (!es->resolved || es->resolved_for_tensor != tensor) {
+        es->resolved_for_tensor = tensor;
         launch_resolve_experts((const uint32_t*)addresses->ptr, (uint32_t)(addresses->bytes / 4u), (const uint32_t*)slots->ptr,
-                               (uint32_t)(slots->bytes / 4u), gate_up ? 4u : 2u, p->experts, rows * (cols / 2u),
-                               rows * (cols / 32u), es->derived.as<uint8_t>(),
+                               (uint32_t)(slots->bytes / 4u), gate_up ? 4u : 2u, p->experts, (uint32_t)rows, (uint32_t)cols,
+                               p->experts - g.native_fp8_resources, tensor, es->derived.as<uint8_t>(),
                                tc_derived_scale_bytes((uint32_t)rows, (uint32_t)cols), es->ptrs.as<ExpertPtrs>(), st);
         p->launches++;
         es->resolved = es->cacheable;
@@ -776,7 +784,7 @@ static int prepare_expert_set(nvmoe_plan* p, bool gate_up, const nvmoe_buffer* a
         launch_derive_scales_tc(el, gate_up, st);
         p->launches += 2;
         if (el.tmaps) {
-            launch_build_tensormaps_tc(el, gate_up, p->tmap_templates.as<uint8_t>() + set * 128, st);
+            launch_build_tensormaps_tc(el, gate_up, p->tmap_templates.as<uint8_t>() + set * 256, st);
             p->launches++;
         }
         es->tensor_ready = es->cacheable;

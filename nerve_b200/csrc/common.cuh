@@ -49,11 +49,18 @@ constexpr uint32_t kSortChunk = 256u;    // routes per block in the multi-block 
 // (address_record_is_resident + dynamic_expert_is_valid of
 // runtime-rs/shaders/independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:120-228).
 // A null w pointer means "not resident": every route to that expert is skipped.
+enum : uint32_t {
+    kFormatCompact = 0u,   // packaged MXFP4: E2M1 codes two per byte, E8M0 scale per 32 columns
+    kFormatExpanded = 1u,  // the same matrix pre-expanded to one E4M3 byte per element, same scales
+    kFormatNativeFp8 = 2u  // E4M3 bytes with one E8M0 scale per 128 x 128 block
+};
 struct ExpertPtrs {
     const uint8_t* w[2];   // gate/up: w1, w3;  down: w2, unused
-    const uint8_t* s[2];   // matching E8M0 scale rows as packaged: [rows][cols/32]
+    const uint8_t* s[2];   // matching E8M0 scales as packaged: [rows][cols/32], or [rows/128][cols/128] (native FP8)
     const uint8_t* ts[2];  // derived copy of the scales, tiled for tcgen05.cp: [row tile][K block][512 bytes]
     uint64_t gen[2];       // generation word of the scale records (what the derived copy is keyed on)
+    uint32_t format;       // kFormat* of the expert's matrices
+    uint32_t reserved;
 };
 
 // Everything a grouped expert kernel needs to find its work, produced by group_slots().
@@ -139,10 +146,13 @@ struct LayerSchedule {
 bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts);
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream);
 // validates the address/slot tables of every expert once per call
+// (rows, cols: logical shape of one matrix; experts from native_start on hold native FP8; with
+// whole_blocks_only an FP8-form matrix whose columns are not whole 128-blocks is treated as not resident:
+// the tensor path stages such a tail for the compact form only)
 void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                             uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
-                            uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
-                            size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream);
+                            uint32_t rows, uint32_t cols, uint32_t native_start, bool whole_blocks_only,
+                            uint8_t* derived_scales, size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream);
 // groups the compact slots the expert shaders would visit by expert (stable), skipping what the
 // shaders skip; writes grouped_routes and expert_offsets and, if `position` is given, the inverse
 // position[route] = place in grouped_routes (0xffffffff for routes that were skipped)

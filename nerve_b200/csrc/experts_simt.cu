@@ -63,6 +63,41 @@ __device__ __forceinline__ void row_dots(const uint8_t* __restrict__ wrow, const
     for (uint32_t t = 0; t < NT; t++) acc[t] = warp_butterfly_sum(acc[t]);
 }
 
+// The same for a matrix held as one E4M3 byte per element (pre-expanded or native FP8): a lane takes the 32
+// bytes of one 32-column group; the group's scale is its E8M0 byte of the packaged scale row, or, for native
+// FP8, the byte of the 128 x 128 block the group lies in
+// (independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:250-262,299-355).
+template <uint32_t NT>
+__device__ __forceinline__ void row_dots_fp8(const uint8_t* __restrict__ wrow, const uint8_t* __restrict__ scales, bool native,
+                                             uint32_t k_dim, const float* act, uint32_t lane, float (&acc)[NT]) {
+#pragma unroll
+    for (uint32_t t = 0; t < NT; t++) acc[t] = 0.0f;
+    const uint4* w16 = reinterpret_cast<const uint4*>(wrow);
+    for (uint32_t chunk = lane; chunk < k_dim / 32u; chunk += 32u) {
+        const uint4 lo = __ldg(w16 + 2u * chunk), hi = __ldg(w16 + 2u * chunk + 1u);
+        // native FP8 scales are plain exponent bytes (byte << 23), without the 2^-127 reading of a zero byte
+        const float ws = native ? __uint_as_float((uint32_t)__ldg(scales + chunk / 4u) << 23) : nvmoe_e8m0_to_f32(__ldg(scales + chunk));
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float part[NT];
+#pragma unroll
+        for (uint32_t t = 0; t < NT; t++) part[t] = 0.0f;
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; j++) {
+#pragma unroll
+            for (uint32_t b = 0; b < 4u; b++) {
+                const float w = nvmoe_e4m3_to_f32((words[j] >> (8u * b)) & 0xffu);
+                const uint32_t col = chunk * 32u + j * 4u + b;
+#pragma unroll
+                for (uint32_t t = 0; t < NT; t++) part[t] = fmaf(w, act[(size_t)t * k_dim + col], part[t]);
+            }
+        }
+#pragma unroll
+        for (uint32_t t = 0; t < NT; t++) acc[t] = fmaf(part[t], ws, acc[t]);
+    }
+#pragma unroll
+    for (uint32_t t = 0; t < NT; t++) acc[t] = warp_butterfly_sum(acc[t]);
+}
+
 __device__ __forceinline__ void fill_lut(Pair* lut) {
     for (uint32_t b = threadIdx.x; b < 256u; b += blockDim.x) {
         lut[b].lo = nvmoe_e2m1_to_f32(b & 0xfu);
@@ -123,11 +158,20 @@ __global__ void __launch_bounds__(kThreads) experts_simt_kernel(ExpertLaunch p, 
             const uint32_t row = tile * kRowsPerBlock + local;
             if (row >= out_rows) break;
             float a0[kTokensPerPass], a1[kTokensPerPass];
-            row_dots<kTokensPerPass>(ptrs.w[0] + (size_t)row * (k_dim / 2u), ptrs.s[0] + (size_t)row * (k_dim / 32u),
-                                     k_dim, act, lut, lane, a0);
-            if (GATE_UP)
-                row_dots<kTokensPerPass>(ptrs.w[1] + (size_t)row * (k_dim / 2u),
-                                         ptrs.s[1] + (size_t)row * (k_dim / 32u), k_dim, act, lut, lane, a1);
+            if (ptrs.format == kFormatCompact) {
+                row_dots<kTokensPerPass>(ptrs.w[0] + (size_t)row * (k_dim / 2u), ptrs.s[0] + (size_t)row * (k_dim / 32u),
+                                         k_dim, act, lut, lane, a0);
+                if (GATE_UP)
+                    row_dots<kTokensPerPass>(ptrs.w[1] + (size_t)row * (k_dim / 2u),
+                                             ptrs.s[1] + (size_t)row * (k_dim / 32u), k_dim, act, lut, lane, a1);
+            } else {
+                const bool native = ptrs.format == kFormatNativeFp8;
+                // scale bytes of this row: its own 32-column groups, or the blocks of its 128-row band
+                const size_t scale_row = native ? (size_t)(row / 128u) * ((k_dim + 127u) / 128u) : (size_t)row * (k_dim / 32u);
+                row_dots_fp8<kTokensPerPass>(ptrs.w[0] + (size_t)row * k_dim, ptrs.s[0] + scale_row, native, k_dim, act, lane, a0);
+                if (GATE_UP)
+                    row_dots_fp8<kTokensPerPass>(ptrs.w[1] + (size_t)row * k_dim, ptrs.s[1] + scale_row, native, k_dim, act, lane, a1);
+            }
             if (lane < count) {
                 // lane t finishes token t of the pass (all lanes hold every sum after the butterfly)
                 float g = 0.0f, u = 0.0f;

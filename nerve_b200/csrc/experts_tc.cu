@@ -132,6 +132,7 @@ struct Barriers {
     uint64_t drain;
     uint32_t tmem_base;
     uint32_t abort;
+    uint32_t format[kMaxStages];  // kFormat* of the weights staged in each slot (written before the slot's arrival)
 };
 
 // TRACE compiles the diagnostics in (cycle counters of CTA 0, per-CTA global-timer stamps): the
@@ -222,7 +223,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             // (The prefetch only loads: whatever is computed from a loaded value is computed when the tile
             // starts, because a thread stalls at the first instruction that needs a load's result.)
             struct Meta {
-                uint32_t pair, m_tile, expert_begin;
+                uint32_t pair, m_tile, expert_begin, format;
                 const uint8_t* ts[C::kSources];
             };
             auto entry_of = [&](uint32_t tile) {
@@ -235,6 +236,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 m.m_tile = tile % m_tiles;
                 const uint32_t expert = pair >> 16;
                 m.expert_begin = __ldg(p.work.expert_offsets + expert);
+                m.format = p.work.experts[expert].format;
 #pragma unroll
                 for (uint32_t src = 0; src < C::kSources; src++) m.ts[src] = p.work.experts[expert].ts[src];
             };
@@ -273,7 +275,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                     } else {
                     // token rows (zeros past the edge of K) and weight scale blocks of every K block present
                     const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
-                    mbar_arrive_expect_tx(&bars->full[slot], whole * C::kMatrices * kTmaBoxBytes +
+                    // a box of one-byte elements brings twice the bytes of a box of packed 4-bit codes
+                    const uint32_t box_bytes = cur.format == kFormatCompact ? kTmaBoxBytes : 2u * kTmaBoxBytes;
+                    *reinterpret_cast<volatile uint32_t*>(&bars->format[slot]) = cur.format;
+                    mbar_arrive_expect_tx(&bars->full[slot], whole * C::kMatrices * box_bytes +
                                                                  present * (C::kBTileBytes + C::kMatrices * kScaleBlockBytes));
                     for (uint32_t sub = 0; sub < present; sub++) {
                         const uint32_t kb = ks * C::kSub + sub;
@@ -325,7 +330,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             const uint8_t* ts[C::kMatrices];
             uint32_t code_rows[kTokenPasses];  // activation row of token my_r + kRowsPerPass i
             uint32_t scale_row;                // activation row of token pt
-            uint32_t valid, m_tile, first;
+            uint32_t valid, m_tile, first, format;
         };
         auto load_meta = [&](uint32_t tile, Meta& m) {
             const uint32_t pair = __ldg(list.tiles + tile / m_tiles);
@@ -336,6 +341,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             m.valid = min(N_TILE, e_end - first);
             m.first = first;
             const ExpertPtrs* ptrs = p.work.experts + expert;
+            m.format = ptrs->format;
 #pragma unroll
             for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
                 m.w[mx] = ptrs->w[C::source_of(mx)];
@@ -359,13 +365,16 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             // this thread's first weight row of each matrix of the tile; its other rows are kRowsPerPass apart
             const uint8_t* wcol[C::kMatrices];
             uint32_t rows_here[C::kMatrices];
+            // a matrix of one-byte elements (pre-expanded or native FP8) has rows, and pieces of 16 elements, twice as long
+            const bool bytes_form = cur.format != kFormatCompact;
+            const uint32_t form_row_bytes = bytes_form ? 2u * row_bytes : row_bytes;
 #pragma unroll
             for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
                 const uint32_t row0 = cur.m_tile * C::kTileRows + C::row_shift(mx);
                 rows_here[mx] = row0 < out_rows ? min(kBlockM, out_rows - row0) : 0u;
-                wcol[mx] = cur.w[mx] + (size_t)(row0 + my_r) * row_bytes + my_c * 8u;
+                wcol[mx] = cur.w[mx] + (size_t)(row0 + my_r) * form_row_bytes + my_c * (bytes_form ? 16u : 8u);
             }
-            const size_t row_step = (size_t)kRowsPerPass * row_bytes;
+            const size_t row_step = (size_t)kRowsPerPass * form_row_bytes;
             for (uint32_t ks = 0; ks < k_stages; ks++, it++) {
                 const long long w0 = TRACE ? clock64() : 0;
                 if (!mbar_wait_warp(&bars->empty[slot], empty_parity, abort_flag, wait_limit)) {
@@ -386,12 +395,16 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
                     const uint32_t a_dst = smem_u32(stage + mx * kATileBytes) + my_dst;
-                    const uint8_t* src = wcol[mx] + kb * 64u;
+                    const uint8_t* src = wcol[mx] + kb * (bytes_form ? 128u : 64u);
 #pragma unroll
                     for (uint32_t i = 0; i < kBlockM / kRowsPerPass; i++) {
                         // rows my_r + kRowsPerPass i share (row & 7), so the swizzled offset only moves by whole rows
                         const bool ok = chunk_ok && (my_r + kRowsPerPass * i < rows_here[mx]);
-                        cp_async_8(a_dst + i * (kRowsPerPass * 128u), ok ? src + i * row_step : cur.w[mx], ok ? 8u : 0u);
+                        if (bytes_form) {
+                            cp_async_16(a_dst + i * (kRowsPerPass * 128u), ok ? src + i * row_step : cur.w[mx], ok ? 16u : 0u);
+                        } else {
+                            cp_async_8(a_dst + i * (kRowsPerPass * 128u), ok ? src + i * row_step : cur.w[mx], ok ? 8u : 0u);
+                        }
                     }
                 }
                 }
@@ -434,6 +447,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                                ok ? 4u : 0u);
                 }
                 }
+                if (!USE_TMA && pt == 0u) *reinterpret_cast<volatile uint32_t*>(&bars->format[slot]) = cur.format;
                 // the arrival fires when this thread's copies have landed; the thread moves on at once
                 cp_async_arrive_noinc(&bars->full[slot]);
                 if (++slot == C::kStages) {
@@ -454,7 +468,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             // One thread feeds the tensor pipe, and a lone thread retires an instruction every few
             // cycles at best: everything that does not depend on the stage is computed once, the four
             // K steps of a stage are unrolled with compile-time descriptors offsets and scale ids.
-            constexpr uint32_t kIdesc = idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, kBlockM, N_TILE);
+            constexpr uint32_t kIdescCompact = idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, kBlockM, N_TILE);
+            constexpr uint32_t kIdescBytes = idesc_mxf8f6f4(kFmtE4M3, kFmtE4M3, kBlockM, N_TILE);  // weights as E4M3 bytes
             constexpr uint32_t kStageUnits = C::kStageBytes >> 4;  // descriptor start addresses count 16 bytes
             constexpr uint32_t kSubUnits = C::kSubBytes >> 4;
             const uint32_t base = smem_u32(smem);
@@ -484,6 +499,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                     }
                     if (TRACE) trace_full += clock64() - f0;
                     tc_fence_after();
+                    const uint32_t kIdesc = *reinterpret_cast<volatile uint32_t*>(&bars->format[slot]) == kFormatCompact ? kIdescCompact
+                                                                                                                 : kIdescBytes;
 #pragma unroll
                     for (uint32_t sub = 0; sub < C::kSub; sub++) {
                     const uint32_t kb = ks * C::kSub + sub;
@@ -696,7 +713,10 @@ __global__ void __launch_bounds__(128) derive_scales_kernel(const ExpertPtrs* ex
     uint8_t* out = const_cast<uint8_t*>(ptrs.ts[mx]) + (size_t)m_tile * k_blocks * kScaleBlockBytes + (r & 31u) * 16u + (r >> 5) * 4u;
     for (uint32_t kb = 0; kb < k_blocks; kb++) {
         uint32_t word = 0x7f7f7f7fu;
-        if (row < rows) {
+        if (row < rows && ptrs.format == kFormatNativeFp8) {
+            // one exponent byte per 128 x 128 block, repeated over the block's four 32-column groups
+            word = 0x01010101u * (uint32_t)ptrs.s[mx][(size_t)(row / 128u) * k_blocks + kb];
+        } else if (row < rows) {
             word = 0u;
             for (uint32_t j = 0; j < 4u; j++) {
                 const uint32_t c = kb * 4u + j;
@@ -724,7 +744,9 @@ __global__ void __launch_bounds__(32) build_tensormaps_kernel(const ExpertPtrs* 
     const uint32_t e = blockIdx.x / matrices, mx = blockIdx.x % matrices;
     const uint8_t* w = experts[e].w[mx];
     if (experts[e].w[0] == nullptr || w == nullptr) return;
-    reinterpret_cast<uint32_t*>(sm)[threadIdx.x] = reinterpret_cast<const uint32_t*>(templ)[threadIdx.x];
+    // `templ` holds the map of the compact form followed by the map of the one-byte-per-element forms
+    const uint8_t* mine = templ + (experts[e].format == kFormatCompact ? 0u : 128u);
+    reinterpret_cast<uint32_t*>(sm)[threadIdx.x] = reinterpret_cast<const uint32_t*>(mine)[threadIdx.x];
     __syncwarp();
     if (threadIdx.x == 0u) tensormap_replace_address(sm, w);
     __syncwarp();
@@ -852,6 +874,25 @@ bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows,
     const cuuint32_t estr[3] = {1u, 1u, 1u};
     CUtensorMap map;
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, any_device_address, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::memcpy(map128, &map, 128);
+    return true;
+}
+
+bool tc_encode_weight_map_bytes(void* map128, void* any_device_address, uint32_t rows, uint32_t cols) {
+    // One E4M3 byte per element, seen like the compact form as {128 elements, cols/128 K blocks, rows}: the
+    // same box coordinates fetch the same operand tile, now without padding.
+    if (cols < kBlockK || cols % kBlockK != 0u) return false;
+    EncodeFn encode = tensor_map_encoder();
+    if (!encode) return false;
+    const cuuint64_t dims[3] = {kBlockK, cols / kBlockK, rows};
+    const cuuint64_t strides[2] = {kBlockK, cols};
+    const cuuint32_t box[3] = {kBlockK, 1u, kBlockM};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUtensorMap map;
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, any_device_address, dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;

@@ -13,6 +13,8 @@ void tc_configure_kernels();
 // Encodes the template tensor map of a [rows][cols] weight matrix (any 32-byte aligned device address
 // will do: it is replaced per expert). False when the shape cannot use TMA.
 bool tc_encode_weight_map(void* map128, void* any_device_address, uint32_t rows, uint32_t cols);
+// The same for a matrix held as one E4M3 byte per element (pre-expanded or native FP8 resources).
+bool tc_encode_weight_map_bytes(void* map128, void* any_device_address, uint32_t rows, uint32_t cols);
 // Encodes the tensor map of an expert-grouped activation matrix [rows][cols] of E4M3 bytes with a box of
 // n_tile rows x 128 bytes (the operand tile of one K block). False when tensor maps are unavailable.
 bool tc_encode_activation_map(void* map128, void* base, uint32_t rows, uint32_t cols, uint32_t n_tile);

@@ -373,16 +373,31 @@ __global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* route
 }
 
 // address_record_is_resident + dynamic_parameter_record_is_valid for every expert, once per call
+// (dynamic_expert_is_valid of independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:166-228: a weight record's
+// representation word is 0 (compact) or 1 (pre-expanded FP8), the same for both matrices of a pair; resources
+// from native_start on are native FP8 and must say 0)
 __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                                        uint32_t slot_words, uint32_t params, uint32_t num_experts,
-                                       uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
-                                       size_t derived_matrix_bytes, ExpertPtrs* out) {
+                                       uint32_t rows, uint32_t cols, uint32_t native_start, bool whole_blocks_only,
+                                       uint8_t* derived_scales, size_t derived_matrix_bytes, ExpertPtrs* out) {
     uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= num_experts) return;
-    ExpertPtrs r{{nullptr, nullptr}, {nullptr, nullptr}, {nullptr, nullptr}, {0u, 0u}};
+    ExpertPtrs r{{nullptr, nullptr}, {nullptr, nullptr}, {nullptr, nullptr}, {0u, 0u}, kFormatCompact, 0u};
     bool ok = true;
     const uint8_t* ptrs[4] = {nullptr, nullptr, nullptr, nullptr};
     uint64_t gens[4] = {0u, 0u, 0u, 0u};
+    const bool native = e >= native_start;
+    // the form of the expert's matrices: the representation word of its first weight record
+    uint32_t format = native ? kFormatNativeFp8 : kFormatCompact;
+    if (!native && (uint64_t)e * params < slot_words) {
+        const uint32_t slot = slots[(uint64_t)e * params];
+        if (slot != kUnboundSlot && slot < address_words / kRecordWords && addresses[(size_t)slot * kRecordWords + 7u] == 1u)
+            format = kFormatExpanded;
+    }
+    if (format != kFormatCompact && whole_blocks_only && cols % 128u != 0u) ok = false;
+    const uint64_t weight_bytes = format == kFormatCompact ? (uint64_t)rows * (cols / 2u) : (uint64_t)rows * cols;
+    const uint64_t scale_bytes = format == kFormatNativeFp8 ? (uint64_t)((rows + 127u) / 128u) * ((cols + 127u) / 128u)
+                                                            : (uint64_t)rows * (cols / 32u);
     for (uint32_t j = 0; j < params && ok; j++) {
         uint64_t index = (uint64_t)e * params + j;
         if (index >= slot_words) {
@@ -398,10 +413,14 @@ __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t addre
         uint64_t address = (uint64_t)rec[0] | ((uint64_t)rec[1] << 32);
         uint64_t bytes = (uint64_t)rec[2] | ((uint64_t)rec[3] << 32);
         uint64_t required = (j & 1u) ? scale_bytes : weight_bytes;
-        // representation 0 (compact MXFP4) is the only one built; anything else fails closed
-        // and the kernels read rows with 16-byte loads and TMA boxes, so the shader's 4-byte rule becomes 32
-        if (address == 0u || (address & 31u) != 0u || bytes < required || (rec[4] | rec[5]) == 0u ||
-            rec[6] != 1u || rec[7] != 0u) {
+        // what the record must say about its form: weights of a compact or native resource 0, of a pre-expanded one 1
+        // (a pair that disagrees fails closed); scale records are not looked at, as in the shader
+        const uint32_t expected = format == kFormatExpanded ? 1u : 0u;
+        // the kernels read rows with 16-byte loads and TMA boxes, so the shader's 4-byte address rule becomes 32
+        // (native FP8 scale blocks are read byte by byte: 4 as in the shader)
+        const uint64_t align_mask = ((j & 1u) && format == kFormatNativeFp8) ? 3u : 31u;
+        if (address == 0u || (address & align_mask) != 0u || bytes < required || (rec[4] | rec[5]) == 0u ||
+            rec[6] != 1u || (!(j & 1u) && rec[7] != expected)) {
             ok = false;
             break;
         }
@@ -416,6 +435,7 @@ __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t addre
         r.w[1] = params == 4u ? ptrs[2] : nullptr;
         r.s[1] = params == 4u ? ptrs[3] : nullptr;
         r.gen[1] = params == 4u ? gens[3] : 0u;
+        r.format = format;
         if (derived_scales) {
             r.ts[0] = derived_scales + ((size_t)e * matrices) * derived_matrix_bytes;
             r.ts[1] = params == 4u ? r.ts[0] + derived_matrix_bytes : nullptr;
@@ -983,11 +1003,11 @@ void launch_route_count(const uint32_t* routes, const uint32_t* slots, uint32_t 
 
 void launch_resolve_experts(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
                             uint32_t slot_words, uint32_t params_per_resource, uint32_t num_experts,
-                            uint64_t weight_bytes, uint64_t scale_bytes, uint8_t* derived_scales,
-                            size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream) {
+                            uint32_t rows, uint32_t cols, uint32_t native_start, bool whole_blocks_only,
+                            uint8_t* derived_scales, size_t derived_matrix_bytes, ExpertPtrs* out, cudaStream_t stream) {
     resolve_experts_kernel<<<(num_experts + 127u) / 128u, 128, 0, stream>>>(
-        addresses, address_words, slots, slot_words, params_per_resource, num_experts, weight_bytes,
-        scale_bytes, derived_scales, derived_matrix_bytes, out);
+        addresses, address_words, slots, slot_words, params_per_resource, num_experts, rows, cols, native_start,
+        whole_blocks_only, derived_scales, derived_matrix_bytes, out);
 }
 
 void launch_group_slots(const uint32_t* routes, const uint32_t* intermediates, const uint32_t* control,

@@ -50,6 +50,7 @@ class MoeConfig:
     act_block: int = 128
     zipf_s: float = 0.0
     logit_softcap: float = 0.0
+    native_fp8_resources: int = 0      # resources at the end of the id range held as native FP8
 
     @property
     def total_k(self) -> int:
@@ -169,6 +170,36 @@ def expert_tensors(cfg: MoeConfig, seed: int, expert: int) -> tuple:
     return (g.integers(0, 256, (I, H // 2), dtype=np.uint8), g.integers(121, 128, (I, H // 32), dtype=np.uint8),
             g.integers(0, 256, (I, H // 2), dtype=np.uint8), g.integers(121, 128, (I, H // 32), dtype=np.uint8),
             g.integers(0, 256, (H, I // 2), dtype=np.uint8), g.integers(121, 128, (H, I // 32), dtype=np.uint8))
+
+
+E2M1_TO_E4M3 = np.array([0x00, 0x30, 0x38, 0x3C, 0x40, 0x44, 0x48, 0x4C, 0x80, 0xB0, 0xB8, 0xBC, 0xC0, 0xC4, 0xC8, 0xCC], dtype=np.uint8)
+
+
+def expand_to_e4m3(packed: np.ndarray) -> np.ndarray:
+    """The pre-expanded form of a packaged MXFP4 matrix: every E2M1 code as the E4M3 byte of the same value,
+    low nibble first ([rows, cols/2] -> [rows, cols])."""
+    out = np.empty((packed.shape[0], packed.shape[1] * 2), dtype=np.uint8)
+    out[:, 0::2] = E2M1_TO_E4M3[packed & 0xF]
+    out[:, 1::2] = E2M1_TO_E4M3[packed >> 4]
+    return out
+
+
+def native_fp8_tensors(cfg: MoeConfig, seed: int, expert: int) -> tuple:
+    """A native FP8 resource: E4M3 weights [rows, cols] (finite codes only) with one E8M0 exponent byte per
+    128 x 128 block, in the six-tensor order of `expert_tensors`."""
+    H, I = cfg.hidden, cfg.intermediate
+    g = _stream(seed, f"native_fp8_expert{expert}")
+
+    def matrix(rows, cols):
+        codes = g.integers(0, 256, (rows, cols), dtype=np.uint8)
+        codes[(codes & 0x7F) == 0x7F] = 0x38  # S.1111.111 is NaN in E4M3
+        scales = g.integers(112, 119, (-(-rows // 128), -(-cols // 128)), dtype=np.uint8)
+        return codes, scales
+
+    w1, s1 = matrix(I, H)
+    w3, s3 = matrix(I, H)
+    w2, s2 = matrix(H, I)
+    return w1, s1, w3, s3, w2, s2
 
 
 def expert_tensor_lists(cfg: MoeConfig, seed: int, experts, placeholder=None) -> dict:

@@ -541,7 +541,11 @@ void oracle_quantize_fp8(const uint16_t* input, uint32_t rows, uint32_t columns,
 typedef struct record_view {
     const uint8_t* ptr;
     uint64_t bytes;
+    uint32_t representation;
 } record_view;
+
+/* how an expert's matrices are held (independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:166-228,250-355) */
+enum { FORM_COMPACT = 0, FORM_EXPANDED = 1, FORM_NATIVE_FP8 = 2 };
 
 /* address_record_is_resident + dynamic_parameter_record_is_valid
  * (independent_sparse_moe_gate_up_batch1_mxfp4.comp.template:120-165) */
@@ -560,9 +564,41 @@ static int resolve_parameter(const uint32_t* addresses, uint32_t address_words,
     if (address == 0u || (address & 3u) != 0u || bytes < required || generation_nonzero == 0u ||
         rec[6] != 1u)
         return 0;
-    if (rec[7] != 0u) return 0; /* only the compact MXFP4 representation is built */
     out->ptr = (const uint8_t*)(uintptr_t)address;
     out->bytes = bytes;
+    out->representation = rec[7];
+    return 1;
+}
+
+/* representation word of a parameter's record, 0 when the slot names no record (dynamic_parameter_representation, :150-157) */
+static uint32_t parameter_representation(const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
+                                         uint32_t slot_words, uint32_t params, uint32_t expert, uint32_t parameter) {
+    uint64_t index = (uint64_t)expert * params + parameter;
+    if (index >= slot_words) return 0u;
+    uint32_t slot = slots[index];
+    if (slot == UNBOUND_SLOT || slot >= address_words / RECORD_WORDS) return 0u;
+    return addresses[(size_t)slot * RECORD_WORDS + 7u];
+}
+
+/* The form of an expert's matrices and the bytes its weight and scale records must hold (:184-228).
+ * Returns 0 when the records' representation words rule the expert out. */
+static int expert_form(const oracle_expert* p, const uint32_t* addresses, uint32_t address_words, const uint32_t* slots,
+                       uint32_t slot_words, uint32_t params, uint32_t expert, uint32_t rows, uint32_t cols,
+                       uint32_t* form, uint64_t* weight_bytes, uint64_t* scale_bytes) {
+    uint32_t native_start = p->native_fp8_start ? p->native_fp8_start : p->num_experts;
+    int native = expert >= native_start;
+    uint32_t rep0 = parameter_representation(addresses, address_words, slots, slot_words, params, expert, 0u);
+    uint32_t rep1 = params == 4u ? parameter_representation(addresses, address_words, slots, slot_words, params, expert, 2u) : rep0;
+    if (native) {
+        if (rep0 != 0u || rep1 != 0u) return 0;
+        *form = FORM_NATIVE_FP8;
+    } else {
+        if (rep0 > 1u || rep1 > 1u || rep0 != rep1) return 0;
+        *form = rep0 == 1u ? FORM_EXPANDED : FORM_COMPACT;
+    }
+    *weight_bytes = *form == FORM_COMPACT ? (uint64_t)rows * (cols / 2u) : (uint64_t)rows * cols;
+    *scale_bytes = *form == FORM_NATIVE_FP8 ? (uint64_t)((rows + 127u) / 128u) * ((cols + 127u) / 128u)
+                                            : (uint64_t)rows * (cols / 32u);
     return 1;
 }
 
@@ -630,6 +666,47 @@ static float row_dot(const uint8_t* wrow, const uint8_t* srow, uint32_t columns,
     return (float)total;
 }
 
+/* A row of a matrix in any of the three forms: for the two one-byte-per-element forms the weight value
+ * is its E4M3 byte decoded (:250-262) and the scale of a 32-column group its E8M0 byte of the packaged
+ * scale row, or, for native FP8, the exponent byte of the 128 x 128 block the group lies in (:299-355:
+ * byte << 23, where a zero byte gives 0). */
+static float matrix_row_dot(const record_view* w, const record_view* s, uint32_t form, uint32_t row, uint32_t columns,
+                            uint32_t block, const float* af, const float* scales, uint32_t tier) {
+    if (form == FORM_COMPACT)
+        return row_dot(w->ptr + (size_t)row * (columns / 2u), s->ptr + (size_t)row * (columns / 32u), columns, block, af, scales, tier);
+    const uint8_t* wrow = w->ptr + (size_t)row * columns;
+    uint32_t native_columns = (columns + 127u) / 128u;
+    if (tier == 0u) {
+        float lanes[64];
+        uint32_t words = columns / 4u;
+        for (uint32_t lane = 0; lane < 64u; lane++) {
+            float acc = 0.0f;
+            for (uint32_t word = lane; word < words; word += 64u) {
+                uint32_t column = word * 4u;
+                double dot = 0.0;
+                for (uint32_t j = 0; j < 4u; j++) dot += (double)af[column + j] * g_e4m3_lut[wrow[column + j]];
+                float ws = form == FORM_NATIVE_FP8
+                               ? nvmoe_bits_f32((uint32_t)s->ptr[(size_t)(row / 128u) * native_columns + column / 128u] << 23)
+                               : nvmoe_e8m0_to_f32(s->ptr[(size_t)row * (columns / 32u) + column / 32u]);
+                acc = fmaf((float)dot, scales[column / block] * ws, acc);
+            }
+            lanes[lane] = acc;
+        }
+        return butterfly_sum64(lanes);
+    }
+    double total = 0.0;
+    for (uint32_t b32 = 0; b32 < columns / 32u; b32++) {
+        double dot = 0.0;
+        for (uint32_t j = 0; j < 32u; j++) dot += (double)af[b32 * 32u + j] * g_e4m3_lut[wrow[b32 * 32u + j]];
+        double sa = scales ? (double)scales[(b32 * 32u) / block] : 1.0;
+        double ws = form == FORM_NATIVE_FP8
+                        ? (double)nvmoe_bits_f32((uint32_t)s->ptr[(size_t)(row / 128u) * native_columns + b32 / 4u] << 23)
+                        : (double)nvmoe_e8m0_to_f32(s->ptr[(size_t)row * (columns / 32u) + b32]);
+        total += dot * sa * ws;
+    }
+    return (float)total;
+}
+
 /* Decode of one compact slot exactly as both expert shaders do (:643-669). Returns 0 to skip. */
 static int decode_slot(const oracle_expert* p, const uint32_t* intermediates,
                        const uint32_t* routes, const uint32_t* control, uint32_t linear_route,
@@ -683,7 +760,10 @@ static void gate_up_impl(const oracle_expert* p, const uint16_t* hidden, const u
             uint32_t expert = packed & 0xffffu;
             if (expert >= p->num_experts) continue;
             record_view w1, s1, w3, s3;
-            uint64_t weight_bytes = (uint64_t)I * (H / 2u), scale_bytes = (uint64_t)I * (H / 32u);
+            uint64_t weight_bytes, scale_bytes;
+            uint32_t form;
+            if (!expert_form(p, addresses, address_words, slots, slot_words, 4u, expert, I, H, &form, &weight_bytes, &scale_bytes))
+                continue;
             if (!resolve_parameter(addresses, address_words, slots, slot_words, 4u, expert, 0u, weight_bytes, &w1) ||
                 !resolve_parameter(addresses, address_words, slots, slot_words, 4u, expert, 1u, scale_bytes, &s1) ||
                 !resolve_parameter(addresses, address_words, slots, slot_words, 4u, expert, 2u, weight_bytes, &w3) ||
@@ -708,8 +788,8 @@ static void gate_up_impl(const oracle_expert* p, const uint16_t* hidden, const u
             uint16_t* out = (uint16_t*)(intermediates + (size_t)batch_index * frame_words + (size_t)route * (I / 2u));
             for (uint32_t row = 0; row < I; row++) {
                 uint32_t tier = sa ? (p->tier == 2u ? 1u : p->tier) : 2u;
-                float gate = row_dot(w1.ptr + (size_t)row * (H / 2u), s1.ptr + (size_t)row * (H / 32u), H, block, af, sa, tier);
-                float up = row_dot(w3.ptr + (size_t)row * (H / 2u), s3.ptr + (size_t)row * (H / 32u), H, block, af, sa, tier);
+                float gate = matrix_row_dot(&w1, &s1, form, row, H, block, af, sa, tier);
+                float up = matrix_row_dot(&w3, &s3, form, row, H, block, af, sa, tier);
                 out[row] = (uint16_t)nvmoe_f32_to_bf16(
                     nvmoe_swiglu(gate, up, p->swiglu_limit, p->swiglu_alpha, p->swiglu_up_offset));
             }
@@ -763,8 +843,12 @@ void oracle_down(const oracle_expert* p, const uint32_t* intermediates, const ui
             uint32_t expert = packed & 0xffffu;
             if (expert >= p->num_experts) continue;
             record_view w2, s2;
-            if (!resolve_parameter(addresses, address_words, slots, slot_words, 2u, expert, 0u, (uint64_t)H * (I / 2u), &w2) ||
-                !resolve_parameter(addresses, address_words, slots, slot_words, 2u, expert, 1u, (uint64_t)H * (I / 32u), &s2))
+            uint64_t weight_bytes, scale_bytes;
+            uint32_t form;
+            if (!expert_form(p, addresses, address_words, slots, slot_words, 2u, expert, H, I, &form, &weight_bytes, &scale_bytes))
+                continue;
+            if (!resolve_parameter(addresses, address_words, slots, slot_words, 2u, expert, 0u, weight_bytes, &w2) ||
+                !resolve_parameter(addresses, address_words, slots, slot_words, 2u, expert, 1u, scale_bytes, &s2))
                 continue;
             float route_weight = nvmoe_bf16_to_f32(packed >> 16);
             const uint16_t* in = (const uint16_t*)(intermediates + (size_t)batch_index * frame_words + (size_t)route * (I / 2u));
@@ -778,7 +862,7 @@ void oracle_down(const oracle_expert* p, const uint32_t* intermediates, const ui
             }
             uint16_t* out = outputs + ((size_t)batch_index * K + route) * H;
             for (uint32_t row = 0; row < H; row++) {
-                float value = row_dot(w2.ptr + (size_t)row * (I / 2u), s2.ptr + (size_t)row * (I / 32u), I, block, af, sa, p->tier);
+                float value = matrix_row_dot(&w2, &s2, form, row, I, block, af, sa, p->tier);
                 out[row] = (uint16_t)nvmoe_f32_to_bf16(value * route_weight);
             }
         }

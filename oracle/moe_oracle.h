@@ -51,6 +51,8 @@ typedef struct oracle_expert {
     float swiglu_up_offset;
     uint32_t act_block;
     uint32_t tier; /* 0 faithful f32 order, 1 same operands with f64 accumulation, 2 ideal (bf16 activations, f64) */
+    uint32_t native_fp8_start; /* NATIVE_FP8_RESOURCE_START: resources from here on hold E4M3 weights with one E8M0
+                                  scale per 128 x 128 block; num_experts = none (a zero is read as none too) */
 } oracle_expert;
 
 /* linear_bf16.comp.template:39-95; with a non-null bias, linear_bias_bf16.comp.template:31-84 */

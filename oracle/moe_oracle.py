@@ -64,6 +64,7 @@ class _Expert(ctypes.Structure):
         ("swiglu_up_offset", ctypes.c_float),
         ("act_block", ctypes.c_uint32),
         ("tier", ctypes.c_uint32),
+        ("native_fp8_start", ctypes.c_uint32),
     ]
 
 
@@ -173,6 +174,7 @@ class ExpertParams:
     swiglu_up_offset: float = 0.0
     act_block: int = 128
     tier: int = 1
+    native_fp8_start: int = 0  # resources from here on hold native FP8 weights (0 = none)
 
     @property
     def frame_words(self) -> int:
@@ -186,7 +188,7 @@ class ExpertParams:
         return _Expert(
             self.hidden_size, self.intermediate_size, self.num_experts, self.experts_per_token,
             self.tile_rows, self.swiglu_limit, self.swiglu_alpha, self.swiglu_up_offset,
-            self.act_block, self.tier,
+            self.act_block, self.tier, self.native_fp8_start,
         )
 
 
@@ -267,12 +269,14 @@ def quantize_fp8(x_bf16: np.ndarray, block: int):
     return q, scales
 
 
-def address_table(resources: list[np.ndarray | None]) -> np.ndarray:
-    """32-byte records {address, byte_count, generation=1, resident=1, representation=0} with
+def address_table(resources: list[np.ndarray | None], representations: list | None = None) -> np.ndarray:
+    """32-byte records {address, byte_count, generation=1, resident=1, representation} with
     host pointers, as the reference test helper builds them
     (runtime-rs/src/vulkan_compute/mxfp4_tests.rs:1633-1652). ``None`` leaves a zero record."""
     words = np.zeros(len(resources) * 8, dtype=np.uint32)
     for slot, res in enumerate(resources):
+        if representations is not None:
+            words[slot * 8 + 7] = representations[slot]
         if res is None:
             continue
         assert res.flags["C_CONTIGUOUS"]
@@ -435,27 +439,30 @@ class ExpertWeights:
     s3: list
     w2: list
     s2: list
+    expanded: frozenset = frozenset()  # experts whose weight records say "pre-expanded FP8" (representation 1)
 
     def gate_up_tables(self, present=None):
         """(address words, slot words, keepalive) with P = 4 per expert."""
         n = len(self.w1)
         present = range(n) if present is None else present
-        resources, slots = [], np.full(n * 4, UNBOUND_SLOT, dtype=np.uint32)
+        resources, reps, slots = [], [], np.full(n * 4, UNBOUND_SLOT, dtype=np.uint32)
         for e in present:
             for j, arr in enumerate((self.w1[e], self.s1[e], self.w3[e], self.s3[e])):
                 slots[e * 4 + j] = len(resources)
                 resources.append(arr)
-        return address_table(resources), slots
+                reps.append(1 if (e in self.expanded and j % 2 == 0) else 0)
+        return address_table(resources, reps), slots
 
     def down_tables(self, present=None):
         n = len(self.w2)
         present = range(n) if present is None else present
-        resources, slots = [], np.full(n * 2, UNBOUND_SLOT, dtype=np.uint32)
+        resources, reps, slots = [], [], np.full(n * 2, UNBOUND_SLOT, dtype=np.uint32)
         for e in present:
             for j, arr in enumerate((self.w2[e], self.s2[e])):
                 slots[e * 2 + j] = len(resources)
                 resources.append(arr)
-        return address_table(resources), slots
+                reps.append(1 if (e in self.expanded and j % 2 == 0) else 0)
+        return address_table(resources, reps), slots
 
 
 def moe_layer(rp: RouterParams, ep: ExpertParams, hidden_bf16: np.ndarray, logit_words: np.ndarray,
@@ -495,4 +502,5 @@ def expert_params_from(cfg, tier: int = 1) -> ExpertParams:
     return ExpertParams(
         hidden_size=cfg.hidden, intermediate_size=cfg.intermediate, num_experts=cfg.total_experts,
         experts_per_token=cfg.total_k, tile_rows=32, swiglu_limit=cfg.swiglu_limit,
-        swiglu_alpha=cfg.swiglu_alpha, swiglu_up_offset=cfg.swiglu_up_offset, act_block=cfg.act_block, tier=tier)
+        swiglu_alpha=cfg.swiglu_alpha, swiglu_up_offset=cfg.swiglu_up_offset, act_block=cfg.act_block, tier=tier,
+        native_fp8_start=(cfg.total_experts - cfg.native_fp8_resources) if getattr(cfg, "native_fp8_resources", 0) else 0)

@@ -24,7 +24,7 @@ def test_library_exports_every_symbol_the_header_declares():
 
 def test_struct_layouts_match_the_header():
     # sizes follow from the field lists in include/nerve_cuda_moe.h
-    assert ctypes.sizeof(capi.Geometry) == 22 * 4
+    assert ctypes.sizeof(capi.Geometry) == 23 * 4
     assert ctypes.sizeof(capi.LayerArgs) == 3 * 4 + 4 + 14 * 8
     assert ctypes.sizeof(capi.WorkReport) == 4 + 8 * 4 + 3 * 4 + 4 * 4 + 8
     assert ctypes.sizeof(capi.EpLayerArgs) == 4 + 4 + 11 * 8
