@@ -284,6 +284,28 @@ int nvmoe_down(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* inter
                const nvmoe_buffer* routes, nvmoe_buffer* outputs, const nvmoe_buffer* addresses,
                const nvmoe_buffer* slots, const nvmoe_buffer* control);
 
+/* Intra-expert tensor parallelism, the reference's `tensor_parallel_expert` strategy
+ * (nerve/model_package_physical_experts.py:98-327): the intermediate dimension is cut into ranges aligned to
+ * 128, one per participant. A participant is a plan whose intermediate_size is its range: nvmoe_gate_up on
+ * the row range of w1/w3 gives its slice of the intermediates (replicated input, partitioned output), and
+ * nvmoe_down_partial on the column range of w2 (resident as a [hidden][range/2] matrix with its
+ * [hidden][range/32] scales) gives the raw f32 sums over that range
+ * (independent_sparse_moe_down_batch1_mxfp4.comp.template:421-505): no route weight, no rounding.
+ * bindings as nvmoe_down with `partial_outputs` [T][K][hidden] f32 in place of the outputs; rows of routes
+ * the participant skips are zero. */
+int nvmoe_down_partial(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* intermediates,
+                       const nvmoe_buffer* routes, nvmoe_buffer* partial_outputs, const nvmoe_buffer* addresses,
+                       const nvmoe_buffer* slots, const nvmoe_buffer* control);
+
+/* The finalisation of a reduced output (runtime-rs/shaders/distributed_sum_f32_scale_packed_bf16_to_bf16.comp:44-66):
+ * partials [participants][lanes][element_count] f32 are added in participant order, scaled by the bf16 in
+ * bits [scale_bit_offset, +16) of scales[lane][element / elements_per_scale] and rounded to bf16 once. For the
+ * expert outputs: element_count = K * hidden, elements_per_scale = hidden, scales = the route words, offset 16.
+ * bindings: 0 partials, 1 scales, 2 output [lanes][element_count] bf16. */
+int nvmoe_sum_f32_scale_packed_bf16(nvmoe_plan* plan, const nvmoe_buffer* partials, const nvmoe_buffer* scales,
+                                    nvmoe_buffer* output, uint32_t element_count, uint32_t participant_count,
+                                    uint32_t lane_count, uint32_t elements_per_scale, uint32_t scale_bit_offset);
+
 /* op `moe_reduce` (runtime-rs/shaders/moe_reduce_batch1_bf16.comp.template:29-55).
  * bindings: 0 expert outputs, 1 output. */
 int nvmoe_reduce(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* expert_outputs,

@@ -378,6 +378,16 @@ class MoePlan:
         self._call("nvmoe_down", batch_width, _h(intermediates), _h(routes), _h(outputs), _h(addresses), _h(slots),
                    _h(control))
 
+    def independent_sparse_moe_down_partial(self, batch_width, intermediates, routes, partial_outputs, addresses, slots, control):
+        """The tensor-parallel form of the down projection: raw f32 sums over this participant's column range."""
+        self._call("nvmoe_down_partial", batch_width, _h(intermediates), _h(routes), _h(partial_outputs), _h(addresses),
+                   _h(slots), _h(control))
+
+    def sum_f32_scale_packed_bf16(self, partials, scales, output, element_count, participant_count, lane_count,
+                                  elements_per_scale, scale_bit_offset=16):
+        self._call("nvmoe_sum_f32_scale_packed_bf16", _h(partials), _h(scales), _h(output), element_count, participant_count,
+                   lane_count, elements_per_scale, scale_bit_offset)
+
     def moe_reduce(self, batch_width, expert_outputs, output):
         self._call("nvmoe_reduce", batch_width, _h(expert_outputs), _h(output))
 

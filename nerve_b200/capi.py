@@ -102,6 +102,9 @@ PROTOTYPES = {
                                        c_void_p, c_void_p]),
     "nvmoe_down": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvmoe_reduce": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p]),
+    "nvmoe_down_partial": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvmoe_sum_f32_scale_packed_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32,
+                                                c_uint32]),
     "nvmoe_layer": (c_int, [c_void_p, POINTER(LayerArgs)]),
     "nvmoe_layer_host": (c_int, [c_void_p, POINTER(LayerArgs), c_void_p, c_void_p]),
     "nvmoe_plan_last_report": (c_int, [c_void_p, POINTER(WorkReport)]),

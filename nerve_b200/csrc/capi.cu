@@ -844,6 +844,7 @@ struct ExpertCall {
     const uint32_t* routes = nullptr;
     uint32_t* intermediates = nullptr;
     uint16_t* outputs = nullptr;
+    float* partial_outputs = nullptr;      // down only: raw f32 sums instead of weighted bf16 rows
     const nvmoe_buffer* addresses = nullptr;
     const nvmoe_buffer* slots = nullptr;
     const uint32_t* control = nullptr;
@@ -881,6 +882,7 @@ static int run_experts(nvmoe_plan* p, const ExpertCall& c) {
     el.routes = c.routes;
     el.intermediates = c.intermediates;
     el.outputs = c.outputs;
+    el.partial_outputs = c.partial_outputs;
     el.status = p->status.as<uint32_t>();
     el.scale_stamps = es->stamps.as<uint64_t>();
     el.cta_trace = p->cta_trace.as<uint64_t>();
@@ -1006,6 +1008,53 @@ int nvmoe_down(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* intermediates, con
     c.slots = slots;
     c.control = (const uint32_t*)control->ptr;
     return run_experts(p, c);
+}
+
+int nvmoe_down_partial(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* intermediates, const nvmoe_buffer* routes,
+                       nvmoe_buffer* partial_outputs, const nvmoe_buffer* addresses, const nvmoe_buffer* slots,
+                       const nvmoe_buffer* control) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    NVMOE_TRY(check_tokens(p, T));
+    const nvmoe_geometry& g = p->g;
+    const size_t out_bytes = (size_t)T * p->K * g.hidden_size * 4u;
+    NVMOE_TRY(check_buffer(p, intermediates, (size_t)T * p->frame_words * 4u, "intermediates"));
+    NVMOE_TRY(check_buffer(p, routes, (size_t)T * p->K * 4u, "routes"));
+    NVMOE_TRY(check_buffer(p, partial_outputs, out_bytes, "partial expert outputs"));
+    NVMOE_TRY(check_buffer(p, control, 28u, "control"));
+    NVMOE_TRY(check_expert_tables(p, addresses, slots, 2u));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    // a route this participant skips contributes a plane of zeros to the sum
+    NVMOE_CUDA(p->device, cudaMemsetAsync(partial_outputs->ptr, 0, out_bytes, p->device->stream));
+    ExpertCall c;
+    c.gate_up = false;
+    c.T = T;
+    c.source = intermediates->ptr;
+    c.routes = (const uint32_t*)routes->ptr;
+    c.intermediates = (uint32_t*)intermediates->ptr;
+    c.partial_outputs = (float*)partial_outputs->ptr;
+    c.addresses = addresses;
+    c.slots = slots;
+    c.control = (const uint32_t*)control->ptr;
+    return run_experts(p, c);
+}
+
+int nvmoe_sum_f32_scale_packed_bf16(nvmoe_plan* p, const nvmoe_buffer* partials, const nvmoe_buffer* scales, nvmoe_buffer* output,
+                                    uint32_t element_count, uint32_t participant_count, uint32_t lane_count,
+                                    uint32_t elements_per_scale, uint32_t scale_bit_offset) {
+    if (!p) return NVMOE_ERR_INVALID_ARGUMENT;
+    if (element_count == 0u || element_count % 2u || participant_count == 0u || lane_count == 0u || elements_per_scale == 0u ||
+        element_count % elements_per_scale || elements_per_scale % 2u || (scale_bit_offset != 0u && scale_bit_offset != 16u))
+        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT,
+                    "sum_f32_scale_packed_bf16: %u elements (even), %u participants, %u lanes, one scale per %u elements (an even "
+                    "divisor), bit offset %u (0 or 16)", element_count, participant_count, lane_count, elements_per_scale, scale_bit_offset);
+    NVMOE_TRY(check_buffer(p, partials, (size_t)participant_count * lane_count * element_count * 4u, "partial planes"));
+    NVMOE_TRY(check_buffer(p, scales, (size_t)lane_count * (element_count / elements_per_scale) * 4u, "packed scales"));
+    NVMOE_TRY(check_buffer(p, output, (size_t)lane_count * element_count * 2u, "output"));
+    NVMOE_CUDA(p->device, cudaSetDevice(p->device->ordinal));
+    launch_sum_f32_scale_packed_bf16((const float*)partials->ptr, (const uint32_t*)scales->ptr, (uint32_t*)output->ptr, element_count,
+                                     participant_count, lane_count, elements_per_scale, scale_bit_offset, p->device->stream);
+    p->launches++;
+    return post_launch(p, "sum_f32_scale_packed_bf16");
 }
 
 int nvmoe_reduce(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* expert_outputs, nvmoe_buffer* output) {

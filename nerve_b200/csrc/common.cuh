@@ -203,6 +203,7 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     const uint32_t* routes;      // route words (down: weights)
     uint32_t* intermediates;     // gate/up output frames
     uint16_t* outputs;           // down output [T][K][H]
+    float* partial_outputs;      // down, tensor-parallel form: raw f32 sums [T][K][H] instead of `outputs` (no route weight, no rounding)
     uint32_t* status;
     const uint8_t* tmaps;        // tensor path: 128-byte tensor maps [expert][matrix], null = move weights with cp.async
     // tensor path: act_q / act_e8m0 hold expert-grouped rows (row = position in grouped_routes);
@@ -240,6 +241,12 @@ void launch_route_preselected(const uint32_t* logits, const uint32_t* selections
 // every row a route of expert 0 in row order: grouped list, offsets [0, rows], inverse, (expert, token tile) list
 void launch_dense_schedule(uint32_t rows, uint32_t n_tile, uint32_t* grouped, uint32_t* offsets, uint32_t* position, uint32_t* tiles,
                            uint32_t* tile_count, cudaStream_t stream);
+
+// reduce.cu: distributed_sum_f32_scale_packed_bf16_to_bf16: out[lane][e] = bf16(sum over participants of
+// partials[participant][lane][e] * bf16(scales[lane * (elements / elements_per_scale) + e / elements_per_scale] >> bit_offset))
+void launch_sum_f32_scale_packed_bf16(const float* partials, const uint32_t* scales, uint32_t* output, uint32_t element_count,
+                                      uint32_t participant_count, uint32_t lane_count, uint32_t elements_per_scale,
+                                      uint32_t scale_bit_offset, cudaStream_t stream);
 
 // probe.cu: a run of `groups` x 8 block-scaled MMAs (128 x n_tile x 32, two alternating accumulators)
 // on every one of `ctas` CTAs; cycles[cta] = clock cycles from first issue to completion

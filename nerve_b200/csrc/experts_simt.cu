@@ -189,8 +189,12 @@ __global__ void __launch_bounds__(kThreads) experts_simt_kernel(ExpertLaunch p, 
                                     (size_t)(ri % K) * I;
                     out[row] = (uint16_t)nvmoe_f32_to_bf16(a);
                 } else {
-                    const float weight = nvmoe_bf16_to_f32(p.routes[ri] >> 16);
-                    p.outputs[(size_t)ri * H + row] = (uint16_t)nvmoe_f32_to_bf16(__fmul_rn(g, weight));
+                    if (p.partial_outputs) {  // tensor-parallel form: the raw sum over this participant's columns
+                        p.partial_outputs[(size_t)ri * H + row] = g;
+                    } else {
+                        const float weight = nvmoe_bf16_to_f32(p.routes[ri] >> 16);
+                        p.outputs[(size_t)ri * H + row] = (uint16_t)nvmoe_f32_to_bf16(__fmul_rn(g, weight));
+                    }
                 }
             }
         }

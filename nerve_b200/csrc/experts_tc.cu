@@ -608,6 +608,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                     if (GATE_UP) {
                         my_row = reinterpret_cast<uint64_t>(reinterpret_cast<uint16_t*>(p.intermediates + (size_t)(ri / K) * frame_words) +
                                                             (size_t)(ri % K) * I);
+                    } else if (p.partial_outputs != nullptr) {
+                        my_row = reinterpret_cast<uint64_t>(p.partial_outputs + (size_t)ri * H);
                     } else {
                         my_row = reinterpret_cast<uint64_t>(p.outputs + (size_t)ri * H);
                         my_weight = nvmoe_bf16_to_f32(__ldg(p.routes + ri) >> 16);
@@ -633,6 +635,17 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                             const float weight = __shfl_sync(0xffffffffu, my_weight, j);
                             bits[t] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__uint_as_float(d0[j]), weight)));
                         }
+                    }
+                    if (!GATE_UP && p.partial_outputs != nullptr) {
+                        // tensor-parallel form: the raw f32 sums over this participant's columns, weighted and rounded
+                        // only after the participants' planes have been added
+#pragma unroll
+                        for (uint32_t t = 0; t < 4u; t++) {
+                            float* out = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, my_row, g0 + t));
+                            if (c0 + g0 + t < valid && row_ok) out[row] = __uint_as_float(d0[g0 + t]);
+                            if (ROW_PAIR && c0 + g0 + t < valid && row + kBlockM < out_rows) out[row + kBlockM] = __uint_as_float(d1[g0 + t]);
+                        }
+                        continue;
                     }
 #pragma unroll
                     for (uint32_t t = 0; t < 4u; t++) {

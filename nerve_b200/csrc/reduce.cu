@@ -64,7 +64,44 @@ __global__ void __launch_bounds__(256) reduce_vec_kernel(const uint4* __restrict
     }
 }
 
+// The finaliser of a tensor-parallel expert stage
+// (runtime-rs/shaders/distributed_sum_f32_scale_packed_bf16_to_bf16.comp:44-66): the participants' f32
+// partial planes are added in participant order, the sum is scaled by a bf16 taken from a packed word
+// (the route weight in the upper half of a route word) and rounded to bf16 once.
+__global__ void __launch_bounds__(256) sum_f32_scale_packed_bf16_kernel(const float* __restrict__ partials,
+                                                                       const uint32_t* __restrict__ scales,
+                                                                       uint32_t* __restrict__ output, uint32_t element_count,
+                                                                       uint32_t participant_count, uint32_t lane_count,
+                                                                       uint32_t elements_per_scale, uint32_t scale_bit_offset) {
+    grid_dependency_sync();
+    const uint32_t words = element_count / 2u, scales_per_lane = element_count / elements_per_scale;
+    const uint64_t total = (uint64_t)lane_count * words;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t lane = (uint32_t)(i / words), element = (uint32_t)(i % words) * 2u;
+        float lo = 0.0f, hi = 0.0f;
+        for (uint32_t part = 0; part < participant_count; part++) {
+            const float2 v = *reinterpret_cast<const float2*>(partials + ((size_t)part * lane_count + lane) * element_count + element);
+            lo = __fadd_rn(lo, v.x);
+            hi = __fadd_rn(hi, v.y);
+        }
+        const float slo = nvmoe_bf16_to_f32(scales[(size_t)lane * scales_per_lane + element / elements_per_scale] >> scale_bit_offset);
+        const float shi = nvmoe_bf16_to_f32(scales[(size_t)lane * scales_per_lane + (element + 1u) / elements_per_scale] >> scale_bit_offset);
+        output[i] = pack_bf16x2(__fmul_rn(lo, slo), __fmul_rn(hi, shi));
+    }
+}
+
 }  // namespace
+
+void launch_sum_f32_scale_packed_bf16(const float* partials, const uint32_t* scales, uint32_t* output, uint32_t element_count,
+                                      uint32_t participant_count, uint32_t lane_count, uint32_t elements_per_scale,
+                                      uint32_t scale_bit_offset, cudaStream_t stream) {
+    const uint64_t total = (uint64_t)lane_count * (element_count / 2u);
+    uint64_t blocks = (total + 255u) / 256u;
+    if (blocks > 148u * 16u) blocks = 148u * 16u;
+    if (blocks == 0u) return;
+    launch_chained(sum_f32_scale_packed_bf16_kernel, dim3((uint32_t)blocks), dim3(256), 0, stream, partials, scales, output,
+                   element_count, participant_count, lane_count, elements_per_scale, scale_bit_offset);
+}
 
 void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t tokens, uint32_t K, uint32_t hidden,
                    float routed_scale, const uint32_t* computed, cudaStream_t stream) {
