@@ -506,6 +506,16 @@ int nvmoe_ep_unique_id(void* id128);
 int nvmoe_ep_create(nvmoe_device* device, const void* id128, uint32_t rank, uint32_t world_size, nvmoe_ep** out);
 void nvmoe_ep_destroy(nvmoe_ep* ep);
 int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe_ep_layer_args* args);
+/* Failure behaviour of nvmoe_ep_layer. Whatever can fail on one rank alone (allocation, the resolution of the
+ * expert tables) happens before the first exchange; once a rank has posted the first exchange it always posts
+ * the second, and reports the first error afterwards, so that no peer is left waiting for a half-finished
+ * step. A peer that does not take part at all (it crashed, or returned before the exchange) is detected by
+ * time: nvmoe_ep_sync waits for the stream for at most timeout_ns, polling the communicator for asynchronous
+ * errors meanwhile, and on an error or on timeout aborts the communicator, which ends the kernels waiting on
+ * the peer; it returns NVMOE_ERR_COLLECTIVE or NVMOE_ERR_TIMEOUT and the communicator refuses further calls.
+ * The counterpart of the reference's queue-progress watchdog
+ * (runtime-rs/src/vulkan_compute/queue_progress_watchdog.rs:18-60) for a step that spans devices. */
+int nvmoe_ep_sync(nvmoe_ep* ep, uint64_t timeout_ns);
 
 #ifdef __cplusplus
 }

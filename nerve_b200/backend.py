@@ -244,6 +244,10 @@ class ExpertParallelGroup:
         a.down_addresses, a.down_slots = _h(bank.down_addresses), _h(bank.down_slots)
         self.device._check(self.device._lib.nvmoe_ep_layer(self._h, home._h, work._h, ctypes.byref(a)))
 
+    def sync(self, timeout_ns: int = 30_000_000_000) -> None:
+        """Bounded wait for the step; aborts the communicator on an asynchronous error or on timeout."""
+        self.device._check(self.device._lib.nvmoe_ep_sync(self._h, timeout_ns))
+
     def destroy(self) -> None:
         if self._h:
             self.device._lib.nvmoe_ep_destroy(self._h)

@@ -121,6 +121,7 @@ PROTOTYPES = {
     "nvmoe_ep_create": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, POINTER(c_void_p)]),
     "nvmoe_ep_destroy": (None, [c_void_p]),
     "nvmoe_ep_layer": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(EpLayerArgs)]),
+    "nvmoe_ep_sync": (c_int, [c_void_p, c_uint64]),
 }
 
 _lib = None

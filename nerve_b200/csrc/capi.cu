@@ -1665,6 +1665,8 @@ struct NcclApi {
     decltype(&ncclSend) send = nullptr;
     decltype(&ncclRecv) recv = nullptr;
     decltype(&ncclGetErrorString) error_string = nullptr;
+    decltype(&ncclCommGetAsyncError) comm_get_async_error = nullptr;
+    decltype(&ncclCommAbort) comm_abort = nullptr;
     std::string problem;
 };
 
@@ -1694,6 +1696,8 @@ const NcclApi& nccl_api() {
         bind(a.send, "ncclSend");
         bind(a.recv, "ncclRecv");
         bind(a.error_string, "ncclGetErrorString");
+        bind(a.comm_get_async_error, "ncclCommGetAsyncError");
+        bind(a.comm_abort, "ncclCommAbort");
         return a;
     }();
     return api;
@@ -1704,6 +1708,7 @@ const NcclApi& nccl_api() {
 struct nvmoe_ep {
     nvmoe_device* device = nullptr;
     ncclComm_t comm = nullptr;
+    bool aborted = false;  // the communicator was aborted after a failure: every later call is refused
     uint32_t rank = 0, world = 1;
     // exchange buffers, sized on first use from the plans' geometry
     DeviceArray logits, routes, send_rows, send_routes, recv_rows, recv_routes, work_out, returned, send_index,
@@ -1720,20 +1725,31 @@ namespace {
     } while (0)
 
 // every rank sends segment `peer` of `send` to rank `peer` and receives segment `peer` of `recv` from it
+// A group that was opened is always closed, whatever a call inside it returned: an open group would swallow
+// every later NCCL call of the thread. The first failure is what is reported.
 int exchange_segments(nvmoe_ep* ep, const void* send_a, void* recv_a, size_t bytes_a, const void* send_b, void* recv_b,
                       size_t bytes_b) {
     const NcclApi& n = nccl_api();
     nvmoe_device* d = ep->device;
     NVMOE_NCCL(d, n.group_start());
-    for (uint32_t peer = 0; peer < ep->world; peer++) {
-        NVMOE_NCCL(d, n.send((const char*)send_a + peer * bytes_a, bytes_a, ncclInt8, (int)peer, ep->comm, d->stream));
-        NVMOE_NCCL(d, n.recv((char*)recv_a + peer * bytes_a, bytes_a, ncclInt8, (int)peer, ep->comm, d->stream));
+    ncclResult_t first = ncclSuccess;
+    const char* what = "";
+    auto note = [&](ncclResult_t r, const char* call) {
+        if (r != ncclSuccess && first == ncclSuccess) {
+            first = r;
+            what = call;
+        }
+    };
+    for (uint32_t peer = 0; peer < ep->world && first == ncclSuccess; peer++) {
+        note(n.send((const char*)send_a + peer * bytes_a, bytes_a, ncclInt8, (int)peer, ep->comm, d->stream), "ncclSend");
+        note(n.recv((char*)recv_a + peer * bytes_a, bytes_a, ncclInt8, (int)peer, ep->comm, d->stream), "ncclRecv");
         if (send_b) {
-            NVMOE_NCCL(d, n.send((const char*)send_b + peer * bytes_b, bytes_b, ncclInt8, (int)peer, ep->comm, d->stream));
-            NVMOE_NCCL(d, n.recv((char*)recv_b + peer * bytes_b, bytes_b, ncclInt8, (int)peer, ep->comm, d->stream));
+            note(n.send((const char*)send_b + peer * bytes_b, bytes_b, ncclInt8, (int)peer, ep->comm, d->stream), "ncclSend");
+            note(n.recv((char*)recv_b + peer * bytes_b, bytes_b, ncclInt8, (int)peer, ep->comm, d->stream), "ncclRecv");
         }
     }
-    NVMOE_NCCL(d, n.group_end());
+    note(n.group_end(), "ncclGroupEnd");
+    if (first != ncclSuccess) return fail(d, NVMOE_ERR_COLLECTIVE, "%s failed: %s", what, n.error_string(first));
     return NVMOE_OK;
 }
 
@@ -1781,7 +1797,7 @@ void nvmoe_ep_destroy(nvmoe_ep* ep) {
     if (!ep) return;
     cudaSetDevice(ep->device->ordinal);
     cudaStreamSynchronize(ep->device->stream);
-    if (ep->comm) nccl_api().comm_destroy(ep->comm);
+    if (ep->comm && !ep->aborted) nccl_api().comm_destroy(ep->comm);
     DeviceArray* all[] = {&ep->logits, &ep->routes, &ep->send_rows, &ep->send_routes, &ep->recv_rows, &ep->recv_routes,
                           &ep->work_out, &ep->returned, &ep->send_index, &ep->dest_counts, &ep->expert_outputs};
     for (DeviceArray* a : all) a->release();
@@ -1829,12 +1845,33 @@ int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe
                  work_out = view(ep->work_out), returned = view(ep->returned), send_index = view(ep->send_index),
                  dest_counts = view(ep->dest_counts), expert_outputs = view(ep->expert_outputs);
 
+    if (ep->aborted) return fail(d, NVMOE_ERR_COLLECTIVE, "the communicator was aborted after an earlier failure");
+    // Everything that can allocate, synchronise or fail on this rank alone happens before the first exchange:
+    // the owner-side scratch and the resolution of both table pairs. Between the two exchanges nothing returns
+    // early, because a rank that posted the first exchange and not the second leaves its peers waiting for rows
+    // that never come.
+    NVMOE_TRY(ensure_layer_scratch(work));
+    {
+        const bool tensor = use_tensor_path(work);
+        ExpertSet* unused = nullptr;
+        NVMOE_TRY(check_expert_tables(work, a->gate_up_addresses, a->gate_up_slots, 4u));
+        NVMOE_TRY(check_expert_tables(work, a->down_addresses, a->down_slots, 2u));
+        NVMOE_TRY(prepare_expert_set(work, true, a->gate_up_addresses, a->gate_up_slots, tensor, &unused));
+        NVMOE_TRY(prepare_expert_set(work, false, a->down_addresses, a->down_slots, tensor, &unused));
+    }
     // this rank's tokens: route, then place every route's row in the segment of the rank owning its expert
     NVMOE_TRY(nvmoe_router_linear(home, T, a->hidden, &logits, a->router_weights, a->router_bias));
     NVMOE_TRY(nvmoe_route(home, T, &logits, &routes, a->bias, a->telemetry));
     NVMOE_TRY(nvmoe_ep_pack(home, T, a->hidden, &routes, a->owner_table, G, ep->rank, &send_rows, &send_routes, &send_index,
                             &dest_counts, (uint32_t)S));
-    NVMOE_TRY(exchange_segments(ep, send_rows.ptr, recv_rows.ptr, S * H * 2u, send_routes.ptr, recv_routes.ptr, S * 4u));
+    int first_error = exchange_segments(ep, send_rows.ptr, recv_rows.ptr, S * H * 2u, send_routes.ptr, recv_routes.ptr, S * 4u);
+    std::string first_text = first_error != NVMOE_OK ? d->error : std::string();
+    auto keep_first = [&](int rc) {
+        if (rc != NVMOE_OK && first_error == NVMOE_OK) {
+            first_error = rc;
+            first_text = d->error;
+        }
+    };
     // the rows this rank owns the experts of: every resource in range, the slot tables keep the owned ones
     nvmoe_layer_args owner{};
     owner.batch_width = (uint32_t)(S * G);
@@ -1847,10 +1884,49 @@ int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe
     owner.gate_up_slots = a->gate_up_slots;
     owner.down_addresses = a->down_addresses;
     owner.down_slots = a->down_slots;
-    NVMOE_TRY(nvmoe_layer(work, &owner));
-    NVMOE_TRY(exchange_segments(ep, work_out.ptr, returned.ptr, S * H * 2u, nullptr, nullptr, 0u));
+    if (first_error == NVMOE_OK) keep_first(nvmoe_layer(work, &owner));
+    // the return exchange is posted whatever happened above (the peers are already waiting for it)
+    keep_first(exchange_segments(ep, work_out.ptr, returned.ptr, S * H * 2u, nullptr, nullptr, 0u));
+    if (first_error != NVMOE_OK) {
+        d->error = first_text;
+        return first_error;
+    }
     NVMOE_TRY(nvmoe_ep_unpack(home, T, &returned, &send_index, &expert_outputs));
     return nvmoe_reduce(home, T, &expert_outputs, a->output);
+}
+
+// Bounded wait for everything queued on the communicator's stream. While it waits it asks NCCL for
+// asynchronous errors; on such an error, or when the time runs out (a peer that never posted its half of an
+// exchange), the communicator is aborted so that the kernels spinning on the peer give up and the stream
+// drains: the host thread and the device both come back. The communicator is unusable afterwards.
+int nvmoe_ep_sync(nvmoe_ep* ep, uint64_t timeout_ns) {
+    if (!ep) return NVMOE_ERR_INVALID_ARGUMENT;
+    nvmoe_device* d = ep->device;
+    const NcclApi& n = nccl_api();
+    NVMOE_CUDA(d, cudaSetDevice(d->ordinal));
+    NVMOE_CUDA(d, cudaEventRecord(d->sync_event, d->stream));
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(d->sync_event);
+        if (q == cudaSuccess) return NVMOE_OK;
+        if (q != cudaErrorNotReady) return fail(d, NVMOE_ERR_CUDA, "device failed while waiting: %s", cudaGetErrorString(q));
+        ncclResult_t async = ncclSuccess;
+        const bool asked = !ep->aborted && n.comm_get_async_error && n.comm_get_async_error(ep->comm, &async) == ncclSuccess;
+        const bool failed = asked && async != ncclSuccess && async != ncclInProgress;
+        const bool late = std::chrono::steady_clock::now() >= deadline;
+        if (failed || late) {
+            if (!ep->aborted && n.comm_abort) {
+                n.comm_abort(ep->comm);
+                ep->comm = nullptr;
+            }
+            ep->aborted = true;
+            if (failed)
+                return fail(d, NVMOE_ERR_COLLECTIVE, "the communicator reported %s; it was aborted", n.error_string(async));
+            return fail(d, NVMOE_ERR_TIMEOUT, "the exchange did not finish within %llu ns; the communicator was aborted",
+                        (unsigned long long)timeout_ns);
+        }
+        std::this_thread::yield();
+    }
 }
 
 }  // extern "C"

@@ -83,10 +83,22 @@ def exchange(ops: ExchangeOps, dist, group=None):
     send_splits = [int(v) for v in dest_counts.cpu().tolist()]
     recv_splits = [int(v) for v in recv_counts.cpu().tolist()]
     n_send, n_recv = sum(send_splits), sum(recv_splits)
-    if len(send_splits) != world or n_send > send_rows.shape[0]:
-        raise RuntimeError(f"destination counts {send_splits} do not describe {send_rows.shape[0]} packed rows")
-    if n_recv > ops.capacity:
-        raise RuntimeError(f"{n_recv} rows arrive but the receive buffers hold {ops.capacity}")
+    problem = None
+    if len(send_splits) != world or min(send_splits, default=0) < 0 or n_send > send_rows.shape[0]:
+        problem = f"destination counts {send_splits} do not describe {send_rows.shape[0]} packed rows"
+    elif min(recv_splits, default=0) < 0:
+        problem = f"a peer announced a negative row count: {recv_splits}"
+    elif n_recv > ops.capacity:
+        problem = f"{n_recv} rows arrive but the receive buffers hold {ops.capacity}"
+    # A rank that found a problem must not simply leave: its peers would wait in the row exchange for rows that
+    # never come. The verdicts are shared first (one small all-reduce beside a host read that the split sizes
+    # need anyway), and every rank gives the step up together.
+    verdict = dest_counts.new_tensor([0 if problem is None else 1])
+    dist.all_reduce(verdict, op=dist.ReduceOp.MAX, group=group)
+    if problem is not None:
+        raise RuntimeError(problem)
+    if int(verdict.cpu().item()) != 0:
+        raise RuntimeError("a peer rejected this step's split sizes: the exchange was given up on every rank")
     hidden = send_rows.shape[1]
     recv_rows = torch.empty((max(n_recv, 1), hidden), dtype=send_rows.dtype, device=send_rows.device)
     recv_routes = torch.empty((max(n_recv, 1),), dtype=send_routes.dtype, device=send_routes.device)

@@ -137,23 +137,48 @@ class CpuOps:
 
 
 def _worker(rank, world, port, cfg_name, small, tokens, mode, result_dir):
+    import datetime
+    import time
+
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
     try:
         cfg = synthetic.small_variant(synthetic.CONFIGS[cfg_name], *small)
         case = synthetic.make_case(cfg, tokens * world, seed=1)
-        capacity = 1 if mode == "undersized" else tokens * cfg.total_k * world
+        # "undersized": rank 1 alone has too small a receive buffer; "miscount": rank 0 alone announces more rows than it packed
+        capacity = 1 if (mode == "undersized" and rank == 1) else tokens * cfg.total_k * world
         backend = CpuOps(cfg, case, rank, world, tokens, capacity)
-        ops = ep.ExchangeOps(backend.route, backend.pack, backend.compute, backend.unpack_reduce, capacity)
-        if mode == "undersized":
+        pack = backend.pack
+        if mode == "miscount" and rank == 0:
+            def pack():
+                rows, routes, counts = backend.pack()
+                counts[1] += 1000
+                return rows, routes, counts
+        ops = ep.ExchangeOps(backend.route, pack, backend.compute, backend.unpack_reduce, capacity)
+        if mode in ("undersized", "miscount"):
+            started = time.monotonic()
             try:
                 ep.exchange(ops, dist)
+                message = "no error"
             except RuntimeError as error:
-                np.save(Path(result_dir) / f"err{rank}.npy", np.array([1]))
-                assert "receive buffers hold" in str(error)
+                message = str(error)
+            (Path(result_dir) / f"err{rank}.txt").write_text(f"{time.monotonic() - started:.2f}\n{message}")
+            return
+        if mode == "absent":
+            # rank 1 never takes part in the step; rank 0 must get an error within the group's timeout, not hang
+            if rank == 1:
+                time.sleep(12)
+                return
+            started = time.monotonic()
+            try:
+                ep.exchange(ops, dist)
+                message = "no error"
+            except Exception as error:  # gloo reports the timeout as a RuntimeError or a DistBackendError
+                message = f"{type(error).__name__}: {error}"
+            (Path(result_dir) / f"err{rank}.txt").write_text(f"{time.monotonic() - started:.2f}\n{message}")
             return
         if mode == "padded":
             ep.exchange_padded(backend.padded_ops(), dist)
@@ -191,10 +216,43 @@ def test_sharded_layer_equals_unsharded_layer(tmp_path, cfg_name, small, mode):
     assert mo.lib() is not None
 
 
-def test_undersized_receive_buffer_is_an_error_not_a_hang(tmp_path):
+def _verdicts(tmp_path):
+    out = {}
+    for rank in range(2):
+        path = tmp_path / f"err{rank}.txt"
+        if path.exists():
+            seconds, message = path.read_text().split("\n", 1)
+            out[rank] = (float(seconds), message)
+    return out
+
+
+def test_undersized_receive_buffer_is_an_error_on_every_rank_not_a_hang(tmp_path):
+    """Only rank 1's buffer is too small, but rank 0 must not be left waiting in the row exchange: both give
+    the step up, at once."""
     pytest.importorskip("torch")
     _spawn("gpt-oss-120b", (64, 96, 8), 6, "undersized", tmp_path)
-    assert (tmp_path / "err0.npy").exists() or (tmp_path / "err1.npy").exists()
+    v = _verdicts(tmp_path)
+    assert "receive buffers hold" in v[1][1]
+    assert "a peer rejected" in v[0][1]
+    assert v[0][0] < 5 and v[1][0] < 5, "the verdict is shared, no rank waits for a timeout"
+
+
+def test_split_sizes_that_do_not_match_the_packed_rows_are_rejected_everywhere(tmp_path):
+    pytest.importorskip("torch")
+    _spawn("gpt-oss-120b", (64, 96, 8), 6, "miscount", tmp_path)
+    v = _verdicts(tmp_path)
+    assert "do not describe" in v[0][1]
+    assert "a peer rejected" in v[1][1] or "receive buffers hold" in v[1][1]
+    assert v[0][0] < 5 and v[1][0] < 5
+
+
+def test_a_rank_that_never_joins_the_step_ends_in_a_timeout_error(tmp_path):
+    """Host-made failure: rank 1 sleeps through the step. Rank 0's collective ends with an error after the
+    process group's timeout (8 s here) instead of blocking for good."""
+    pytest.importorskip("torch")
+    _spawn("gpt-oss-120b", (64, 96, 8), 6, "absent", tmp_path)
+    seconds, message = _verdicts(tmp_path)[0]
+    assert message != "no error" and seconds < 11, (seconds, message)
 
 
 def test_owner_tables():
