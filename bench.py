@@ -463,8 +463,10 @@ def run_expert_parallel(args, cfg, tokens):
     owned = cfg.experts // world + cfg.always_count
     touched = max(1, min(tokens * world * cfg.total_k, owned)) * per_expert
     banks = args.banks or max(2, min(8, -(-4 * L2_BYTES // touched)))
+    # segments bounded at twice the mean rows per peer (NVMOE_EP_CAPACITY=0: the worst case); an overflow is reported
     layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks,
-                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"))
+                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"),
+                                capacity_factor=float(os.environ.get("NVMOE_EP_CAPACITY", "2.0")))
     for _ in range(max(args.warmup, 3, banks + 1)):
         layer.step(dist)
     torch.cuda.synchronize()
@@ -514,6 +516,8 @@ def run_expert_parallel(args, cfg, tokens):
 
     e2e_blocks, _ = repeat(host_step, 0.2)
     ms, e2e_ms = statistics.median(blocks), statistics.median(e2e_blocks)
+    overflow = torch.tensor([1 if layer.overflowed() else 0], device=f"cuda:{local}")
+    dist.all_reduce(overflow, op=dist.ReduceOp.MAX)
 
     # parity of this rank's slice of the global batch against the CPU checker (outside every timed region)
     parity = None
@@ -554,7 +558,8 @@ def run_expert_parallel(args, cfg, tokens):
                 "experts_per_rank": cfg.experts // world,
                 "parallelism": f"ep{world}: experts sharded by contiguous range, tokens data-parallel, "
                                "NCCL all-to-all dispatch and combine",
-                "exchange": layer.mode,
+                "exchange": layer.mode, "segment_rows": layer.segment, "capacity_factor": layer.capacity_factor,
+                "segment_overflow_in_timed_steps": bool(overflow.item()),
                 "l2": f"inputs larger than L2: {banks} resident weight banks per rank visited in turn, "
                       f"{touched * banks / 1e6:.0f} MB of weights read between two reads of the same bytes"},
             "timing": spread(blocks), "clocks": clocks,

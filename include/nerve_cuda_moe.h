@@ -93,7 +93,9 @@ enum {
     NVMOE_STATUS_ROUTE_NONFINITE = 1u << 0,   /* a token had no selectable finite score */
     NVMOE_STATUS_ROUTE_OUT_OF_RANGE = 1u << 1,/* compact slot or expert id out of range: skipped */
     NVMOE_STATUS_EXPERT_NOT_RESIDENT = 1u << 2,/* address record failed validation: skipped */
-    NVMOE_STATUS_WAIT_EXPIRED = 1u << 3       /* a bounded in-kernel wait gave up */
+    NVMOE_STATUS_WAIT_EXPIRED = 1u << 3,      /* a bounded in-kernel wait gave up */
+    NVMOE_STATUS_EXCHANGE_OVERFLOW = 1u << 4  /* more rows were bound for one rank than its segment holds: the
+                                                 excess routes were left out (their rows count as zeros) */
 };
 
 /*
@@ -454,7 +456,11 @@ int nvmoe_probe_mma_rate(nvmoe_device* device, uint32_t n_tile, uint32_t k_group
  * before the exchange). segment_rows > 0 (at least T*K) gives every destination rank its own segment
  * of that many slots in send_rows / send_routes (world_size * segment_rows slots in all): unused
  * slots carry the route word 0xffffffff, which no scheduler keeps, so the exchange can use equal
- * splits and nothing has to reach the host; send_index then holds slots of that layout.
+ * splits and nothing has to reach the host; send_index then holds slots of that layout. Segments of
+ * T*K rows can never overflow. Smaller segments (a capacity bound, say twice the mean T*K/world) move
+ * and schedule proportionally less; if more rows are bound for a rank than its segment holds, the excess
+ * routes are left out, their rows count as zeros in the combine, and NVMOE_STATUS_EXCHANGE_OVERFLOW is
+ * raised in the plan's status word: the caller repeats the step with full segments.
  */
 int nvmoe_ep_pack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* hidden,
                   const nvmoe_buffer* routes, const nvmoe_buffer* owner_table, uint32_t world_size,
@@ -476,7 +482,7 @@ int nvmoe_ep_unpack(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buffer* 
  *
  * `home` is the plan of this rank's tokens (the layer's geometry, max_tokens the same on every
  * rank); `work` the owner-side plan: top_k 1 over the same experts and sizes, max_tokens at least
- * world_size * home.max_tokens * home.top_k. The slot tables name the experts this rank holds
+ * world_size * the segment size (args.capacity_rows, or home.max_tokens * home.top_k when that is 0). The slot tables name the experts this rank holds
  * (0xffffffff for the others); owner_table[expert] is the rank holding each expert (0xffffffff =
  * replicated, kept local). One step is: projection and router on the rank's tokens, rows placed in
  * fixed segments per owner (nvmoe_ep_pack with segment_rows), one grouped send/receive of rows and
@@ -501,6 +507,8 @@ typedef struct nvmoe_ep_layer_args {
     const nvmoe_buffer* down_slots;
     nvmoe_buffer* output;               /* [batch_width][hidden] bf16 */
     nvmoe_buffer* telemetry;            /* optional */
+    uint32_t capacity_rows;             /* rows of the segment each rank keeps for each peer, the same on every rank;
+                                           0 = home.max_tokens * top_k (cannot overflow). See nvmoe_ep_pack. */
 } nvmoe_ep_layer_args;
 int nvmoe_ep_unique_id(void* id128);
 int nvmoe_ep_create(nvmoe_device* device, const void* id128, uint32_t rank, uint32_t world_size, nvmoe_ep** out);

@@ -235,9 +235,10 @@ class ExpertParallelGroup:
         self._h = handle
 
     def layer(self, home: "MoePlan", work: "MoePlan", batch_width, bank: "ExpertBank", hidden, output, owner_table,
-              router_weights, router_bias=None, bias=None, telemetry=None) -> None:
+              router_weights, router_bias=None, bias=None, telemetry=None, capacity_rows: int = 0) -> None:
         a = capi.EpLayerArgs()
         a.batch_width = batch_width
+        a.capacity_rows = capacity_rows
         a.hidden, a.output, a.owner_table = _h(hidden), _h(output), _h(owner_table)
         a.router_weights, a.router_bias, a.bias, a.telemetry = _h(router_weights), _h(router_bias), _h(bias), _h(telemetry)
         a.gate_up_addresses, a.gate_up_slots = _h(bank.gate_up_addresses), _h(bank.gate_up_slots)

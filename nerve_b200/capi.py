@@ -14,6 +14,7 @@ NVMOE_OK = 0
 ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_TIMEOUT, ERR_OUT_OF_MEMORY, ERR_UNSUPPORTED, ERR_COLLECTIVE, ERR_DEVICE_STATUS = (
     -1, -2, -3, -4, -5, -6, -7)
 STATUS_ROUTE_NONFINITE, STATUS_ROUTE_OUT_OF_RANGE, STATUS_EXPERT_NOT_RESIDENT, STATUS_WAIT_EXPIRED = 1, 2, 4, 8
+STATUS_EXCHANGE_OVERFLOW = 16
 STAGE_NAMES = ("linear", "route", "schedule", "quantize_hidden", "gate_up", "quantize_intermediate", "down", "reduce")
 
 
@@ -45,6 +46,7 @@ class EpLayerArgs(ctypes.Structure):
         ("batch_width", c_uint32), ("hidden", c_void_p), ("router_weights", c_void_p), ("router_bias", c_void_p),
         ("bias", c_void_p), ("owner_table", c_void_p), ("gate_up_addresses", c_void_p), ("gate_up_slots", c_void_p),
         ("down_addresses", c_void_p), ("down_slots", c_void_p), ("output", c_void_p), ("telemetry", c_void_p),
+        ("capacity_rows", c_uint32),
     ]
 
 

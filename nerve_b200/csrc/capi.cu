@@ -1276,9 +1276,6 @@ int nvmoe_ep_pack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const n
     NVMOE_TRY(check_buffer(p, hidden, (size_t)T * g.hidden_size * 2u, "hidden"));
     NVMOE_TRY(check_buffer(p, routes, R * 4u, "routes"));
     NVMOE_TRY(check_buffer(p, owner_table, (size_t)p->experts * 4u, "owner table"));
-    if (segment_rows != 0u && segment_rows < R)
-        return fail(p->device, NVMOE_ERR_INVALID_ARGUMENT, "segments of %u rows cannot hold the %zu routes one rank may receive",
-                    segment_rows, R);
     const size_t send_slots = segment_rows ? (size_t)world * segment_rows : R;
     NVMOE_TRY(check_buffer(p, send_rows, send_slots * g.hidden_size * 2u, "send rows"));
     NVMOE_TRY(check_buffer(p, send_routes, send_slots * 4u, "send routes"));
@@ -1293,7 +1290,7 @@ int nvmoe_ep_pack(nvmoe_plan* p, uint32_t T, const nvmoe_buffer* hidden, const n
     launch_ep_pack((const uint16_t*)hidden->ptr, (const uint32_t*)routes->ptr, (const uint32_t*)owner_table->ptr, T, p->K,
                    g.hidden_size, p->experts, world, rank, (uint16_t*)send_rows->ptr, (uint32_t*)send_routes->ptr,
                    (uint32_t*)send_index->ptr, total + 64, (uint32_t*)dest_counts->ptr, total, segment_rows,
-                   total + 64 + (size_t)p->g.max_tokens * p->K, sort_scratch(p), p->device->stream);
+                   total + 64 + (size_t)p->g.max_tokens * p->K, p->status.as<uint32_t>(), sort_scratch(p), p->device->stream);
     p->launches += segment_rows ? 2 : 3;
     return post_launch(p, "expert-parallel pack");
 }
@@ -1812,7 +1809,9 @@ int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe
     const uint32_t T = a->batch_width, K = home->K, G = ep->world;
     NVMOE_TRY(check_tokens(home, T));
     const size_t H = home->g.hidden_size;
-    const size_t S = (size_t)home->g.max_tokens * K;  // slots per peer: the same on every rank
+    // slots per peer, the same on every rank: the worst case unless the caller bounds it
+    const size_t worst = (size_t)home->g.max_tokens * K;
+    const size_t S = (a->capacity_rows != 0u && a->capacity_rows < worst) ? a->capacity_rows : worst;
     if (work->K != 1u || work->g.hidden_size != home->g.hidden_size || work->g.intermediate_size != home->g.intermediate_size ||
         work->experts != home->experts || (size_t)work->g.max_tokens < S * G)
         return fail(d, NVMOE_ERR_INVALID_ARGUMENT,
@@ -1832,10 +1831,10 @@ int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe
     want(ep->recv_rows, G * S * H * 2u);
     want(ep->recv_routes, G * S * 4u);
     want(ep->work_out, G * S * H * 2u);
-    want(ep->returned, G * S * H * 2u);
-    want(ep->send_index, S * 4u);
+    want(ep->returned, (G * S > worst ? G * S : worst) * H * 2u);
+    want(ep->send_index, worst * 4u);
     want(ep->dest_counts, (size_t)G * 4u);
-    want(ep->expert_outputs, S * H * 2u);
+    want(ep->expert_outputs, worst * H * 2u);
     if (err != cudaSuccess)
         return fail(d, err == cudaErrorMemoryAllocation ? NVMOE_ERR_OUT_OF_MEMORY : NVMOE_ERR_CUDA,
                     "exchange buffer allocation failed: %s", cudaGetErrorString(err));

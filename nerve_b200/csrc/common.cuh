@@ -168,7 +168,7 @@ void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32
                     uint32_t K, uint32_t hidden_size, uint32_t num_experts, uint32_t world, uint32_t self,
                     uint16_t* send_rows, uint32_t* send_routes, uint32_t* send_index, uint32_t* send_source,
                     uint32_t* dest_counts, uint32_t* total, uint32_t segment_rows, uint32_t* contiguous_routes,
-                    const SortScratch& scratch, cudaStream_t stream);
+                    uint32_t* status, const SortScratch& scratch, cudaStream_t stream);
 void launch_ep_unpack(const uint16_t* returned_rows, const uint32_t* send_index, uint32_t tokens, uint32_t K,
                       uint32_t hidden_size, uint16_t* expert_outputs, cudaStream_t stream);
 

@@ -853,10 +853,14 @@ __global__ void __launch_bounds__(256) ep_pad_kernel(const uint4* __restrict__ h
                                                     const uint32_t* __restrict__ dest_counts,
                                                     const uint32_t* __restrict__ send_source, uint32_t world, uint32_t cap,
                                                     uint32_t K, uint32_t row_vec, uint4* __restrict__ rows_out,
-                                                    uint32_t* __restrict__ routes_out, uint32_t* __restrict__ send_index) {
+                                                    uint32_t* __restrict__ routes_out, uint32_t* __restrict__ send_index,
+                                                    uint32_t* status) {
     grid_dependency_sync();
     const uint32_t warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t slots = world * cap;
+    // a segment that cannot hold what is bound for its rank: the excess routes stay "nowhere" (send_index keeps
+    // its all-ones mark, the combine counts their rows as zeros) and the caller is told
+    if (blockIdx.x == 0u && threadIdx.x < world && dest_counts[threadIdx.x] > cap) raise_status(status, NVMOE_STATUS_EXCHANGE_OVERFLOW);
     for (uint32_t slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; slot < slots; slot += warps) {
         const uint32_t d = slot / cap, j = slot % cap;
         if (j >= min_u32(dest_counts[d], cap)) {
@@ -893,7 +897,7 @@ void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32
                     uint32_t K, uint32_t hidden_size, uint32_t num_experts, uint32_t world, uint32_t self,
                     uint16_t* send_rows, uint32_t* send_routes, uint32_t* send_index, uint32_t* send_source,
                     uint32_t* dest_counts, uint32_t* total, uint32_t segment_rows, uint32_t* contiguous_routes,
-                    const SortScratch& scratch, cudaStream_t stream) {
+                    uint32_t* status, const SortScratch& scratch, cudaStream_t stream) {
     const uint32_t count = tokens * K;
     DestKey key{routes, owner, num_experts, world, self};
     // the padded form packs positions only; its route words and rows are placed by ep_pad_kernel
@@ -914,7 +918,7 @@ void launch_ep_pack(const uint16_t* hidden, const uint32_t* routes, const uint32
         if (pad_blocks > 148u * 8u) pad_blocks = 148u * 8u;
         launch_chained(ep_pad_kernel, dim3(pad_blocks), dim3(256), 0, stream, reinterpret_cast<const uint4*>(hidden), routes,
                        dest_counts, send_source, world, segment_rows, K, row_vec, reinterpret_cast<uint4*>(send_rows),
-                       send_routes, send_index);
+                       send_routes, send_index, status);
         return;
     }
     sum_counts_kernel<<<1, 32, 0, stream>>>(dest_counts, world, total);

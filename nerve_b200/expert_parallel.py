@@ -151,11 +151,14 @@ class ExpertParallelLayer:
 
     def __init__(self, cfg, tokens_per_rank: int, rank: int, world: int, device_index: int, seed: int = 0,
                  owner_table: np.ndarray | None = None, expert_path: int = 0, mode: str = "auto", banks: int = 1,
-                 dist=None):
+                 dist=None, capacity_factor: float = 0.0):
         """mode: "native" = the library issues the collectives itself (one call per step, needs `dist` once to
         hand the communicator id round); "padded" / "ragged" = the same protocol over torch.distributed with
         fixed segments / with split sizes read on the host; "auto" = native when `dist` is given and the
-        fixed segments are small enough, else padded or ragged by size."""
+        fixed segments are small enough, else padded or ragged by size.
+        capacity_factor (native form): the segment a rank keeps for each peer holds this many times the mean
+        number of rows per peer (tokens * top_k / world), instead of the worst case tokens * top_k; 0 = worst
+        case. A step whose routing overflows a segment raises NVMOE_STATUS_EXCHANGE_OVERFLOW (`overflowed()`)."""
         import torch
 
         from . import synthetic
@@ -174,18 +177,24 @@ class ExpertParallelLayer:
         self.stream = torch.cuda.Stream(device=self.tdev)
         self.device.set_stream(self.stream.cuda_stream)
         T, K, H, G = tokens_per_rank, cfg.total_k, cfg.hidden, world
-        self.capacity = T * K * G
-        self.segment = T * K  # the most rows one rank can be sent by one peer
+        bounded = T * K  # the most rows one rank can be sent by one peer
+        if capacity_factor > 0.0 and G > 1:
+            eights = -(-int(np.ceil(capacity_factor * T * K / G)) // 8) * 8  # whole groups of eight rows
+            bounded = max(8, min(T * K, eights))
         if mode == "auto":
             mode = os.environ.get("NVMOE_EP_MODE", "auto")
         if mode == "auto":
-            small = self.capacity * H * 2 <= PADDED_EXCHANGE_LIMIT_BYTES
+            small = bounded * G * H * 2 <= PADDED_EXCHANGE_LIMIT_BYTES
             mode = ("native" if dist is not None else "padded") if small else "ragged"
         if mode not in ("native", "padded", "ragged"):
             raise ValueError(f"unknown exchange mode {mode!r}")
         if mode == "native" and dist is None:
             raise ValueError("the native exchange needs torch.distributed once, to share the communicator id")
         self.mode = mode
+        # the fixed-segment forms may bound their segments; the ragged form sizes its receive buffer for the worst case
+        self.segment = bounded if mode in ("native", "padded") else T * K
+        self.capacity_factor = capacity_factor if self.segment < T * K else 0.0
+        self.capacity = self.segment * G
         # this rank's tokens: rank r owns tokens [r*T, (r+1)*T) of the global batch
         case = synthetic.make_case(cfg, T * G, seed=seed, with_weights=False)
         self.case = case
@@ -325,7 +334,8 @@ class ExpertParallelLayer:
         if self.mode == "native":
             b = self.b
             self.group.layer(self.home, self.work, self.tokens, self.bank, b["hidden"], b["output"], b["owner"],
-                             b["router_w"], self.router_bias, self.select_bias, self.telemetry)
+                             b["router_w"], self.router_bias, self.select_bias, self.telemetry,
+                             capacity_rows=self.segment if self.segment < self.tokens * self.cfg.total_k else 0)
             return self.tokens * self.cfg.total_k, -1
         with self.torch.cuda.stream(self.stream):
             if self.mode == "padded":
@@ -336,3 +346,8 @@ class ExpertParallelLayer:
     def output(self) -> np.ndarray:
         self.torch.cuda.synchronize()
         return self.t_output.cpu().numpy().view(np.uint16)
+
+    def overflowed(self) -> bool:
+        """Whether a step since the last call left routes out because a capacity-bounded segment was full
+        (reads and clears the plan's status word: synchronises)."""
+        return bool(self.home.status() & 16)

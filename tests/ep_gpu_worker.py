@@ -31,16 +31,26 @@ def main() -> int:
         alone = LayerRunner(cfg, tokens * world, 5, path, device_index=local, banks=1)
         alone.plan.layer(tokens * world, alone.bank, alone.hidden, alone.output, **alone.kw)
         want = alone.output.read(np.uint16).reshape(tokens * world, cfg.hidden)[rank * tokens:(rank + 1) * tokens]
-        # split sizes read on the host / fixed segments over torch.distributed / the library's own collectives
-        for mode in ("ragged", "padded", "native"):
-            layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path, mode=mode, dist=dist)
+        # split sizes read on the host / fixed segments over torch.distributed / the library's own collectives, the
+        # last two also with segments bounded at 1.5 times the mean rows per peer
+        for mode, factor in (("ragged", 0.0), ("padded", 0.0), ("native", 0.0), ("padded", 1.5), ("native", 1.5)):
+            layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path, mode=mode, dist=dist,
+                                        capacity_factor=factor)
             for _ in range(2):  # the second step reuses every buffer
                 sent, received = layer.step(dist)
             got = layer.output()
-            same = np.array_equal(got, want)
-            print(f"rank {rank} path {path} {mode}: sent {sent} received {received} parity {'ok' if same else 'FAILED'} "
-                  f"({int((got != want).sum())} of {got.size} values differ)", flush=True)
+            same = np.array_equal(got, want) and not layer.overflowed()
+            print(f"rank {rank} path {path} {mode} x{factor}: sent {sent} received {received} segment {layer.segment} "
+                  f"parity {'ok' if same else 'FAILED'} ({int((got != want).sum())} of {got.size} values differ)", flush=True)
             failures += 0 if same else 1
+        # segments far too small: the step completes, leaves the excess routes out and says so
+        layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=5, expert_path=path, mode="native", dist=dist,
+                                    capacity_factor=0.25)
+        layer.step(dist)
+        layer.output()
+        noticed = layer.overflowed()
+        print(f"rank {rank} path {path} native x0.25: segment {layer.segment} overflow {'noticed' if noticed else 'MISSED'}", flush=True)
+        failures += 0 if noticed else 1
     flag = torch.tensor([failures], device=f"cuda:{local}")
     dist.all_reduce(flag)
     dist.destroy_process_group()

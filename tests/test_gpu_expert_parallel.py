@@ -35,4 +35,5 @@ def test_sharded_layer_matches_single_gpu_layer(world):
            "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "ep_gpu_worker.py")]
     done = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=240)
     assert done.returncode == 0, done.stdout[-4000:] + done.stderr[-4000:]
-    assert done.stdout.count("parity ok") == 6 * world  # two expert paths x three exchange forms per rank
+    assert done.stdout.count("parity ok") == 10 * world  # two expert paths x five exchange forms per rank
+    assert done.stdout.count("overflow noticed") == 2 * world

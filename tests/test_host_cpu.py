@@ -27,7 +27,7 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(capi.Geometry) == 23 * 4
     assert ctypes.sizeof(capi.LayerArgs) == 3 * 4 + 4 + 14 * 8
     assert ctypes.sizeof(capi.WorkReport) == 4 + 8 * 4 + 3 * 4 + 4 * 4 + 8
-    assert ctypes.sizeof(capi.EpLayerArgs) == 4 + 4 + 11 * 8
+    assert ctypes.sizeof(capi.EpLayerArgs) == 4 + 4 + 11 * 8 + 8
 
 
 def test_expert_parallel_entry_points_reject_bad_arguments_without_a_gpu():
