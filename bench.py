@@ -445,8 +445,62 @@ def run_single_gpu(args, cfg, tokens, bound):
 
 # ---- N GPUs: the layer expert-sharded over the ranks ------------------------------------------------------------
 
+def ep_timed(torch, dist, layer, step_fn, steps, min_seconds, local):
+    """Blocks of exactly `steps` steps back to back between two events on the stream they run on, a barrier and a
+    synchronise on both sides of every block, the slowest rank's time; blocks repeat until `min_seconds` of
+    device time. Every rank sees the same (all-reduced) times, so every rank stops after the same block."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blocks, total, launches = [], 0.0, 0
+    while total < min_seconds * 1e3 and len(blocks) < 200:
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        before = layer.home.launches() + layer.work.launches()
+        start.record(layer.stream)
+        for _ in range(steps):
+            step_fn()
+        stop.record(layer.stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([start.elapsed_time(stop) / steps], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        launches = layer.home.launches() + layer.work.launches() - before
+        blocks.append(float(t.item()))
+        total += blocks[-1] * steps
+    return blocks, launches
+
+
+def ep_parity(torch, dist, layer, cfg, tokens, rank, world, local, seed, sample=8):
+    """This rank's slice of the global batch against the CPU checker (outside every timed region): routes of all
+    its tokens bit for bit, the layer output on a seeded sample of them; the worst rank is reported."""
+    from oracle import sampled
+
+    layer.step(dist)
+    got = layer.output()
+    with torch.cuda.stream(layer.stream):
+        layer._route()  # this rank's routes into buffers the host can read (the library's step keeps its own)
+    torch.cuda.synchronize()
+    case = layer.case
+    mine = np.arange(rank * tokens, (rank + 1) * tokens)
+    hidden, bias = case.hidden[mine], case.select_bias
+    want_logits, want_routes, _ = sampled.routing_for_batch(cfg, hidden, case.router_w, case.router_bias, bias)
+    picked = sampled.sample_tokens(tokens, sample, seed=rank)
+    want = sampled.layer_on_sample(cfg, hidden, want_logits, bias, picked, lambda e: synthetic.expert_tensors(cfg, seed, e))
+    m = sampled.error_metrics(got[picked], want["output"])
+    routes_exact = bool(np.array_equal(layer.t_routes.cpu().numpy().view(np.uint32), want_routes))
+    overflow = layer.overflowed()
+    ok = torch.tensor([1 if (sampled.within_tolerance(m) and routes_exact and not overflow) else 0], device=f"cuda:{local}")
+    worst = torch.tensor([m["rel_l2"], m["max_abs_over_peak"], m["max_abs"]], device=f"cuda:{local}", dtype=torch.float64)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {"pass": bool(ok.item()), "routes_exact": routes_exact, "rel_l2": float(worst[0]), "max_abs_over_peak": float(worst[1]),
+            "max_abs": float(worst[2]), "sample_tokens": int(len(picked)) * world,
+            "note": "every rank checks a seeded sample of its own tokens against the CPU checker; worst rank shown"}
+
+
 def run_expert_parallel(args, cfg, tokens):
-    """bench.py --gpus N: the layer expert-sharded over N ranks, tokens per rank fixed (weak scaling)."""
+    """bench.py --gpus N: the layer expert-sharded over N ranks, tokens per rank fixed (weak scaling); the two
+    large layers follow as `extra`, their whole batch split over the ranks (strong scaling)."""
     import torch
     import torch.distributed as dist
 
@@ -458,6 +512,7 @@ def run_expert_parallel(args, cfg, tokens):
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    capacity_factor = float(os.environ.get("NVMOE_EP_CAPACITY", "2.0"))
     # enough resident copies of this rank's experts that a step's weights were last read 4 x L2 ago
     per_expert = cfg.expert_weight_bytes
     owned = cfg.experts // world + cfg.always_count
@@ -465,44 +520,15 @@ def run_expert_parallel(args, cfg, tokens):
     banks = args.banks or max(2, min(8, -(-4 * L2_BYTES // touched)))
     # segments bounded at twice the mean rows per peer (NVMOE_EP_CAPACITY=0: the worst case); an overflow is reported
     layer = ExpertParallelLayer(cfg, tokens, rank, world, local, seed=args.seed, expert_path=args.expert_path, banks=banks,
-                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"),
-                                capacity_factor=float(os.environ.get("NVMOE_EP_CAPACITY", "2.0")))
+                                dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"), capacity_factor=capacity_factor)
     for _ in range(max(args.warmup, 3, banks + 1)):
         layer.step(dist)
     torch.cuda.synchronize()
     dist.barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-
-    def block(step_fn):
-        # exactly `steps` steps back to back between two events on the stream they run on, a barrier and a
-        # synchronise on both sides, the slowest rank's time
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        before = layer.home.launches() + layer.work.launches()
-        start.record(layer.stream)
-        for _ in range(args.steps):
-            step_fn()
-        stop.record(layer.stream)
-        torch.cuda.synchronize()
-        dist.barrier()
-        t = torch.tensor([start.elapsed_time(stop) / args.steps], device=f"cuda:{local}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), layer.home.launches() + layer.work.launches() - before
-
-    def repeat(step_fn, min_seconds):
-        # every rank sees the same (all-reduced) block times, so every rank stops after the same block
-        blocks, total, launches = [], 0.0, 0
-        while total < min_seconds * 1e3 and len(blocks) < 200:
-            ms, launches = block(step_fn)
-            blocks.append(ms)
-            total += ms * args.steps
-        return blocks, launches
-
-    blocks, launches = repeat(lambda: layer.step(dist), MIN_TIMED_SECONDS)
+    blocks, launches = ep_timed(torch, dist, layer, lambda: layer.step(dist), args.steps, MIN_TIMED_SECONDS, local)
     clocks = sampler.stop() if sampler else None
     # end to end: tokens start in pinned host memory, the result is read back
     host_in = torch.from_numpy(layer.hidden_host.view(np.int16)).pin_memory()
@@ -514,36 +540,55 @@ def run_expert_parallel(args, cfg, tokens):
             layer.step(dist)
             host_out.copy_(layer.t_output, non_blocking=True)
 
-    e2e_blocks, _ = repeat(host_step, 0.2)
+    e2e_blocks, _ = ep_timed(torch, dist, layer, host_step, args.steps, 0.2, local)
     ms, e2e_ms = statistics.median(blocks), statistics.median(e2e_blocks)
     overflow = torch.tensor([1 if layer.overflowed() else 0], device=f"cuda:{local}")
     dist.all_reduce(overflow, op=dist.ReduceOp.MAX)
+    parity = None if args.no_parity else ep_parity(torch, dist, layer, cfg, tokens, rank, world, local, args.seed)
+    headline = {"mode": layer.mode, "segment": layer.segment, "capacity_factor": layer.capacity_factor}
+    del layer
+    torch.cuda.empty_cache()
 
-    # parity of this rank's slice of the global batch against the CPU checker (outside every timed region)
-    parity = None
-    if not args.no_parity:
-        from oracle import sampled
-
-        layer.step(dist)
-        got = layer.output()
-        with torch.cuda.stream(layer.stream):
-            layer._route()  # this rank's routes into buffers the host can read (the library's step keeps its own)
-        torch.cuda.synchronize()
-        case = layer.case
-        want_logits, want_routes, _ = sampled.routing_for_batch(cfg, case.hidden, case.router_w, case.router_bias, case.select_bias)
-        mine = np.arange(rank * tokens, (rank + 1) * tokens)
-        picked = mine[sampled.sample_tokens(tokens, 8, seed=rank)]
-        want = sampled.layer_on_sample(cfg, case.hidden, want_logits, case.select_bias, picked,
-                                       lambda e: synthetic.expert_tensors(cfg, args.seed, e))
-        m = sampled.error_metrics(got[picked - rank * tokens], want["output"])
-        routes_exact = bool(np.array_equal(layer.t_routes.cpu().numpy().view(np.uint32), want_routes[mine]))
-        ok = torch.tensor([1 if (sampled.within_tolerance(m) and routes_exact) else 0], device=f"cuda:{local}")
-        worst = torch.tensor([m["rel_l2"], m["max_abs_over_peak"], m["max_abs"]], device=f"cuda:{local}", dtype=torch.float64)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-        parity = {"pass": bool(ok.item()), "routes_exact": routes_exact, "rel_l2": float(worst[0]), "max_abs_over_peak": float(worst[1]),
-                  "max_abs": float(worst[2]), "sample_tokens": int(len(picked)) * world,
-                  "note": "every rank checks a seeded sample of its own tokens against the CPU checker; worst rank shown"}
+    # the layers the expert-parallel configurations are stated for: the whole batch split over the ranks
+    extra = {}
+    if not args.no_extra and args.workload == "gpt-oss-20b-decode":
+        for key, workload in (("ep_gpt_oss_120b", "gpt-oss-120b"), ("ep_deepseek_v3", "deepseek-v3")):
+            try:
+                big_name, total, _ = WORKLOADS[workload]
+                big = synthetic.CONFIGS[big_name]
+                if total % world or big.experts % world:
+                    raise ValueError(f"{total} tokens or {big.experts} experts do not split over {world} ranks")
+                per_rank = total // world
+                big_layer = ExpertParallelLayer(big, per_rank, rank, world, local, seed=args.seed, expert_path=args.expert_path,
+                                                banks=1, dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"),
+                                                capacity_factor=1.5 if capacity_factor > 0.0 else 0.0)
+                for _ in range(3):
+                    big_layer.step(dist)
+                torch.cuda.synchronize()
+                big_blocks, big_launches = ep_timed(torch, dist, big_layer, lambda: big_layer.step(dist), 3, 0.1, local)
+                big_ms = statistics.median(big_blocks)
+                big_overflow = torch.tensor([1 if big_layer.overflowed() else 0], device=f"cuda:{local}")
+                dist.all_reduce(big_overflow, op=dist.ReduceOp.MAX)
+                entry = {
+                    "tokens": total, "tokens_per_rank": per_rank, "experts_per_rank": big.experts // world, "scaling": "strong",
+                    "tokens_per_s": total / (big_ms * 1e-3), "ms_per_step": big_ms, "timing": spread(big_blocks),
+                    "launches_per_step": big_launches / 3, "exchange": big_layer.mode, "segment_rows": big_layer.segment,
+                    "segment_overflow_in_timed_steps": bool(big_overflow.item()),
+                    # rows of routed experts that leave a rank, each way: (world - 1) / world of its routed rows on average
+                    "all_to_all_bytes_per_direction_per_rank": int(per_rank * big.k * big.hidden * 2 * (world - 1) / world),
+                    "layer_tflops": layer_flops(big, total) / (big_ms * 1e-3) / 1e12,
+                }
+                if not args.no_parity:
+                    entry["parity"] = ep_parity(torch, dist, big_layer, big, per_rank, rank, world, local, args.seed, sample=4)
+                extra[key] = entry
+                del big_layer
+                torch.cuda.empty_cache()
+            except Exception as error:  # the headline line must not depend on an extra
+                extra[key] = {"error": f"{type(error).__name__}: {error}"}
+                try:
+                    dist.barrier()
+                except Exception:
+                    pass
 
     if rank == 0:
         total_tokens = tokens * world
@@ -558,7 +603,7 @@ def run_expert_parallel(args, cfg, tokens):
                 "experts_per_rank": cfg.experts // world,
                 "parallelism": f"ep{world}: experts sharded by contiguous range, tokens data-parallel, "
                                "NCCL all-to-all dispatch and combine",
-                "exchange": layer.mode, "segment_rows": layer.segment, "capacity_factor": layer.capacity_factor,
+                "exchange": headline["mode"], "segment_rows": headline["segment"], "capacity_factor": headline["capacity_factor"],
                 "segment_overflow_in_timed_steps": bool(overflow.item()),
                 "l2": f"inputs larger than L2: {banks} resident weight banks per rank visited in turn, "
                       f"{touched * banks / 1e6:.0f} MB of weights read between two reads of the same bytes"},
@@ -574,6 +619,8 @@ def run_expert_parallel(args, cfg, tokens):
         }
         if parity:
             line["parity"] = parity
+        if extra:
+            line["extra"] = extra
         print(json.dumps(line))
     dist.destroy_process_group()
 

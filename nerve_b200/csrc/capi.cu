@@ -1890,6 +1890,14 @@ int nvmoe_ep_layer(nvmoe_ep* ep, nvmoe_plan* home, nvmoe_plan* work, const nvmoe
         d->error = first_text;
         return first_error;
     }
+    // the combine reads the returned rows through the positions the pack step recorded; shapes it cannot take
+    // that way go through the explicit unpack
+    NVMOE_TRY(check_buffer(home, a->output, (size_t)T * H * 2u, "output"));
+    if (launch_reduce_gather((const uint16_t*)returned.ptr, (const uint32_t*)send_index.ptr, (uint16_t*)a->output->ptr, T, K,
+                             (uint32_t)H, home->g.reduce_scale, d->stream)) {
+        home->launches++;
+        return post_launch(home, "combine of returned rows");
+    }
     NVMOE_TRY(nvmoe_ep_unpack(home, T, &returned, &send_index, &expert_outputs));
     return nvmoe_reduce(home, T, &expert_outputs, a->output);
 }

@@ -242,6 +242,10 @@ void launch_route_preselected(const uint32_t* logits, const uint32_t* selections
 void launch_dense_schedule(uint32_t rows, uint32_t n_tile, uint32_t* grouped, uint32_t* offsets, uint32_t* position, uint32_t* tiles,
                            uint32_t* tile_count, cudaStream_t stream);
 
+// reduce.cu: the same combine with route (t, r) read from row gather[t * K + r] of `rows` (all-ones = a row of
+// zeros); false when the shape needs the plain form (hidden not a multiple of 8, unaligned buffers)
+bool launch_reduce_gather(const uint16_t* rows, const uint32_t* gather, uint16_t* output, uint32_t tokens, uint32_t K,
+                          uint32_t hidden, float routed_scale, cudaStream_t stream);
 // reduce.cu: distributed_sum_f32_scale_packed_bf16_to_bf16: out[lane][e] = bf16(sum over participants of
 // partials[participant][lane][e] * bf16(scales[lane * (elements / elements_per_scale) + e / elements_per_scale] >> bit_offset))
 void launch_sum_f32_scale_packed_bf16(const float* partials, const uint32_t* scales, uint32_t* output, uint32_t element_count,

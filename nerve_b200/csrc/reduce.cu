@@ -64,6 +64,39 @@ __global__ void __launch_bounds__(256) reduce_vec_kernel(const uint4* __restrict
     }
 }
 
+// The combine of an expert-parallel step read straight from the rows that came back from the owners:
+// route (t, r) lies at row gather[t * K + r] of `rows` (all-ones: the route was left out and counts as a row
+// of zeros). The same adds in the same order with the same roundings as reduce_vec_kernel; only where a row is
+// read from differs, which saves the pass that would put the rows back into [T][K][H] order first.
+__global__ void __launch_bounds__(256) reduce_gather_kernel(const uint4* __restrict__ rows, const uint32_t* __restrict__ gather,
+                                                           uint4* __restrict__ output, uint32_t tokens, uint32_t K,
+                                                           uint32_t hidden_vecs, float routed_scale) {
+    grid_dependency_sync();
+    const uint64_t total = (uint64_t)tokens * hidden_vecs;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / hidden_vecs), vec = (uint32_t)(i % hidden_vecs);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] = 0.0f;
+        for (uint32_t r = 0; r < K; r++) {
+            const uint32_t row = __ldg(gather + (size_t)t * K + r);
+            const uint4 c = row == kUnboundSlot ? make_uint4(0u, 0u, 0u, 0u) : rows[(size_t)row * hidden_vecs + vec];
+            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                acc[2 * j] = nvmoe_round_bf16(__fadd_rn(acc[2 * j], nvmoe_bf16_to_f32(w[j])));
+                acc[2 * j + 1] = nvmoe_round_bf16(__fadd_rn(acc[2 * j + 1], nvmoe_bf16_to_f32(w[j] >> 16)));
+            }
+        }
+        uint4 out;
+        out.x = pack_bf16x2(__fmul_rn(acc[0], routed_scale), __fmul_rn(acc[1], routed_scale));
+        out.y = pack_bf16x2(__fmul_rn(acc[2], routed_scale), __fmul_rn(acc[3], routed_scale));
+        out.z = pack_bf16x2(__fmul_rn(acc[4], routed_scale), __fmul_rn(acc[5], routed_scale));
+        out.w = pack_bf16x2(__fmul_rn(acc[6], routed_scale), __fmul_rn(acc[7], routed_scale));
+        output[i] = out;
+    }
+}
+
 // The finaliser of a tensor-parallel expert stage
 // (runtime-rs/shaders/distributed_sum_f32_scale_packed_bf16_to_bf16.comp:44-66): the participants' f32
 // partial planes are added in participant order, the sum is scaled by a bf16 taken from a packed word
@@ -101,6 +134,18 @@ void launch_sum_f32_scale_packed_bf16(const float* partials, const uint32_t* sca
     if (blocks == 0u) return;
     launch_chained(sum_f32_scale_packed_bf16_kernel, dim3((uint32_t)blocks), dim3(256), 0, stream, partials, scales, output,
                    element_count, participant_count, lane_count, elements_per_scale, scale_bit_offset);
+}
+
+bool launch_reduce_gather(const uint16_t* rows, const uint32_t* gather, uint16_t* output, uint32_t tokens, uint32_t K,
+                          uint32_t hidden, float routed_scale, cudaStream_t stream) {
+    if (hidden % 8u != 0u || ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(output)) & 15u) != 0u) return false;
+    const uint64_t vecs = (uint64_t)tokens * (hidden / 8u);
+    uint64_t blocks = (vecs + 255u) / 256u;
+    if (blocks > 148u * 16u) blocks = 148u * 16u;
+    if (blocks == 0u) return true;
+    launch_chained(reduce_gather_kernel, dim3((uint32_t)blocks), dim3(256), 0, stream, reinterpret_cast<const uint4*>(rows), gather,
+                   reinterpret_cast<uint4*>(output), tokens, K, hidden / 8u, routed_scale);
+    return true;
 }
 
 void launch_reduce(const uint16_t* expert_outputs, uint16_t* output, uint32_t tokens, uint32_t K, uint32_t hidden,
