@@ -559,9 +559,22 @@ def run_expert_parallel(args, cfg, tokens):
                 if total % world or big.experts % world:
                     raise ValueError(f"{total} tokens or {big.experts} experts do not split over {world} ranks")
                 per_rank = total // world
-                big_layer = ExpertParallelLayer(big, per_rank, rank, world, local, seed=args.seed, expert_path=args.expert_path,
-                                                banks=1, dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"),
-                                                capacity_factor=1.5 if capacity_factor > 0.0 else 0.0)
+                # building the layer is the step that can fail on one rank alone (memory): the ranks agree on the
+                # outcome before any of them enters a collective of the measurement
+                big_layer, problem = None, ""
+                try:
+                    big_layer = ExpertParallelLayer(big, per_rank, rank, world, local, seed=args.seed, expert_path=args.expert_path,
+                                                    banks=1, dist=dist, mode=os.environ.get("NVMOE_EP_MODE", "auto"),
+                                                    capacity_factor=1.5 if capacity_factor > 0.0 else 0.0)
+                except Exception as error:
+                    problem = f"{type(error).__name__}: {error}"
+                failed = torch.tensor([0 if big_layer is not None else 1], device=f"cuda:{local}")
+                dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+                if int(failed.item()):
+                    del big_layer
+                    torch.cuda.empty_cache()
+                    extra[key] = {"error": problem or "another rank could not build the layer"}
+                    continue
                 for _ in range(3):
                     big_layer.step(dist)
                 torch.cuda.synchronize()
@@ -585,10 +598,7 @@ def run_expert_parallel(args, cfg, tokens):
                 torch.cuda.empty_cache()
             except Exception as error:  # the headline line must not depend on an extra
                 extra[key] = {"error": f"{type(error).__name__}: {error}"}
-                try:
-                    dist.barrier()
-                except Exception:
-                    pass
+                break  # a rank that failed inside a measurement is no longer in step with the others
 
     if rank == 0:
         total_tokens = tokens * world

@@ -137,7 +137,7 @@ struct nvmoe_plan {
     DeviceArray tmap_templates;  // tensor maps of the two weight matrix shapes; each expert's map is one with its address patched in
     bool tma[2] = {false, false};
     // scratch of the fused layer call
-    DeviceArray logits, routes, frames, expert_outputs, controls, combine_counters, hidden_dev, output_dev;
+    DeviceArray logits, routes, frames, expert_outputs, controls, hidden_dev, output_dev;
     void* pinned_in = nullptr;
     void* pinned_out = nullptr;
     size_t pinned_bytes = 0;
@@ -845,7 +845,6 @@ struct ExpertCall {
     uint32_t* intermediates = nullptr;
     uint16_t* outputs = nullptr;
     float* partial_outputs = nullptr;      // down only: raw f32 sums instead of weighted bf16 rows
-    uint16_t* combine_out = nullptr;       // down on the tensor path only: the epilogue also combines into [T][H]
     const nvmoe_buffer* addresses = nullptr;
     const nvmoe_buffer* slots = nullptr;
     const uint32_t* control = nullptr;
@@ -901,12 +900,6 @@ static int run_experts(nvmoe_plan* p, const ExpertCall& c) {
             el.q_out = p->grouped_q[1].as<uint8_t>();
             el.q_e8m0 = p->grouped_e8m0[1].as<uint32_t>();
             el.down_position = p->position[1].as<uint32_t>();
-        }
-        if (c.combine_out && !gate_up) {
-            el.down_position = p->position[1].as<uint32_t>();
-            el.combine_out = c.combine_out;
-            el.combine_counters = p->combine_counters.as<uint32_t>();
-            el.combine_scale = g.reduce_scale;
         }
     }
     if (p->profile_stages) cudaEventRecord(p->kernel_ev[set][0], st);
@@ -1334,7 +1327,6 @@ static int ensure_layer_scratch(nvmoe_plan* p) {
     want(p->frames, T * (size_t)p->frame_words * 4u);
     want(p->expert_outputs, T * p->K * (size_t)g.hidden_size * 2u);
     want(p->controls, 64u);
-    want(p->combine_counters, T * ((g.hidden_size + 127u) / 128u) * 4u);
     if (err == cudaSuccess && fresh_frames) err = cudaMemsetAsync(p->frames.ptr, 0, p->frames.bytes, p->device->stream);
     if (err != cudaSuccess)
         return fail(p->device, err == cudaErrorMemoryAllocation ? NVMOE_ERR_OUT_OF_MEMORY : NVMOE_ERR_CUDA,
@@ -1394,18 +1386,8 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     ExpertSet* sets[2] = {nullptr, nullptr};
     NVMOE_TRY(prepare_expert_set(p, true, a->gate_up_addresses, a->gate_up_slots, tensor, &sets[0]));
     NVMOE_TRY(prepare_expert_set(p, false, a->down_addresses, a->down_slots, tensor, &sets[1]));
-    // The small schedule kernel can prepare what the down kernel needs to do the combine in its epilogue: the
-    // arrival counters at zero and zero rows for tokens the stage computes nothing for.
-    const bool fused_combine =
-        tensor && !a->expert_outputs && g.hidden_size % 4u == 0u && layer_schedule_prepares_combine(T, p->K, p->experts);
     if (layer_schedule_is_small(T, p->K, p->experts)) {
         LayerSchedule ls{};
-        if (fused_combine) {
-            ls.zero_output = (uint16_t*)a->output->ptr;
-            ls.zero_hidden = g.hidden_size;
-            ls.combine_counters = p->combine_counters.as<uint32_t>();
-            ls.combine_words = T * ((g.hidden_size + 127u) / 128u);
-        }
         ls.routes = (const uint32_t*)routes->ptr;
         ls.intermediates = (uint32_t*)frames.ptr;
         ls.slots[0] = (const uint32_t*)a->gate_up_slots->ptr;
@@ -1478,10 +1460,9 @@ int nvmoe_layer(nvmoe_plan* p, const nvmoe_layer_args* a) {
     call.control = (const uint32_t*)down_control.ptr;
     call.prepared = sets[1];
     call.fuse_quantise = false;
-    call.combine_out = fused_combine ? (uint16_t*)a->output->ptr : nullptr;
     NVMOE_TRY(run_experts(p, call));
     mark(kStageReduce);
-    if (!a->expert_outputs && !fused_combine) {
+    if (!a->expert_outputs) {
         launch_reduce((const uint16_t*)outs.ptr, (uint16_t*)a->output->ptr, T, p->K, g.hidden_size, g.reduce_scale,
                       p->position[1].as<uint32_t>(), st);
         p->launches++;

@@ -142,16 +142,8 @@ struct LayerSchedule {
     uint32_t* tile_count[2];
     uint32_t* status;
     uint32_t tokens, expert_start, expert_count, K, I, tiles_per_route[2], num_experts, n_tile[2];
-    // optional: the layer's output [tokens][zero_hidden] bf16; the row of a token none of whose routes the down
-    // stage computes is set to zero here (the fused combine of the down kernel never visits such a token)
-    uint16_t* zero_output;
-    uint32_t zero_hidden;
-    // optional: the arrival counters of the down kernel's fused combine, set to zero here for this launch
-    uint32_t* combine_counters;
-    uint32_t combine_words;
 };
 bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts);
-bool layer_schedule_prepares_combine(uint32_t tokens, uint32_t K, uint32_t num_experts);
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream);
 // validates the address/slot tables of every expert once per call
 // (rows, cols: logical shape of one matrix; experts from native_start on hold native FP8; with
@@ -217,16 +209,8 @@ struct ExpertLaunch {  // experts_simt.cu and experts_tc.cu
     // tensor path: act_q / act_e8m0 hold expert-grouped rows (row = position in grouped_routes);
     // act_tmap is the tensor map of act_q with a box of [token tile][128 bytes] (null: fetch rows with cp.async)
     const uint8_t* act_tmap;
-    // tensor path: where the down stage's grouping puts each route (its operand row; all-ones = the stage skips
-    // the route). Gate/up uses it to place the down stage's operands, down to know which routes a token waits for.
+    // tensor path, gate/up only: where the down stage's grouping puts each route (its operand row)
     const uint32_t* down_position;
-    // tensor path, down only, optional: the combine done by the epilogue. combine_out [T][H] bf16 receives, for
-    // every token and row tile, the sum of the token's K rows in route order with the reduce shader's roundings,
-    // written by whichever warp stores the last of those rows (combine_counters [T][row tiles] counts arrivals and
-    // is zero when the kernel starts).
-    uint16_t* combine_out;
-    uint32_t* combine_counters;
-    float combine_scale;
     // tensor path, gate/up only, optional: the down stage's activation quantisation done in the epilogue
     // (E4M3 bytes [down_position][I], E8M0 bytes [down_position][ceil(I/128)] words); needs act_block 32
     uint8_t* q_out;

@@ -691,56 +691,6 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             }
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[acc]);
-            if (!GATE_UP && p.combine_out != nullptr) {
-                // The combine, fused (runtime-rs/shaders/moe_reduce_batch1_bf16.comp.template:29-55). A token's rows of
-                // this row tile are written by the four warps of one epilogue group, in this tile and in the tiles of
-                // the token's other experts. Every warp counts itself in for each of its tokens once its rows are
-                // visible; the warp that completes the count (four warps for every route the down stage computes)
-                // adds the token's rows in route order, rounding to bf16 after every add as the shader does, and
-                // writes the output. No barrier between warps: a warp that gave up a wait cannot leave another waiting.
-                __threadfence();
-                __syncwarp();
-                for (uint32_t j0 = 0; j0 < N_TILE; j0 += 32u) {
-                    const uint32_t j = j0 + lane;
-                    const bool mine = j < valid && (kShareByFours ? (j / 4u) % C::kEpilogueGroups == epilogue_group
-                                                                  : (j / 16u) % C::kEpilogueGroups == epilogue_group);
-                    uint32_t token = 0u;
-                    bool last = false;
-                    if (mine) {
-                        token = __ldg(p.work.grouped_routes + first + j) / K;
-                        uint32_t expected = 0u;
-                        for (uint32_t r = 0; r < K; r++) expected += __ldg(p.down_position + (size_t)token * K + r) != kUnboundSlot ? 1u : 0u;
-                        uint32_t* counter = p.combine_counters + (size_t)token * m_tiles + m_tile;
-                        last = atomicAdd(counter, 1u) + 1u == 4u * expected;
-                    }
-                    uint32_t pending = __ballot_sync(0xffffffffu, last);
-                    if (pending != 0u) __threadfence();  // the other warps' rows, published before their arrivals
-                    while (pending != 0u) {
-                        const uint32_t t = __shfl_sync(0xffffffffu, token, __ffs(pending) - 1);
-                        pending &= pending - 1u;
-#pragma unroll
-                        for (uint32_t pass = 0; pass < C::kTileRows / kBlockM; pass++) {
-                            const uint32_t r0 = m_tile * C::kTileRows + pass * kBlockM + 4u * lane;  // four rows a lane
-                            if (r0 >= out_rows) continue;
-                            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                            for (uint32_t r = 0; r < K; r++) {
-                                const size_t route = (size_t)t * K + r;
-                                uint2 v = make_uint2(0u, 0u);  // a route the stage skipped counts as a row of zeros
-                                if (__ldg(p.down_position + route) != kUnboundSlot)
-                                    v = __ldcg(reinterpret_cast<const uint2*>(p.outputs + route * H + r0));
-                                sum[0] = nvmoe_round_bf16(__fadd_rn(sum[0], nvmoe_bf16_to_f32(v.x)));
-                                sum[1] = nvmoe_round_bf16(__fadd_rn(sum[1], nvmoe_bf16_to_f32(v.x >> 16)));
-                                sum[2] = nvmoe_round_bf16(__fadd_rn(sum[2], nvmoe_bf16_to_f32(v.y)));
-                                sum[3] = nvmoe_round_bf16(__fadd_rn(sum[3], nvmoe_bf16_to_f32(v.y >> 16)));
-                            }
-                            uint2 out;
-                            out.x = pack_bf16x2(__fmul_rn(sum[0], p.combine_scale), __fmul_rn(sum[1], p.combine_scale));
-                            out.y = pack_bf16x2(__fmul_rn(sum[2], p.combine_scale), __fmul_rn(sum[3], p.combine_scale));
-                            *reinterpret_cast<uint2*>(p.combine_out + (size_t)t * H + r0) = out;
-                        }
-                    }
-                }
-            }
         }
         if (TRACE && blockIdx.x == 0u && threadIdx.x == 0u) {
             trace[6] = (uint64_t)trace_epi_wait;                 // epilogue: cycles waiting for an accumulator

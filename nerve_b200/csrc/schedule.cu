@@ -741,16 +741,6 @@ __global__ void __launch_bounds__(1024) layer_schedule_rank_kernel(LayerSchedule
             if (s.position[stage]) s.position[stage][i] = place;
         }
     }
-    for (uint32_t i = threadIdx.x; i < s.combine_words; i += blockDim.x) s.combine_counters[i] = 0u;
-    if (s.zero_output != nullptr && s.position[1] != nullptr) {
-        __syncthreads();  // the positions above were written by other threads of this block
-        for (uint32_t t = threadIdx.x; t < s.tokens; t += blockDim.x) {
-            bool any = false;
-            for (uint32_t r = 0; r < s.K; r++) any = any || s.position[1][(size_t)t * s.K + r] != kUnboundSlot;
-            if (!any)
-                for (uint32_t h = 0; h < s.zero_hidden / 2u; h++) reinterpret_cast<uint32_t*>(s.zero_output)[(size_t)t * (s.zero_hidden / 2u) + h] = 0u;
-        }
-    }
     for (uint32_t i = threadIdx.x; i < 2u * B; i += blockDim.x) {
         const uint32_t stage = i / B, b = i % B;
         // bucket E is never kept, so gbase[stage][E] is already the total the offsets end with
@@ -985,11 +975,6 @@ static bool three_sort_schedule_fits(uint64_t count, uint32_t num_experts) {
 bool layer_schedule_is_small(uint32_t tokens, uint32_t K, uint32_t num_experts) {
     const uint64_t count = (uint64_t)tokens * K;
     return rank_schedule_fits(count, num_experts) || three_sort_schedule_fits(count, num_experts);
-}
-
-// only the ranking form of the one-block schedule sets up the down kernel's fused combine
-bool layer_schedule_prepares_combine(uint32_t tokens, uint32_t K, uint32_t num_experts) {
-    return rank_schedule_fits((uint64_t)tokens * K, num_experts);
 }
 
 void launch_layer_schedule_small(const LayerSchedule& s, cudaStream_t stream) {
