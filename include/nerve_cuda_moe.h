@@ -162,7 +162,13 @@ int nvmoe_buffer_fill(nvmoe_buffer* buffer, size_t offset, int byte_value, size_
  * destroying it frees the handle only. The reference's buffers are always device-owned
  * (resident_buffers.rs:39-60); this exists so that collectives and kernels can share memory. */
 int nvmoe_buffer_wrap(nvmoe_device* device, void* device_ptr, size_t bytes, nvmoe_buffer** out);
+/* The address is for the caller's own kernels and copies. What a plan resolved from an address or slot
+ * table (validated pointers, re-tiled scales, tensor maps) is kept until the table is written through
+ * nvmoe_buffer_write or nvmoe_buffer_fill; a caller that changes a table through this address instead says
+ * so with nvmoe_buffer_mark_dirty before the next call that uses the table, or the old resolution is used.
+ * (Tables in wrapped buffers are resolved afresh on every call and need no mark.) */
 uint64_t nvmoe_buffer_device_address(const nvmoe_buffer* buffer);
+int nvmoe_buffer_mark_dirty(nvmoe_buffer* buffer);
 size_t nvmoe_buffer_byte_capacity(const nvmoe_buffer* buffer);
 
 /* Bounded wait for everything queued on the device (run_resident_kernel_sequence's

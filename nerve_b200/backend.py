@@ -129,6 +129,10 @@ class ResidentBuffer:
     def device_address(self) -> int:
         return int(self.device._lib.nvmoe_buffer_device_address(self._h))
 
+    def mark_dirty(self) -> None:
+        """Says that the contents changed behind this handle (through ``device_address``): plans resolve the table again."""
+        self.device._check(self.device._lib.nvmoe_buffer_mark_dirty(self._h))
+
     def destroy(self) -> None:
         if self._h:
             self.device._lib.nvmoe_buffer_destroy(self._h)

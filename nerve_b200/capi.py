@@ -85,6 +85,7 @@ PROTOTYPES = {
     "nvmoe_plan_status": (c_int, [c_void_p, POINTER(c_uint32)]),
     "nvmoe_plan_set_expert_path": (c_int, [c_void_p, c_int]),
     "nvmoe_plan_set_profiling": (c_int, [c_void_p, c_int]),
+    "nvmoe_buffer_mark_dirty": (c_int, [c_void_p]),
     "nvmoe_plan_set_wait_limit": (c_int, [c_void_p, c_uint64]),
     "nvmoe_plan_debug_withhold_arrival": (c_int, [c_void_p, c_int]),
     "nvmoe_router_linear": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p]),

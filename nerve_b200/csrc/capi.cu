@@ -374,7 +374,9 @@ int nvmoe_buffer_wrap(nvmoe_device* d, void* device_ptr, size_t bytes, nvmoe_buf
     b->ptr = device_ptr;
     b->bytes = bytes;
     b->owned = false;
-    b->uid = g_next_buffer_uid.fetch_add(1);
+    // handles over the same memory share an identity: a table that is wrapped afresh for every call keeps its
+    // place (and its derived copies) in a plan's cache instead of claiming a new one each time
+    b->uid = (1ull << 63) | (uint64_t)(uintptr_t)device_ptr;
     *out = b;
     return NVMOE_OK;
 }
@@ -430,6 +432,12 @@ int nvmoe_buffer_fill(nvmoe_buffer* b, size_t offset, int byte_value, size_t byt
 }
 
 uint64_t nvmoe_buffer_device_address(const nvmoe_buffer* b) { return b ? (uint64_t)(uintptr_t)b->ptr : 0u; }
+
+int nvmoe_buffer_mark_dirty(nvmoe_buffer* b) {
+    if (!b) return NVMOE_ERR_INVALID_ARGUMENT;
+    b->version++;
+    return NVMOE_OK;
+}
 size_t nvmoe_buffer_byte_capacity(const nvmoe_buffer* b) { return b ? b->bytes : 0u; }
 
 int nvmoe_sync(nvmoe_device* d, uint64_t timeout_ns) {

@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 from nerve_b200 import synthetic
-from nerve_b200.backend import CudaComputeDevice, CudaError, ExpertBank, MoePlan, address_table, geometry_from_config
+from nerve_b200.backend import CudaComputeDevice, CudaError, ExpertBank, MoePlan, ResidentBuffer, address_table, geometry_from_config
 from oracle import moe_oracle as mo
 from tests.helpers import assert_close, error_metrics, expert_params, oracle_layer, oracle_weights, router_params
 
@@ -143,6 +143,46 @@ def test_fails_closed_on_invalid_dynamic_metadata(device, path):
     routes.write_bytes(np.array([BF16_ONE << 16], dtype=np.uint32))
     plan.status()
     assert run().all()
+    plan.destroy()
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_table_changed_behind_its_handle_is_resolved_again_once_marked(device, path):
+    """A slot table rewritten through its device address (here: through a second handle over the same
+    memory) is only seen by a plan after nvmoe_buffer_mark_dirty; handles that wrap the same memory share
+    one place in the plan's cache."""
+    W = 128
+    cfg = _const_cfg(W)
+    plan = make_plan(device, cfg, 1, path)
+    hidden = device.resident_buffer_from(np.full(W, BF16_ONE, dtype=np.uint16))
+    routes = device.resident_buffer_from(np.array([BF16_ONE << 16], dtype=np.uint32))
+    inter = device.create_resident_buffer(plan.frame_words * 4)
+    wt = device.resident_buffer_from(np.full(W * W // 2, 0x22, dtype=np.uint8))
+    sc = device.resident_buffer_from(np.full(W * W // 32, 120, dtype=np.uint8))
+    gaddr = address_table(device, [wt, sc, wt, sc])
+    gslots = device.resident_buffer_from(np.array([0, 1, 2, 3], dtype=np.uint32))
+    control = device.resident_buffer_from(np.array([1, 0, 0, 0, 0, 0, 0], dtype=np.uint32))
+
+    def run(slots):
+        inter.fill(0)
+        inter.write_bytes(np.array([0], dtype=np.uint32), offset=plan.data_words * 4)
+        plan.independent_sparse_moe_gate_up(1, hidden, routes, inter, gaddr, slots, control)
+        return inter.read(np.uint16, W)
+
+    assert run(gslots).all()
+    alias = ResidentBuffer.wrap(device, gslots.device_address(), 16)
+    alias.write_bytes(np.array([0, 1, 0xFFFFFFFF, 3], dtype=np.uint32))  # unbinds w3 behind gslots' back
+    assert run(gslots).all(), "the resolution kept for an unchanged handle is still in use"
+    gslots.mark_dirty()
+    assert not run(gslots).any()
+    assert plan.status() & 4
+    # tables in wrapped buffers are resolved on every call, whichever handle over the memory is passed
+    alias.write_bytes(np.array([0, 1, 2, 3], dtype=np.uint32))
+    assert run(alias).all()
+    again = ResidentBuffer.wrap(device, gslots.device_address(), 16)
+    assert run(again).all()
+    for handle in (alias, again):
+        handle.destroy()
     plan.destroy()
 
 
