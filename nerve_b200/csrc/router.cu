@@ -360,6 +360,111 @@ __global__ void __launch_bounds__(64) router_linear_kernel(const uint16_t* __res
     }
 }
 
+// The same projection for large batches. What bounds the kernel above there is not the arithmetic but the
+// operands: a block of 4 x 16 pairs reads its 20 rows from L2 for 128 multiply-adds a step, and every weight row is
+// fetched again by every block of four tokens. Here a block of 256 threads owns 32 tokens x 16 outputs: the rows of
+// a 128-column chunk are staged in shared memory by 16-byte asynchronous copies (two buffers, the next chunk lands
+// while this one is used) and shared by the block's eight warps, each of which owns 8 tokens x 8 outputs. A thread
+// plays two of the shader's 64 lanes, l and l + 32, for every pair of its warp's tile: the first butterfly step
+// (lane v with lane v ^ 32) is then an add inside the thread and the other five are the usual shuffles. Sums, their
+// order and the roundings are those of router_linear_kernel, bit for bit.
+constexpr int kTileTokens = 32, kTileOutputs = 16, kSubTokens = 8, kSubOutputs = 8;
+__global__ void __launch_bounds__(256, 1) router_linear_tiled_kernel(const uint16_t* __restrict__ x,
+                                                                    const uint16_t* __restrict__ w,
+                                                                    const uint16_t* __restrict__ bias,
+                                                                    uint32_t* __restrict__ logits, uint32_t tokens,
+                                                                    uint32_t hidden, uint32_t outputs) {
+    constexpr int kRows = kTileTokens + kTileOutputs;
+    __shared__ __align__(16) uint32_t stage[2][kRows][64];   // [buffer][token rows, then output rows][word of the chunk]
+    __shared__ float result[kTileTokens][kTileOutputs];
+    grid_dependency_sync();
+    const uint32_t warp = threadIdx.x >> 5, l = threadIdx.x & 31u;
+    const uint32_t t0 = blockIdx.y * kTileTokens, e0 = blockIdx.x * kTileOutputs;
+    const uint32_t ta = (warp >> 1) * kSubTokens, eb = (warp & 1u) * kSubOutputs;  // this warp's corner of the block's tile
+    const uint32_t words = hidden / 2u;
+    const uint32_t chunks = (words + 63u) / 64u;
+    const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
+    const uint32_t* ww = reinterpret_cast<const uint32_t*>(w);
+    // the 16-byte pieces of a chunk this thread copies: row = piece / 16, four words from word 4 (piece % 16)
+    auto fetch = [&](uint32_t chunk, uint32_t buffer) {
+#pragma unroll
+        for (uint32_t i = 0; i < (kRows * 16u) / 256u; i++) {
+            const uint32_t piece = threadIdx.x + 256u * i;
+            const uint32_t row = piece >> 4, col = (piece & 15u) * 4u;
+            const uint32_t cw = chunk * 64u + col;
+            const bool token_row = row < (uint32_t)kTileTokens;
+            const uint32_t index = token_row ? t0 + row : e0 + row - kTileTokens;
+            const bool ok = cw < words && index < (token_row ? tokens : outputs);
+            const uint32_t* src = ok ? (token_row ? xw : ww) + (size_t)index * words + cw : xw;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&stage[buffer][row][col]);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16u : 0u) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[2][kSubTokens][kSubOutputs];
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int a = 0; a < kSubTokens; a++)
+#pragma unroll
+            for (int b = 0; b < kSubOutputs; b++) acc[h][a][b] = 0.0f;
+    fetch(0u, 0u);
+    for (uint32_t chunk = 0; chunk < chunks; chunk++) {
+        const uint32_t buffer = chunk & 1u;
+        if (chunk + 1u < chunks) {
+            fetch(chunk + 1u, buffer ^ 1u);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            // lane l + 32 h of the shader; a lane whose word lies past the row adds nothing (not even zeros: -0 + 0 = +0)
+            if (chunk * 64u + l + 32u * h < words) {
+                uint32_t xr[kSubTokens], wr[kSubOutputs];
+#pragma unroll
+                for (int a = 0; a < kSubTokens; a++) xr[a] = stage[buffer][ta + a][l + 32u * h];
+#pragma unroll
+                for (int b = 0; b < kSubOutputs; b++) wr[b] = stage[buffer][kTileTokens + eb + b][l + 32u * h];
+#pragma unroll
+                for (int a = 0; a < kSubTokens; a++) {
+                    const float xl = nvmoe_bf16_to_f32(xr[a]), xh = nvmoe_bf16_to_f32(xr[a] >> 16);
+#pragma unroll
+                    for (int b = 0; b < kSubOutputs; b++) {
+                        acc[h][a][b] = __fmaf_rn(xl, nvmoe_bf16_to_f32(wr[b]), acc[h][a][b]);
+                        acc[h][a][b] = __fmaf_rn(xh, nvmoe_bf16_to_f32(wr[b] >> 16), acc[h][a][b]);
+                    }
+                }
+            }
+        }
+        __syncthreads();  // the buffer is refilled by the fetch of the next round
+    }
+#pragma unroll
+    for (int a = 0; a < kSubTokens; a++)
+#pragma unroll
+        for (int b = 0; b < kSubOutputs; b++) {
+            // butterfly step 32 (lane l with lane l + 32) inside the thread, then 16 .. 1 across the warp
+            const float sum = warp_butterfly_sum(__fadd_rn(acc[0][a][b], acc[1][a][b]));
+            if (l == 0u) result[ta + a][eb + b] = sum;
+        }
+    __syncthreads();
+    const uint32_t out_words = (outputs + 1u) / 2u;
+    for (uint32_t i = threadIdx.x; i < kTileTokens * (kTileOutputs / 2); i += 256u) {
+        const uint32_t a = i / (kTileOutputs / 2), bw = i % (kTileOutputs / 2);
+        const uint32_t t = t0 + a, e = e0 + 2u * bw;
+        if (t >= tokens || e >= outputs) continue;
+        float lo = result[a][2u * bw], hi = result[a][2u * bw + 1u];
+        if (bias) {
+            lo = __fadd_rn(lo, nvmoe_bf16_to_f32(bias[e]));
+            if (e + 1u < outputs) hi = __fadd_rn(hi, nvmoe_bf16_to_f32(bias[e + 1u]));
+        }
+        uint32_t word = nvmoe_f32_to_bf16(lo);
+        if (e + 1u < outputs) word |= nvmoe_f32_to_bf16(hi) << 16;
+        logits[(size_t)t * out_words + e / 2u] = word;
+    }
+}
+
 }  // namespace
 
 void launch_router(const RouterLaunch& p, cudaStream_t stream) {
@@ -378,6 +483,9 @@ void launch_router_linear(const uint16_t* x, const uint16_t* w, const uint16_t* 
     if (tokens <= 256u) {
         dim3 grid((outputs + 3u) / 4u, (tokens + 1u) / 2u);
         launch_chained(router_linear_kernel<2, 4>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
+    } else if (hidden % 8u == 0u && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0u) {
+        dim3 grid((outputs + kTileOutputs - 1u) / kTileOutputs, (tokens + kTileTokens - 1u) / kTileTokens);
+        launch_chained(router_linear_tiled_kernel, grid, dim3(256), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
     } else {
         dim3 grid((outputs + 15u) / 16u, (tokens + 3u) / 4u);
         launch_chained(router_linear_kernel<4, 16>, grid, dim3(64), 0, stream, x, w, bias, logits, tokens, hidden, outputs);
