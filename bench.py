@@ -114,7 +114,7 @@ def timed_blocks(torch, runner, steps, warmup, scratch=None, sample_clocks=False
     if sampler:
         sampler.start()
     blocks, total, launches = [], 0.0, 0
-    while total < min_seconds * 1e3 and len(blocks) < max_blocks:
+    while (total < min_seconds * 1e3 or not blocks) and len(blocks) < max_blocks:
         if scratch is not None:
             flush_l2(torch, scratch)
         before = runner.plan.launches()
@@ -337,7 +337,7 @@ def measure_workload(torch, args, workload, tokens, peaks, peak_kind, probe, sha
         runner.plan.set_profiling(False)
         for _ in range(max(3, runner.n_banks + 1)):
             runner.step_host()
-        e2e_ms, t_end = [], time.perf_counter() + 0.3
+        e2e_ms, t_end = [], time.perf_counter() + 0.6 * min_seconds
         while len(e2e_ms) < steps or (time.perf_counter() < t_end and len(e2e_ms) < 5000):
             e2e_ms.append(runner.step_host())
         e2e = statistics.median(e2e_ms)
@@ -395,7 +395,7 @@ def run_single_gpu(args, cfg, tokens, bound):
         dev.close()
 
     head, runner = measure_workload(torch, args, args.workload, tokens, peaks, peak_kind, probe, scratch=scratch,
-                                    sample_clocks=True, with_e2e=True)
+                                    sample_clocks=True, with_e2e=True, min_seconds=args.min_seconds)
     line = {
         "metric": METRIC, "value": head["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -403,7 +403,7 @@ def run_single_gpu(args, cfg, tokens, bound):
         "config": workload_config(args, cfg, tokens),
         "run": {"distinct_experts": head["distinct_experts"], "expert_path": head["expert_path"], "l2": head["l2"],
                 "parallelism": "single device"},
-        "timing": head["timing"] | {"rule": f"blocks of {args.steps} steps repeated until {MIN_TIMED_SECONDS} s of device time; "
+        "timing": head["timing"] | {"rule": f"blocks of {args.steps} steps repeated until {args.min_seconds} s of device time; "
                                             "ms_per_step is the median block"},
         "clocks": head["clocks"], "roofline": head["roofline"], "e2e": head["e2e"],
         "gpu_launches": head["launches_per_block"], "launches_per_step": head["launches_per_step"],
@@ -451,7 +451,7 @@ def ep_timed(torch, dist, layer, step_fn, steps, min_seconds, local):
     device time. Every rank sees the same (all-reduced) times, so every rank stops after the same block."""
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     blocks, total, launches = [], 0.0, 0
-    while total < min_seconds * 1e3 and len(blocks) < 200:
+    while (total < min_seconds * 1e3 or not blocks) and len(blocks) < 200:
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
@@ -653,6 +653,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the check of the timed output against the CPU checker")
     ap.add_argument("--no-probe", action="store_true", help="skip the tensor-pipe peak probe")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="device time the timed blocks of --steps steps are repeated for (0: one block, for a profiler capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 

@@ -47,8 +47,8 @@ def assert_close(got_bf16, want_bf16, what=""):
 
 
 def record_metrics(case_id: str, metrics: dict) -> None:
-    """Appends the measured error of one parity case to gpurun_out/parity_metrics.jsonl (the folder a GPU
-    run brings back), so that the figures behind a green run can be kept."""
+    """Appends the measured error of one parity case to parity_metrics.jsonl in the run-output folder at the
+    repository root, so that the figures behind a green run can be kept (profiles/ holds a summary)."""
     folder = Path(__file__).resolve().parent.parent / "gpurun_out"
     try:
         folder.mkdir(exist_ok=True)
