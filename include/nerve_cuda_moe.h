@@ -94,8 +94,10 @@ enum {
     NVMOE_STATUS_ROUTE_OUT_OF_RANGE = 1u << 1,/* compact slot or expert id out of range: skipped */
     NVMOE_STATUS_EXPERT_NOT_RESIDENT = 1u << 2,/* address record failed validation: skipped */
     NVMOE_STATUS_WAIT_EXPIRED = 1u << 3,      /* a bounded in-kernel wait gave up */
-    NVMOE_STATUS_EXCHANGE_OVERFLOW = 1u << 4  /* more rows were bound for one rank than its segment holds: the
+    NVMOE_STATUS_EXCHANGE_OVERFLOW = 1u << 4, /* more rows were bound for one rank than its segment holds: the
                                                  excess routes were left out (their rows count as zeros) */
+    NVMOE_STATUS_INTERNAL = 1u << 5           /* a kernel found a precondition of its own broken (shared-memory
+                                                 alignment) and did nothing */
 };
 
 /*

@@ -47,7 +47,6 @@ constexpr uint32_t kFirstProducerThread = 192u;    // warps 0-3 epilogue, 4 MMA,
 constexpr uint32_t kTmaBoxBytes = kBlockM * 64u;   // global bytes of one 128 x 128 box of 4-bit codes
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
-constexpr uint32_t kSmemBudget = 225u * 1024u;  // of the 227 KB a CTA may have; the rest is alignment slack and barriers
 constexpr uint32_t kMaxStages = 8u;
 
 struct TileList {
@@ -90,20 +89,40 @@ struct Config {
     // matrix, so a stage of one block would carry half the bytes of a gate/up stage for the same
     // barrier traffic and issue overhead: it takes two blocks a stage.
     static constexpr uint32_t kSub = kMatrices == 2u ? 1u : 2u;
-    // every block starts on a 1024-byte boundary: the 128-byte swizzle is a function of the address
-    static constexpr uint32_t kSubBytes =
-        (kMatrices * kATileBytes + kBTileBytes + (kMatrices + 1u) * kScaleBlockBytes + 1023u) / 1024u * 1024u;
-    static constexpr uint32_t kStageBytes = kSub * kSubBytes;
-    static constexpr uint32_t kStagesRaw = kSmemBudget / kStageBytes;
-    static constexpr uint32_t kStages = kStagesRaw > kMaxStages ? kMaxStages : kStagesRaw;
+    // Shared memory is three regions, each an array over (slot, K block of the stage): the weight tiles, the token
+    // tiles (both need 1024-byte alignment: the 128-byte swizzle is a function of the address) and the scale blocks.
+    // Kept apart, nothing has to be padded to a 1024-byte boundary per K block, and the throughput of the pipeline is
+    // the bytes its slots hold in flight: for the narrow down tiles the padding was the difference between five
+    // slots and six.
+    static constexpr uint32_t kABytes = kMatrices * kATileBytes;               // weight tiles of one K block
+    // weight scale blocks, then the token scale block: 32 entries of 16 bytes, entry n % 32 holding token n's scales.
+    // A tile of 16 tokens fills half of it; the copy into tensor memory still reads 512 bytes, the second half
+    // being whatever follows in shared memory (the next block's scales, or the barriers): scales of token columns
+    // that do not exist.
+    static constexpr uint32_t kSfBytes = kMatrices * kScaleBlockBytes + (N_TILE <= 16u ? kScaleBlockBytes / 2u : kScaleBlockBytes);
+    static constexpr uint32_t kStageBytes = kSub * (kABytes + kBTileBytes + kSfBytes);
+    static constexpr uint32_t kBarrierBytes = 256u;
+    // The arrays start at the first 1024-byte boundary of the dynamic shared memory. Room for that round-up is set
+    // aside unless leaving it out buys another slot; the kernel then insists on a base that is aligned already
+    // (it is when the kernel has no static shared memory) and does nothing, with NVMOE_STATUS_INTERNAL, otherwise.
+    static constexpr uint32_t kSmemMax = 227u * 1024u;
+    static constexpr uint32_t stages_for(uint32_t slack) {
+        const uint32_t n = (kSmemMax - kBarrierBytes - slack) / kStageBytes;
+        return n > kMaxStages ? kMaxStages : n;
+    }
+    static constexpr bool kNeedsAlignedBase = stages_for(0u) > stages_for(1024u);
+    static constexpr uint32_t kStages = stages_for(kNeedsAlignedBase ? 0u : 1024u);
+    static constexpr uint32_t kBlocks = kStages * kSub;                        // K blocks resident at once
+    static constexpr uint32_t kBRegion = kBlocks * kABytes;                    // offset of the token tiles
+    static constexpr uint32_t kSfRegion = kBRegion + kBlocks * kBTileBytes;    // offset of the scale blocks
     static constexpr uint32_t kAccColumns = kMatrices * N_TILE;
     static constexpr uint32_t kAccStages = (2u * kAccColumns + 16u <= 512u) ? 2u : 1u;
     static constexpr uint32_t kScaleColumns = 4u * (kMatrices + 1u);
     static constexpr uint32_t kColumnsUsed = kAccStages * kAccColumns + kScaleColumns;
     static constexpr uint32_t kTmemColumns = kColumnsUsed <= 32u ? 32u : kColumnsUsed <= 64u ? 64u : kColumnsUsed <= 128u ? 128u : kColumnsUsed <= 256u ? 256u : 512u;
-    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024u /* alignment slack */ + 256u /* barriers */;
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + (kNeedsAlignedBase ? 0u : 1024u) + kBarrierBytes;
     static_assert(N_TILE % 16u == 0u && N_TILE >= 16u && N_TILE <= 128u, "token tile");
-    static_assert(kBTileBytes % 1024u == 0u, "the scale blocks behind the token tile keep their alignment");
+    static_assert(kBTileBytes % 1024u == 0u && kABytes % 1024u == 0u, "operand tiles keep their 1024-byte alignment");
     static_assert(kStages >= 3u, "pipeline too shallow");
 };
 
@@ -147,7 +166,13 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023u));
     Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kStages * C::kStageBytes);
+    static_assert(sizeof(Barriers) <= C::kBarrierBytes, "barrier block");
     volatile uint32_t* abort_flag = &bars->abort;
+    if (C::kNeedsAlignedBase && smem != smem_raw) {  // (uniform) no room was set aside for the round-up
+        grid_dependency_sync();
+        if (threadIdx.x == 0u) raise_status(p.status, NVMOE_STATUS_INTERNAL);
+        return;
+    }
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t H = p.g.hidden_size, I = p.g.intermediate_size;
@@ -274,7 +299,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                         withhold = false;
                     } else {
                     // token rows (zeros past the edge of K) and weight scale blocks of every K block present
-                    const uint32_t stage = smem_u32(smem + slot * C::kStageBytes);
+                    const uint32_t smem_base = smem_u32(smem);
                     // a box of one-byte elements brings twice the bytes of a box of packed 4-bit codes
                     const uint32_t box_bytes = cur.format == kFormatCompact ? kTmaBoxBytes : 2u * kTmaBoxBytes;
                     *reinterpret_cast<volatile uint32_t*>(&bars->format[slot]) = cur.format;
@@ -282,17 +307,18 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                                                                  present * (C::kBTileBytes + C::kMatrices * kScaleBlockBytes));
                     for (uint32_t sub = 0; sub < present; sub++) {
                         const uint32_t kb = ks * C::kSub + sub;
-                        const uint32_t block = stage + sub * C::kSubBytes;
+                        const uint32_t block = slot * C::kSub + sub;  // index into the three shared-memory arrays
                         if (sub < whole) {
 #pragma unroll
                             for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                                tma_load_3d(block + mx * kATileBytes, maps + C::source_of(mx) * 128u, 0, (int)kb,
+                                tma_load_3d(smem_base + block * C::kABytes + mx * kATileBytes, maps + C::source_of(mx) * 128u, 0, (int)kb,
                                             row0 + (int)C::row_shift(mx), &bars->full[slot]);  // rows past the matrix: zeros
                         }
-                        tma_load_2d(block + C::kMatrices * kATileBytes, p.act_tmap, (int)(kb * kBlockK), token0, &bars->full[slot]);
+                        tma_load_2d(smem_base + C::kBRegion + block * C::kBTileBytes, p.act_tmap, (int)(kb * kBlockK), token0,
+                                    &bars->full[slot]);
 #pragma unroll
                         for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                            bulk_copy_g2s(block + C::kMatrices * kATileBytes + C::kBTileBytes + mx * kScaleBlockBytes,
+                            bulk_copy_g2s(smem_base + C::kSfRegion + block * C::kSfBytes + mx * kScaleBlockBytes,
                                           scale_blocks[mx] + (size_t)kb * kScaleBlockBytes, kScaleBlockBytes, &bars->full[slot]);
                     }
                     }
@@ -386,7 +412,8 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 for (uint32_t sub = 0; sub < C::kSub; sub++) {
                 const uint32_t kb = ks * C::kSub + sub;
                 if (kb >= k_blocks) break;  // the last stage of an odd count holds one block
-                unsigned char* stage = smem + slot * C::kStageBytes + sub * C::kSubBytes;
+                const uint32_t block = slot * C::kSub + sub;  // index into the three shared-memory arrays
+                unsigned char* a_tiles = smem + block * C::kABytes;
                 const uint32_t k_left = k_dim - kb * kBlockK;  // elements of K from this block on
                 const bool chunk_ok = my_c * 16u < k_left;
                 // weights: 8-byte pieces of 16 codes into the low half of 16-byte slots
@@ -394,7 +421,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 if (!USE_TMA || k_left < kBlockK) {
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++) {
-                    const uint32_t a_dst = smem_u32(stage + mx * kATileBytes) + my_dst;
+                    const uint32_t a_dst = smem_u32(a_tiles + mx * kATileBytes) + my_dst;
                     const uint8_t* src = wcol[mx] + kb * (bytes_form ? 128u : 64u);
 #pragma unroll
                     for (uint32_t i = 0; i < kBlockM / kRowsPerPass; i++) {
@@ -409,7 +436,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 }
                 }
                 // activations: 16-byte pieces of 16 E4M3 codes (with TMA the whole tile is one box)
-                const uint32_t b_dst = smem_u32(stage + C::kMatrices * kATileBytes) + my_dst;
+                const uint32_t b_dst = smem_u32(smem + C::kBRegion + block * C::kBTileBytes) + my_dst;
                 if (!USE_TMA) {
 #pragma unroll
                 for (uint32_t i = 0; i < kTokenPasses; i++) {
@@ -423,7 +450,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 }
                 // scales: the derived copy already has the 32x16-byte layout tcgen05.cp reads, one 512-byte
                 // block per (row tile, K block); token scales are gathered four bytes (one K block) a row
-                unsigned char* sf = stage + C::kMatrices * kATileBytes + C::kBTileBytes;
+                unsigned char* sf = smem + C::kSfRegion + block * C::kSfBytes;
                 // (threads from the far end of the producer group, so that with few tokens a tile these are not
                 // the threads that carry the token rows)
                 const uint32_t st = kProducerThreads - 1u - pt;
@@ -470,12 +497,11 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             // K steps of a stage are unrolled with compile-time descriptors offsets and scale ids.
             constexpr uint32_t kIdescCompact = idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, kBlockM, N_TILE);
             constexpr uint32_t kIdescBytes = idesc_mxf8f6f4(kFmtE4M3, kFmtE4M3, kBlockM, N_TILE);  // weights as E4M3 bytes
-            constexpr uint32_t kStageUnits = C::kStageBytes >> 4;  // descriptor start addresses count 16 bytes
-            constexpr uint32_t kSubUnits = C::kSubBytes >> 4;
+            // descriptor start addresses count 16 bytes
             const uint32_t base = smem_u32(smem);
             const uint64_t a_desc0 = desc_k_major_sw128(base);
-            const uint64_t b_desc0 = desc_k_major_sw128(base + C::kMatrices * kATileBytes);
-            const uint64_t sf_desc0 = desc_scale_block(base + C::kMatrices * kATileBytes + C::kBTileBytes);
+            const uint64_t b_desc0 = desc_k_major_sw128(base + C::kBRegion);
+            const uint64_t sf_desc0 = desc_scale_block(base + C::kSfRegion);
             const uint32_t tail_groups = (k_dim % kBlockK) / 32u;  // K steps of a trailing partial block, 0 = none
             const uint32_t sfb_tmem = tmem_scales + 4u * C::kMatrices;
             uint32_t it = 0u, acc_it = 0u, slot = 0u, full_parity = 0u;
@@ -505,8 +531,10 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                     for (uint32_t sub = 0; sub < C::kSub; sub++) {
                     const uint32_t kb = ks * C::kSub + sub;
                     if (kb >= k_blocks) break;
-                    const uint64_t off = (uint64_t)(slot * kStageUnits + sub * kSubUnits);
-                    const uint64_t a_desc = a_desc0 + off, b_desc = b_desc0 + off, sf_desc = sf_desc0 + off;
+                    const uint32_t block = slot * C::kSub + sub;  // index into the three shared-memory arrays
+                    const uint64_t a_desc = a_desc0 + (uint64_t)(block * (C::kABytes >> 4));
+                    const uint64_t b_desc = b_desc0 + (uint64_t)(block * (C::kBTileBytes >> 4));
+                    const uint64_t sf_desc = sf_desc0 + (uint64_t)(block * (C::kSfBytes >> 4));
 #pragma unroll
                     for (uint32_t mx = 0; mx <= C::kMatrices; mx++)
                         tc_copy_scales(tmem_scales + 4u * mx, sf_desc + mx * (kScaleBlockBytes >> 4));
