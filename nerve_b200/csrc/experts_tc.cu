@@ -94,6 +94,7 @@ struct Config {
     // Kept apart, nothing has to be padded to a 1024-byte boundary per K block, and the throughput of the pipeline is
     // the bytes its slots hold in flight: for the narrow down tiles the padding was the difference between five
     // slots and six.
+    static constexpr uint32_t kScaleStride = kSources * kScaleBlockBytes;      // between K blocks of the derived weight scales
     static constexpr uint32_t kABytes = kMatrices * kATileBytes;               // weight tiles of one K block
     // weight scale blocks, then the token scale block: 32 entries of 16 bytes, entry n % 32 holding token n's scales.
     // A tile of 16 tokens fills half of it; the copy into tensor memory still reads 512 bytes, the second half
@@ -282,7 +283,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 const uint8_t* scale_blocks[C::kMatrices];
 #pragma unroll
                 for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                    scale_blocks[mx] = cur.ts[C::source_of(mx)] + (size_t)scale_tile(m_tile, mx) * k_blocks * kScaleBlockBytes;
+                    scale_blocks[mx] = cur.ts[C::source_of(mx)] + (size_t)scale_tile(m_tile, mx) * k_blocks * C::kScaleStride;
                 for (uint32_t ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait(&bars->empty[slot], empty_parity, abort_flag, wait_limit)) {
                         alive = false;
@@ -316,10 +317,16 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                         }
                         tma_load_2d(smem_base + C::kBRegion + block * C::kBTileBytes, p.act_tmap, (int)(kb * kBlockK), token0,
                                     &bars->full[slot]);
+                        if (C::kSources == 2u) {
+                            // the gate and the up block of this (row tile, K block) are neighbours in the derived copy
+                            bulk_copy_g2s(smem_base + C::kSfRegion + block * C::kSfBytes, scale_blocks[0] + (size_t)kb * C::kScaleStride,
+                                          2u * kScaleBlockBytes, &bars->full[slot]);
+                        } else {
 #pragma unroll
-                        for (uint32_t mx = 0; mx < C::kMatrices; mx++)
-                            bulk_copy_g2s(smem_base + C::kSfRegion + block * C::kSfBytes + mx * kScaleBlockBytes,
-                                          scale_blocks[mx] + (size_t)kb * kScaleBlockBytes, kScaleBlockBytes, &bars->full[slot]);
+                            for (uint32_t mx = 0; mx < C::kMatrices; mx++)
+                                bulk_copy_g2s(smem_base + C::kSfRegion + block * C::kSfBytes + mx * kScaleBlockBytes,
+                                              scale_blocks[mx] + (size_t)kb * C::kScaleStride, kScaleBlockBytes, &bars->full[slot]);
+                        }
                     }
                     }
                     stage_it++;
@@ -456,7 +463,7 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
                 const uint32_t st = kProducerThreads - 1u - pt;
                 if (!USE_TMA && st < 32u * C::kMatrices) {
                     const uint32_t mx = st >> 5, l = st & 31u;
-                    const uint8_t* src = cur.ts[mx] + ((size_t)scale_tile(cur.m_tile, mx) * k_blocks + kb) * kScaleBlockBytes + l * 16u;
+                    const uint8_t* src = cur.ts[mx] + ((size_t)scale_tile(cur.m_tile, mx) * k_blocks + kb) * C::kScaleStride + l * 16u;
                     cp_async_16(smem_u32(sf + mx * kScaleBlockBytes + l * 16u), src, 16u);
                 }
                 if (USE_TMA) {
@@ -751,7 +758,10 @@ __global__ void __launch_bounds__(128) derive_scales_kernel(const ExpertPtrs* ex
     const uint64_t* stamp = stamps + ((size_t)e * matrices + mx) * 2u;
     if (stamp[0] == (uint64_t)(uintptr_t)ptrs.s[mx] && stamp[1] == ptrs.gen[mx]) return;
     const uint32_t r = threadIdx.x, row = m_tile * kBlockM + r, row_bytes = cols / 32u;
-    uint8_t* out = const_cast<uint8_t*>(ptrs.ts[mx]) + (size_t)m_tile * k_blocks * kScaleBlockBytes + (r & 31u) * 16u + (r >> 5) * 4u;
+    // (the blocks of an expert's `matrices` tensors are interleaved: block (m_tile, kb) of tensor mx lies at
+    // ((m_tile * k_blocks + kb) * matrices + mx) * 512, and ts[mx] already points at mx * 512)
+    const size_t stride = (size_t)matrices * kScaleBlockBytes;
+    uint8_t* out = const_cast<uint8_t*>(ptrs.ts[mx]) + (size_t)m_tile * k_blocks * stride + (r & 31u) * 16u + (r >> 5) * 4u;
     for (uint32_t kb = 0; kb < k_blocks; kb++) {
         uint32_t word = 0x7f7f7f7fu;
         if (row < rows && ptrs.format == kFormatNativeFp8) {
@@ -764,7 +774,7 @@ __global__ void __launch_bounds__(128) derive_scales_kernel(const ExpertPtrs* ex
                 word |= (uint32_t)(c < row_bytes ? ptrs.s[mx][(size_t)row * row_bytes + c] : 127u) << (8u * j);
             }
         }
-        *reinterpret_cast<uint32_t*>(out + (size_t)kb * kScaleBlockBytes) = word;
+        *reinterpret_cast<uint32_t*>(out + (size_t)kb * stride) = word;
     }
 }
 

@@ -438,7 +438,8 @@ __global__ void resolve_experts_kernel(const uint32_t* addresses, uint32_t addre
         r.format = format;
         if (derived_scales) {
             r.ts[0] = derived_scales + ((size_t)e * matrices) * derived_matrix_bytes;
-            r.ts[1] = params == 4u ? r.ts[0] + derived_matrix_bytes : nullptr;
+            // gate and up blocks of the same (row tile, K block) lie side by side, 512 bytes each: one copy brings both
+            r.ts[1] = params == 4u ? r.ts[0] + 512u : nullptr;
         }
     }
     out[e] = r;
