@@ -48,6 +48,7 @@ constexpr uint32_t kTmaBoxBytes = kBlockM * 64u;   // global bytes of one 128 x 
 constexpr uint32_t kATileBytes = kBlockM * 128u;   // one byte slot per element
 constexpr uint32_t kScaleBlockBytes = 512u;        // 128 rows x 4 scale bytes
 constexpr uint32_t kMaxStages = 8u;
+constexpr uint32_t kWatchWarp = 2u;     // the epilogue warp that polls for a finished accumulator (not on the MMA or TMA warp's scheduler)
 
 struct TileList {
     const uint32_t* tiles;   // (expert << 16) | token tile within the expert
@@ -153,6 +154,7 @@ struct Barriers {
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t format[kMaxStages];  // kFormat* of the weights staged in each slot (written before the slot's arrival)
+    uint32_t acc_ready[2];        // the verdict of the epilogue warp that watches acc_full, for the others
 };
 
 // TRACE compiles the diagnostics in (cycle counters of CTA 0, per-CTA global-timer stamps): the
@@ -607,7 +609,18 @@ __global__ void __launch_bounds__((Config<GATE_UP, N_TILE, USE_TMA, ROW_PAIR>::k
             const uint32_t valid = min(N_TILE, e_end - first);
             const uint32_t acc = acc_it % C::kAccStages;
             const long long e0 = TRACE ? clock64() : 0;
-            if (!mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag, wait_limit)) break;
+            // One warp watches the accumulator's barrier; the others sleep on a hardware barrier until it has a
+            // verdict. A warp that polls takes issue slots from whatever shares its scheduler, and the epilogue warps
+            // (three to a scheduler) wait through most of a tile beside the one thread that feeds the tensor pipe
+            // and the one that issues the copies. Every epilogue warp reaches the hardware barrier in every round,
+            // whatever the verdict, so none is left waiting there.
+            if (warp == kWatchWarp) {
+                const bool ready = mbar_wait_warp(&bars->acc_full[acc], (acc_it / C::kAccStages) & 1u, abort_flag, wait_limit);
+                if (lane == 0u) *reinterpret_cast<volatile uint32_t*>(&bars->acc_ready[acc_it & 1u]) = ready ? 1u : 0u;
+                __threadfence_block();
+            }
+            named_barrier(1u, C::kEpilogueThreads);
+            if (*reinterpret_cast<volatile uint32_t*>(&bars->acc_ready[acc_it & 1u]) == 0u) break;
             if (TRACE) trace_epi_wait += clock64() - e0;
             tc_fence_after();
             const uint32_t row = m_tile * C::kTileRows + quad * 32u + lane;  // (with row pairs: of the first half)
