@@ -250,7 +250,7 @@ int nvmoe_route_compact(nvmoe_plan* plan, uint32_t batch_width, const nvmoe_buff
  * Limits: ceil(batch_width * top_k / 256) * (num_experts + 1) <= 65536 and num_experts <= 1022;
  * larger calls return NVMOE_ERR_INVALID_ARGUMENT with the sizes in nvmoe_last_error.
  * The first call on a device looks up the array's address (no allocation, but a runtime call that is
- * not a stream operation): make one call on each device before starting any stream capture.
+ * not a stream operation); later calls on that device only launch kernels.
  * Every plan and every call on a device shares the one array. Nothing in it has to start at zero
  * (each call writes every word it later reads), so calls that follow one another on one stream need
  * no clearing; calls that overlap on different streams of one device race on it and must be
