@@ -270,6 +270,161 @@ __global__ void __launch_bounds__(128) router_kernel(RouterLaunch p, uint32_t wa
     }
 }
 
+// ---- the same router with a token's experts in registers ------------------------------------------
+// For up to 32 * EPL experts and at most 32 selections a token, without group-limited masking: lane l keeps the
+// experts l, l + 32, .. in registers, lane r keeps selection r once it is made, and everything the kernel above
+// does through shared memory by one lane (the weights, the ascending order, packing, telemetry) is done by the
+// lanes side by side. Every sum that has an order keeps it (values travel by shuffle and are added in the same
+// sequence); the results are bit for bit those of router_kernel, which remains for the other cases.
+template <int EPL>
+__global__ void __launch_bounds__(128) router_reg_kernel(RouterLaunch p) {
+    grid_dependency_sync();
+    constexpr uint32_t kFull = 0xffffffffu;
+    const uint32_t E = p.g.routed_experts;
+    const uint32_t k = p.g.routed_k;
+    const uint32_t kind = p.g.router_kind;
+    const uint32_t always = kind == NVMOE_ROUTER_SCORE_TOPK ? p.g.always_count : 0u;
+    const uint32_t total_k = k + always;
+    const uint32_t total_resources = E + always;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t token = blockIdx.x * 4u + warp;
+    if (token >= p.tokens) return;
+    const uint32_t* row = p.logits + (size_t)token * ((E + 1u) / 2u);
+
+    float val[EPL], score[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; j++) {
+        const uint32_t e = lane + 32u * j;
+        val[j] = e < E ? unpack_logit(row, e) : 0.0f;
+        score[j] = 0.0f;
+    }
+    // ---- activation and selection score ---------------------------------------------------
+    if (kind == NVMOE_ROUTER_SCORE_TOPK) {
+        if (p.g.activation == NVMOE_ACT_SOFTMAX) {
+            float smax = kNegInf;
+#pragma unroll
+            for (int j = 0; j < EPL; j++)
+                if (lane + 32u * j < E) smax = fmaxf(smax, val[j]);
+            smax = warp_max(smax);
+            float lo = 0.0f, hi = 0.0f;  // virtual lanes `lane` and `lane + 32` of a 64-wide group
+#pragma unroll
+            for (int j = 0; j < EPL; j++) {
+                if (lane + 32u * j < E) {
+                    val[j] = nvmoe_expf(__fsub_rn(val[j], smax));
+                    if (j & 1) hi = __fadd_rn(hi, val[j]); else lo = __fadd_rn(lo, val[j]);
+                }
+            }
+            const float sden = warp_butterfly_sum(__fadd_rn(lo, hi));
+#pragma unroll
+            for (int j = 0; j < EPL; j++) val[j] = __fdiv_rn(val[j], sden);
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPL; j++)
+                val[j] = p.g.activation == NVMOE_ACT_SIGMOID ? nvmoe_sigmoidf(val[j]) : __fsqrt_rn(nvmoe_softplusf(val[j]));
+        }
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            const uint32_t e = lane + 32u * j;
+            score[j] = e < E ? __fadd_rn(val[j], read_bias(p.bias, p.g.bias_dtype, e)) : 0.0f;
+        }
+    } else if (kind == NVMOE_ROUTER_TOPK_SOFTMAX) {
+#pragma unroll
+        for (int j = 0; j < EPL; j++) score[j] = val[j];
+    } else {
+        const bool sigmoid = p.g.activation == NVMOE_ACT_SIGMOID;
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            const uint32_t e = lane + 32u * j;
+            float v = val[j];
+            if (p.g.logit_softcap > 0.0f) v = __fmul_rn(nvmoe_tanhf(__fdiv_rn(v, p.g.logit_softcap)), p.g.logit_softcap);
+            val[j] = v;
+            score[j] = e < E ? __fadd_rn(sigmoid ? nvmoe_sigmoidf(v) : v, read_bias(p.bias, p.g.bias_dtype, e)) : 0.0f;
+        }
+    }
+
+    // ---- k rounds of arg-max: lane r keeps selection r ---------------------------------------
+    uint32_t taken = 0u, my_e = kUnboundSlot;
+    float my_v = 0.0f;
+    bool missing = false;
+    for (uint32_t r = 0; r < k; r++) {
+        float best = kNegInf, best_v = 0.0f;
+        uint32_t best_e = kUnboundSlot;
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            const uint32_t e = lane + 32u * j;
+            if (e < E && ((taken >> j) & 1u) == 0u && better(score[j], e, best, best_e)) {
+                best = score[j];
+                best_e = e;
+                best_v = val[j];
+            }
+        }
+        float s = best;
+        uint32_t winner = best_e;
+        warp_argmax(s, winner);
+        if (winner == kUnboundSlot) {
+            missing = true;
+            break;
+        }
+        // the winner is the best candidate of the lane that owns it
+        const float winner_v = __shfl_sync(kFull, best_v, winner & 31u);
+        if (lane == (winner & 31u)) taken |= 1u << (winner >> 5);
+        if (lane == r) {
+            my_e = winner;
+            my_v = winner_v;
+        }
+    }
+    uint32_t* out = p.routes + (size_t)token * total_k;
+    if (missing) {
+        // no selectable score (NaN logits): fail closed instead of indexing out of bounds
+        if (lane == 0u) {
+            for (uint32_t r = 0; r < total_k; r++) out[r] = 0u;
+            raise_status(p.status, NVMOE_STATUS_ROUTE_NONFINITE);
+        }
+        return;
+    }
+
+    // ---- weights, in the summation orders the shaders fix ----------------------------------
+    float w = 0.0f;
+    if (kind == NVMOE_ROUTER_SCORE_TOPK) {
+        float den = 0.0f;
+        if (p.g.normalize_selected)
+            for (uint32_t r = 0; r < k; r++) den = __fadd_rn(den, __shfl_sync(kFull, my_v, r));
+        w = p.g.normalize_selected ? __fmul_rn(__fdiv_rn(my_v, den), p.g.routed_scale) : __fmul_rn(my_v, p.g.routed_scale);
+        if (lane >= k && lane < total_k) {
+            my_e = E + (lane - k);
+            w = p.g.always_weight;
+        }
+    } else {
+        const bool sigmoid = kind == NVMOE_ROUTER_TOPK_ROUTED && p.g.activation == NVMOE_ACT_SIGMOID;
+        const bool divide = kind == NVMOE_ROUTER_TOPK_SOFTMAX || p.g.normalize_selected || !sigmoid;
+        const float maximum = __shfl_sync(kFull, my_v, 0);
+        const float t = sigmoid ? nvmoe_sigmoidf(my_v) : nvmoe_expf(__fsub_rn(my_v, maximum));
+        float den = 0.0f;
+        for (uint32_t r = 0; r < k; r++) den = __fadd_rn(den, __shfl_sync(kFull, t, r));
+        w = divide ? __fdiv_rn(t, den) : t;
+    }
+
+    // ---- ascending expert id, pack, telemetry ----------------------------------------------------
+    uint32_t rank = 0u;
+    for (uint32_t q = 0; q < total_k; q++) {
+        const uint32_t other = __shfl_sync(kFull, my_e, q);
+        if (other < my_e) rank++;
+    }
+    if (lane < total_k) {
+        out[rank] = (nvmoe_f32_to_bf16(w) << 16) | my_e;
+        if (p.telemetry) atomicAdd(p.telemetry + my_e, 1u);
+    }
+    if (p.telemetry) {
+        for (uint32_t q = 0; q < total_k; q++) {
+            const uint32_t right = __shfl_sync(kFull, my_e, q);
+            if (lane < total_k && my_e < right) {
+                const uint32_t preceding = my_e * (2u * total_resources - my_e - 1u) / 2u;
+                atomicAdd(p.telemetry + total_resources + preceding + right - my_e - 1u, 1u);
+            }
+        }
+    }
+}
+
 // ---- router projection ----------------------------------------------------------------------
 // The shader gives every output row 64 lanes that stride over the packed input words with two
 // f32 fma per word and then sums the lanes.  Here a block of 64 threads owns a TT x ET tile of
@@ -469,6 +624,20 @@ __global__ void __launch_bounds__(256, 1) router_linear_tiled_kernel(const uint1
 
 void launch_router(const RouterLaunch& p, cudaStream_t stream) {
     const uint32_t E = p.g.routed_experts;
+    const uint32_t total_k = p.g.routed_k + (p.g.router_kind == NVMOE_ROUTER_SCORE_TOPK ? p.g.always_count : 0u);
+    // the routed form's softmax over all experts (neither normalised over the selection nor sigmoid) sums in expert order
+    const bool sums_all = p.g.router_kind == NVMOE_ROUTER_TOPK_ROUTED && !p.g.normalize_selected && p.g.activation != NVMOE_ACT_SIGMOID;
+    if (E <= 256u && total_k <= 32u && p.g.n_group == 0u && !sums_all && p.g.router_kind <= NVMOE_ROUTER_TOPK_ROUTED) {
+        const dim3 grid((p.tokens + 3u) / 4u), block(128);
+        if (E <= 32u) {
+            launch_chained(router_reg_kernel<1>, grid, block, 0, stream, p);
+        } else if (E <= 128u) {
+            launch_chained(router_reg_kernel<4>, grid, block, 0, stream, p);
+        } else {
+            launch_chained(router_reg_kernel<8>, grid, block, 0, stream, p);
+        }
+        return;
+    }
     const size_t per_warp = (size_t)E * 12u + kMaxTopK * 8u + 32u * 4u;
     uint32_t warps = E <= 1024u ? 4u : 1u;
     size_t smem = per_warp * warps;
