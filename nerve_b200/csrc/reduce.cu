@@ -44,15 +44,26 @@ __global__ void __launch_bounds__(256) reduce_vec_kernel(const uint4* __restrict
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[j] = 0.0f;
-        for (uint32_t r = 0; r < K; r++) {
-            // a route the down stage skipped (computed[route] says "nowhere") counts as a row of zeros
-            const bool skipped = computed && computed[(size_t)t * K + r] == kUnboundSlot;
-            const uint4 c = skipped ? make_uint4(0u, 0u, 0u, 0u) : in[(size_t)r * hidden_vecs];
-            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+        // four routes at a time: their marks and rows are fetched together (one memory round trip instead of one
+        // per route), the adds keep the route order
+        for (uint32_t r0 = 0; r0 < K; r0 += 4u) {
+            bool skipped[4];
+            uint4 c[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                acc[2 * j] = nvmoe_round_bf16(__fadd_rn(acc[2 * j], nvmoe_bf16_to_f32(w[j])));
-                acc[2 * j + 1] = nvmoe_round_bf16(__fadd_rn(acc[2 * j + 1], nvmoe_bf16_to_f32(w[j] >> 16)));
+            for (uint32_t u = 0; u < 4u; u++)
+                // a route the down stage skipped (computed[route] says "nowhere") counts as a row of zeros
+                skipped[u] = r0 + u >= K || (computed && __ldg(computed + (size_t)t * K + r0 + u) == kUnboundSlot);
+#pragma unroll
+            for (uint32_t u = 0; u < 4u; u++) c[u] = skipped[u] ? make_uint4(0u, 0u, 0u, 0u) : in[(size_t)(r0 + u) * hidden_vecs];
+#pragma unroll
+            for (uint32_t u = 0; u < 4u; u++) {
+                if (r0 + u >= K) break;
+                const uint32_t w[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[2 * j] = nvmoe_round_bf16(__fadd_rn(acc[2 * j], nvmoe_bf16_to_f32(w[j])));
+                    acc[2 * j + 1] = nvmoe_round_bf16(__fadd_rn(acc[2 * j + 1], nvmoe_bf16_to_f32(w[j] >> 16)));
+                }
             }
         }
         uint4 out;
@@ -78,14 +89,24 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const uint4* __restr
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[j] = 0.0f;
-        for (uint32_t r = 0; r < K; r++) {
-            const uint32_t row = __ldg(gather + (size_t)t * K + r);
-            const uint4 c = row == kUnboundSlot ? make_uint4(0u, 0u, 0u, 0u) : rows[(size_t)row * hidden_vecs + vec];
-            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+        // four routes at a time, as in reduce_vec_kernel: the row numbers together, then the rows together
+        for (uint32_t r0 = 0; r0 < K; r0 += 4u) {
+            uint32_t row[4];
+            uint4 c[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                acc[2 * j] = nvmoe_round_bf16(__fadd_rn(acc[2 * j], nvmoe_bf16_to_f32(w[j])));
-                acc[2 * j + 1] = nvmoe_round_bf16(__fadd_rn(acc[2 * j + 1], nvmoe_bf16_to_f32(w[j] >> 16)));
+            for (uint32_t u = 0; u < 4u; u++) row[u] = r0 + u < K ? __ldg(gather + (size_t)t * K + r0 + u) : kUnboundSlot;
+#pragma unroll
+            for (uint32_t u = 0; u < 4u; u++)
+                c[u] = row[u] == kUnboundSlot ? make_uint4(0u, 0u, 0u, 0u) : rows[(size_t)row[u] * hidden_vecs + vec];
+#pragma unroll
+            for (uint32_t u = 0; u < 4u; u++) {
+                if (r0 + u >= K) break;
+                const uint32_t w[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[2 * j] = nvmoe_round_bf16(__fadd_rn(acc[2 * j], nvmoe_bf16_to_f32(w[j])));
+                    acc[2 * j + 1] = nvmoe_round_bf16(__fadd_rn(acc[2 * j + 1], nvmoe_bf16_to_f32(w[j] >> 16)));
+                }
             }
         }
         uint4 out;

@@ -842,7 +842,17 @@ __global__ void __launch_bounds__(256) ep_gather_rows_kernel(const uint4* __rest
             continue;
         }
         const uint4* from = src + (size_t)(s / divide) * row_vec;
-        for (uint32_t c = lane; c < row_vec; c += 32u) dst[(size_t)r * row_vec + c] = from[c];
+        uint4* to = dst + (size_t)r * row_vec;
+        // eight loads in flight a lane (see ep_pad_kernel)
+        for (uint32_t c0 = lane; c0 < row_vec; c0 += 256u) {
+            uint4 piece[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; u++)
+                if (c0 + 32u * u < row_vec) piece[u] = __ldg(from + c0 + 32u * u);
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; u++)
+                if (c0 + 32u * u < row_vec) to[c0 + 32u * u] = piece[u];
+        }
     }
 }
 
@@ -878,7 +888,17 @@ __global__ void __launch_bounds__(256) ep_pad_kernel(const uint4* __restrict__ h
             send_index[i] = slot;
         }
         const uint4* from = hidden + (size_t)(i / K) * row_vec;
-        for (uint32_t c = lane; c < row_vec; c += 32u) rows_out[(size_t)slot * row_vec + c] = from[c];
+        uint4* to = rows_out + (size_t)slot * row_vec;
+        // eight loads in flight a lane: a row copied piece by piece costs one memory round trip per piece
+        for (uint32_t c0 = lane; c0 < row_vec; c0 += 256u) {
+            uint4 piece[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; u++)
+                if (c0 + 32u * u < row_vec) piece[u] = __ldg(from + c0 + 32u * u);
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; u++)
+                if (c0 + 32u * u < row_vec) to[c0 + 32u * u] = piece[u];
+        }
     }
 }
 
